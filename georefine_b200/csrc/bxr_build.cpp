@@ -1,0 +1,501 @@
+// Host builder and host twin of the BXR1 resident layout (see bxr_format.h for the layout itself).
+//
+// bxr_build re-codes decoded BF16 words (the output of the BCTX index walk) into the image the fused
+// kernels stream; bxr_decode_host walks an image exactly the way a GPU lane does (slot records, forward
+// and backward segment cursors, escape bytes) and returns the words, so a loader can bind the image to
+// the frame's source digest before it is uploaded.  This plays the role of the load-time transcode the
+// reference performs for its other resident formats (glc_serve/bctx_v21_transcode.py) and of the digest
+// check in bitexact_context_gpu.py:104-105.
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <memory>
+#include <new>
+#include <thread>
+#include <vector>
+
+#include "bxr_format.h"
+
+namespace {
+
+inline uint32_t exponent_of(uint16_t w) { return (w >> 7) & 0xFFu; }
+inline uint8_t raw_byte_of(uint16_t w) { return uint8_t((w & 0x7Fu) | ((w >> 8) & 0x80u)); }
+
+struct Plan {
+  uint32_t rows, cols, row_blocks, chunks, workers;
+  std::vector<bxr_item> items;
+  std::vector<uint32_t> worker_items;  // workers + 1
+  uint32_t partial_slots = 0;
+};
+
+// Equal shares of the (row block, chunk) sequence; a share is cut at row-block boundaries into items.
+Plan make_plan(uint32_t rows, uint32_t cols, uint32_t workers) {
+  Plan p;
+  p.rows = rows;
+  p.cols = cols;
+  p.row_blocks = (rows + BXR_ROWS - 1) / BXR_ROWS;
+  p.chunks = (cols + BXR_COLS - 1) / BXR_COLS;
+  p.workers = workers;
+  const uint64_t units = uint64_t(p.row_blocks) * p.chunks;
+  p.worker_items.assign(workers + 1, 0);
+  std::vector<uint32_t> parts(p.row_blocks, 0);
+  for (uint32_t w = 0; w < workers; ++w) {
+    uint64_t u = units * w / workers;
+    const uint64_t end = units * (w + 1) / workers;
+    p.worker_items[w] = uint32_t(p.items.size());
+    while (u < end) {
+      const uint32_t rb = uint32_t(u / p.chunks), c0 = uint32_t(u % p.chunks);
+      const uint32_t c1 = uint32_t(std::min<uint64_t>(p.chunks, c0 + (end - u)));
+      bxr_item it{};
+      it.row_block = rb;
+      it.chunk_begin = c0;
+      it.chunk_end = c1;
+      it.part = parts[rb]++;
+      p.items.push_back(it);
+      u += c1 - c0;
+    }
+  }
+  p.worker_items[workers] = uint32_t(p.items.size());
+  for (auto& it : p.items) {
+    it.parts = parts[it.row_block];
+    it.slot = 0;
+  }
+  // Partial tiles of one row block occupy consecutive slots in item (= K) order.
+  std::vector<uint32_t> first(p.row_blocks, 0);
+  uint32_t next = 0;
+  for (uint32_t rb = 0; rb < p.row_blocks; ++rb)
+    if (parts[rb] > 1) { first[rb] = next; next += parts[rb]; }
+  for (auto& it : p.items)
+    if (it.parts > 1) it.slot = first[it.row_block] + it.part;
+  p.partial_slots = next;
+  return p;
+}
+
+struct Source {
+  const uint16_t* words;
+  uint32_t rows, cols;
+  // Padded rows repeat the last row (keeps the statistics).  Padded columns never reach an output (the
+  // activation tile is zero there), so they carry whatever finite word is cheapest to code.
+  uint16_t at(uint32_t r, uint32_t c) const { return words[size_t(std::min(r, rows - 1)) * cols + c]; }
+  uint16_t padded(uint32_t r, uint32_t c, const uint8_t* base) const {
+    return c < cols ? at(r, c) : uint16_t((uint32_t(base[r]) + 10u) << 7);
+  }
+};
+
+void parallel_for(uint32_t n, uint32_t threads, const std::function<void(uint32_t)>& fn) {
+  threads = std::max(1u, std::min(threads, n));
+  if (threads == 1) {
+    for (uint32_t i = 0; i < n; ++i) fn(i);
+    return;
+  }
+  std::atomic<uint32_t> next{0};
+  std::vector<std::thread> pool;
+  for (uint32_t t = 0; t < threads; ++t)
+    pool.emplace_back([&] {
+      for (uint32_t i = next.fetch_add(1); i < n; i = next.fetch_add(1)) fn(i);
+    });
+  for (auto& th : pool) th.join();
+}
+
+// Chooses the exponent window of every row: start from the row's most frequent exponent, then move the
+// window by a few binades if that lowers the row's cost under the tensor-wide nibble statistics.
+std::vector<uint8_t> choose_bases(const Source& src, uint32_t rows_pad, uint32_t threads) {
+  std::vector<uint32_t> hist(size_t(rows_pad) * 256, 0);
+  parallel_for(rows_pad, threads, [&](uint32_t r) {
+    uint32_t* h = &hist[size_t(r) * 256];
+    for (uint32_t c = 0; c < src.cols; ++c) ++h[exponent_of(src.at(r, c))];
+  });
+  std::vector<uint8_t> base(rows_pad);
+  for (uint32_t r = 0; r < rows_pad; ++r) {
+    const uint32_t* h = &hist[size_t(r) * 256];
+    const uint32_t mode = uint32_t(std::max_element(h, h + 256) - h);
+    base[r] = uint8_t(std::min<int>(241, std::max<int>(0, int(mode) - 10)));
+  }
+  for (int round = 0; round < 2; ++round) {
+    double cnt[16] = {0};
+    for (uint32_t r = 0; r < rows_pad; ++r) {
+      const uint32_t* h = &hist[size_t(r) * 256];
+      for (uint32_t e = 0; e < 256; ++e) {
+        if (!h[e]) continue;
+        const int n = int(e) - int(base[r]);
+        cnt[(n >= 0 && n <= 14) ? n : 15] += h[e];
+      }
+    }
+    double total = 0;
+    for (double c : cnt) total += c;
+    double cost[16];
+    for (int n = 0; n < 16; ++n) cost[n] = -std::log2((cnt[n] + 0.5) / (total + 8.0));
+    cost[15] += 8.0;
+    for (uint32_t r = 0; r < rows_pad; ++r) {
+      const uint32_t* h = &hist[size_t(r) * 256];
+      double best = 0;
+      int best_base = -1;
+      for (int cand = std::max(0, int(base[r]) - 3); cand <= std::min(241, int(base[r]) + 3); ++cand) {
+        double bits = 0;
+        for (uint32_t e = 0; e < 256; ++e) {
+          if (!h[e]) continue;
+          const int n = int(e) - cand;
+          bits += h[e] * cost[(n >= 0 && n <= 14) ? n : 15];
+        }
+        if (best_base < 0 || bits < best) { best = bits; best_base = cand; }
+      }
+      base[r] = uint8_t(best_base);
+    }
+  }
+  return base;
+}
+
+inline uint32_t nibble_of(uint32_t e, uint32_t base) {
+  const uint32_t n = e - base;  // wraps for e < base
+  return n <= 14 ? n : uint32_t(BXR_ESCAPE);
+}
+
+// Pair counts -> frequencies with sum 4096, at least 1 for every pair that occurs.
+void quantise_pairs(const std::vector<uint64_t>& counts, uint32_t* freq) {
+  uint64_t total = 0;
+  for (uint64_t c : counts) total += c;
+  std::vector<uint32_t> seen;
+  std::vector<uint64_t> rem(256, 0);
+  int64_t sum = 0;
+  for (uint32_t s = 0; s < 256; ++s) {
+    freq[s] = 0;
+    if (!counts[s]) continue;
+    const uint64_t scaled = counts[s] * uint64_t(BXR_PROB_TOTAL);
+    freq[s] = std::max<uint32_t>(1u, uint32_t(scaled / total));
+    rem[s] = scaled % total;
+    sum += freq[s];
+    seen.push_back(s);
+  }
+  if (seen.empty()) { freq[0] = BXR_PROB_TOTAL; return; }
+  if (sum < BXR_PROB_TOTAL) {
+    std::sort(seen.begin(), seen.end(), [&](uint32_t a, uint32_t b) { return rem[a] != rem[b] ? rem[a] > rem[b] : a < b; });
+    uint32_t lack = uint32_t(BXR_PROB_TOTAL - sum);
+    for (size_t j = 0; lack; j = (j + 1) % seen.size(), --lack) ++freq[seen[j]];
+  } else if (sum > BXR_PROB_TOTAL) {
+    // take from the largest frequencies first: they lose the least precision
+    std::sort(seen.begin(), seen.end(), [&](uint32_t a, uint32_t b) { return freq[a] != freq[b] ? freq[a] > freq[b] : a < b; });
+    uint32_t extra = uint32_t(sum - BXR_PROB_TOTAL);
+    for (size_t j = 0; extra; j = (j + 1) % seen.size())
+      if (freq[seen[j]] > 1) { --freq[seen[j]]; --extra; }
+  }
+}
+
+struct StreamCoder {
+  uint32_t x = BXR_STATE_LOW;
+  std::vector<uint16_t>* out;
+  void renorm(uint64_t ceiling) {
+    if (x >= ceiling) { out->push_back(uint16_t(x)); x >>= 16; }
+  }
+  void put_symbol(uint32_t f, uint32_t cum) {
+    renorm(uint64_t(f) << 20);
+    x = ((x / f) << BXR_PROB_BITS) + (x % f) + cum;
+  }
+  void put_byte(uint32_t v) {
+    renorm(uint64_t(1) << 24);
+    x = (x << 8) | v;
+  }
+};
+
+struct ItemCode {
+  std::vector<uint16_t> words[BXR_STREAMS];         // decode order, all chunks of the item
+  std::vector<uint8_t> per_chunk[BXR_STREAMS];      // words consumed in each chunk
+  uint32_t state[BXR_STREAMS];
+};
+
+void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, const uint32_t* freq, const uint32_t* cum,
+                 ItemCode& code) {
+  const uint32_t nch = it.chunk_end - it.chunk_begin;
+  std::vector<uint16_t> rev;
+  for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
+    const uint32_t q = sid / BXR_ROWS, r = sid % BXR_ROWS;
+    const uint32_t row = it.row_block * BXR_ROWS + r;
+    const uint32_t b = base[row];
+    rev.clear();
+    StreamCoder coder;
+    coder.out = &rev;
+    auto& counts = code.per_chunk[sid];
+    counts.assign(nch, 0);
+    for (uint32_t c = it.chunk_end; c-- > it.chunk_begin;) {
+      const size_t before = rev.size();
+      for (int t = BXR_STEPS - 1; t >= 0; --t) {
+        const uint32_t col = c * BXR_COLS + q * BXR_PHASE_COLS + 2 * uint32_t(t);
+        const uint32_t e0 = exponent_of(src.padded(row, col, base)), e1 = exponent_of(src.padded(row, col + 1, base));
+        const uint32_t n0 = nibble_of(e0, b), n1 = nibble_of(e1, b);
+        if (n1 == BXR_ESCAPE) coder.put_byte(e1);
+        if (n0 == BXR_ESCAPE) coder.put_byte(e0);
+        const uint32_t sym = n0 | n1 << 4;
+        coder.put_symbol(freq[sym], cum[sym]);
+      }
+      const size_t used = rev.size() - before;
+      // At most 3 words per step (one symbol, two escape bytes), so 48 per chunk; 255 flags an overflow.
+      counts[c - it.chunk_begin] = used > 120 ? uint8_t(255) : uint8_t(used);
+    }
+    code.state[sid] = coder.x;
+    code.words[sid].assign(rev.rbegin(), rev.rend());
+  }
+}
+
+uint64_t align16(uint64_t v) { return (v + 15) & ~uint64_t(15); }
+
+}  // namespace
+
+extern "C" {
+
+void bxr_free(void* p) { std::free(p); }
+
+// Builds the image.  workers = CTAs the kernels will run (one per SM); threads = host threads.
+// force_raw != 0 skips entropy coding (also chosen automatically when a chunk would not fit its slot).
+// Returns 0, 1 bad arguments, 2 out of memory, 3 other failure.  The image is malloc'ed; free with bxr_free.
+int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t workers, uint32_t threads,
+              uint32_t force_raw, const uint8_t* source_sha256, uint8_t** image, uint64_t* image_bytes) {
+  try {
+    if (!words || !rows || !cols || !workers || workers > 4096 || !image || !image_bytes) return 1;
+    if (!threads) threads = std::max(1u, std::thread::hardware_concurrency());
+    const Source src{words, rows, cols};
+    Plan plan = make_plan(rows, cols, workers);
+    const uint32_t rows_pad = plan.row_blocks * BXR_ROWS, cols_pad = plan.chunks * BXR_COLS;
+    const uint32_t nblobs = plan.row_blocks * plan.chunks;
+    const uint32_t nitems = uint32_t(plan.items.size());
+
+    std::vector<uint8_t> base(rows_pad, 0);
+    std::vector<uint64_t> lut(BXR_PROB_TOTAL, 0);
+    std::vector<std::vector<uint8_t>> blobs(nblobs);
+    std::vector<uint32_t> states(size_t(nitems) * BXR_STREAMS, BXR_STATE_LOW);
+    bool raw_mode = force_raw != 0;
+
+    if (!raw_mode) {
+      base = choose_bases(src, rows_pad, threads);
+      // pair statistics
+      std::vector<std::vector<uint64_t>> local(threads, std::vector<uint64_t>(256, 0));
+      {
+        std::atomic<uint32_t> next{0};
+        std::vector<std::thread> pool;
+        for (uint32_t t = 0; t < threads; ++t)
+          pool.emplace_back([&, t] {
+            auto& cnt = local[t];
+            for (uint32_t r = next.fetch_add(1); r < rows_pad; r = next.fetch_add(1))
+              for (uint32_t c = 0; c < cols_pad; c += 2)
+                ++cnt[nibble_of(exponent_of(src.padded(r, c, base.data())), base[r]) |
+                      nibble_of(exponent_of(src.padded(r, c + 1, base.data())), base[r]) << 4];
+          });
+        for (auto& th : pool) th.join();
+      }
+      std::vector<uint64_t> counts(256, 0);
+      for (auto& l : local)
+        for (int s = 0; s < 256; ++s) counts[s] += l[s];
+      uint32_t freq[256], cum[257];
+      quantise_pairs(counts, freq);
+      cum[0] = 0;
+      for (int s = 0; s < 256; ++s) cum[s + 1] = cum[s] + freq[s];
+      for (uint32_t s = 0; s < 256; ++s)
+        for (uint32_t slot = cum[s]; slot < cum[s + 1]; ++slot) {
+          const uint32_t n0 = s & 15, n1 = s >> 4;
+          const uint32_t lo = freq[s] | (n0 == BXR_ESCAPE ? BXR_LUT_ESC0 : 0) | (n1 == BXR_ESCAPE ? BXR_LUT_ESC1 : 0) |
+                              (slot - cum[s]) << 16;
+          const uint32_t hi = (n0 == BXR_ESCAPE ? 0 : n0) << 7 | (n1 == BXR_ESCAPE ? 0 : n1) << 23;
+          lut[slot] = uint64_t(lo) | uint64_t(hi) << 32;
+        }
+
+      std::atomic<bool> overflow{false};
+      parallel_for(nitems, threads, [&](uint32_t i) {
+        if (overflow.load()) return;
+        const bxr_item& it = plan.items[i];
+        auto code = std::make_unique<ItemCode>();
+        encode_item(src, it, base.data(), freq, cum, *code);
+        std::copy(code->state, code->state + BXR_STREAMS, &states[size_t(i) * BXR_STREAMS]);
+        std::vector<uint32_t> cursor(BXR_STREAMS, 0);
+        for (uint32_t c = it.chunk_begin; c < it.chunk_end; ++c) {
+          const uint32_t k = c - it.chunk_begin;
+          uint32_t total = 0;
+          bool bad = false;
+          for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
+            if (code->per_chunk[sid][k] == 255) bad = true;
+            total += code->per_chunk[sid][k];
+          }
+          if (bad || total > BXR_WORDS_MAX) { overflow.store(true); return; }
+          std::vector<uint8_t>& blob = blobs[size_t(it.row_block) * plan.chunks + c];
+          blob.assign(size_t(align16(BXR_WORDS_AT + 2ull * total)), 0);
+          uint8_t* raw = blob.data() + BXR_COUNT_BYTES;
+          for (uint32_t q = 0; q < BXR_PHASES; ++q)
+            for (uint32_t j = 0; j < 2; ++j)
+              for (uint32_t r = 0; r < BXR_ROWS; ++r) {
+                uint8_t* piece = raw + (size_t(q * 2 + j) * BXR_ROWS + r) * 16;
+                const uint32_t row = it.row_block * BXR_ROWS + r, col = c * BXR_COLS + q * BXR_PHASE_COLS + j * 16;
+                for (uint32_t e = 0; e < 16; ++e) piece[e] = raw_byte_of(src.padded(row, col + e, base.data()));
+              }
+          uint16_t* w = reinterpret_cast<uint16_t*>(blob.data() + BXR_WORDS_AT);
+          uint32_t at = 0;
+          for (uint32_t g = 0; g < BXR_SEGMENTS; ++g) {
+            const uint32_t h = g / BXR_ROWS, r = g % BXR_ROWS;
+            const uint32_t fwd = (2 * h) * BXR_ROWS + r, bwd = (2 * h + 1) * BXR_ROWS + r;
+            const uint32_t nf = code->per_chunk[fwd][k], nb = code->per_chunk[bwd][k];
+            blob[g] = uint8_t(nf + nb);
+            for (uint32_t e = 0; e < nf; ++e) w[at + e] = code->words[fwd][cursor[fwd] + e];
+            for (uint32_t e = 0; e < nb; ++e) w[at + nf + nb - 1 - e] = code->words[bwd][cursor[bwd] + e];
+            cursor[fwd] += nf;
+            cursor[bwd] += nb;
+            at += nf + nb;
+          }
+        }
+      });
+      if (overflow.load()) raw_mode = true;
+    }
+
+    if (raw_mode) {
+      std::fill(base.begin(), base.end(), 0);
+      std::fill(states.begin(), states.end(), BXR_STATE_LOW);
+      parallel_for(nblobs, threads, [&](uint32_t bi) {
+        const uint32_t rb = bi / plan.chunks, c = bi % plan.chunks;
+        std::vector<uint8_t>& blob = blobs[bi];
+        blob.assign(BXR_RAW_TILE_BYTES, 0);
+        for (uint32_t a = 0; a < 2; ++a)
+          for (uint32_t r = 0; r < BXR_ROWS; ++r)
+            for (uint32_t j = 0; j < 8; ++j) {
+              uint16_t* dst = reinterpret_cast<uint16_t*>(blob.data() + a * 16384 + r * 128 + ((j ^ (r & 7)) * 16));
+              for (uint32_t e = 0; e < 8; ++e) dst[e] = src.padded(rb * BXR_ROWS + r, c * BXR_COLS + a * 64 + j * 8 + e, base.data());
+            }
+      });
+    }
+
+    bxr_header h{};
+    h.magic = BXR_MAGIC;
+    h.mode = raw_mode ? BXR_MODE_RAW : BXR_MODE_CODED;
+    h.rows = rows;
+    h.cols = cols;
+    h.row_blocks = plan.row_blocks;
+    h.chunks = plan.chunks;
+    h.workers = workers;
+    h.items = nitems;
+    h.partial_slots = plan.partial_slots;
+    uint64_t at = align16(sizeof(bxr_header));
+    at = (at + 255) & ~uint64_t(255);
+    h.lut_at = at;            at += raw_mode ? 0 : sizeof(uint64_t) * BXR_PROB_TOTAL;
+    h.base_at = at;           at = align16(at + rows_pad);
+    h.items_at = at;          at = align16(at + sizeof(bxr_item) * nitems);
+    h.worker_items_at = at;   at = align16(at + 4ull * (workers + 1));
+    h.states_at = at;         at = align16(at + (raw_mode ? 0 : 4ull * states.size()));
+    h.blob_index_at = at;     at = align16(at + 4ull * (nblobs + 1));
+    at = (at + 255) & ~uint64_t(255);
+    h.blobs_at = at;
+    std::vector<uint32_t> index(nblobs + 1);
+    uint64_t run = 0;
+    for (uint32_t b = 0; b < nblobs; ++b) { index[b] = uint32_t(run >> 4); run += blobs[b].size(); }
+    if ((run >> 4) > 0xFFFFFFFFull) return 3;
+    index[nblobs] = uint32_t(run >> 4);
+    h.total_bytes = at + run;
+    h.coded_bytes = run + (raw_mode ? 0 : 4ull * states.size()) + 4ull * (nblobs + 1);
+    if (source_sha256) std::memcpy(h.source_sha256, source_sha256, 32);
+
+    auto* img = static_cast<uint8_t*>(std::calloc(size_t(h.total_bytes), 1));
+    if (!img) return 2;
+    std::memcpy(img, &h, sizeof h);
+    if (!raw_mode) std::memcpy(img + h.lut_at, lut.data(), sizeof(uint64_t) * BXR_PROB_TOTAL);
+    std::memcpy(img + h.base_at, base.data(), rows_pad);
+    std::memcpy(img + h.items_at, plan.items.data(), sizeof(bxr_item) * nitems);
+    std::memcpy(img + h.worker_items_at, plan.worker_items.data(), 4ull * (workers + 1));
+    if (!raw_mode) std::memcpy(img + h.states_at, states.data(), 4ull * states.size());
+    std::memcpy(img + h.blob_index_at, index.data(), 4ull * (nblobs + 1));
+    parallel_for(nblobs, threads, [&](uint32_t b) {
+      std::memcpy(img + h.blobs_at + (uint64_t(index[b]) << 4), blobs[b].data(), blobs[b].size());
+    });
+    *image = img;
+    *image_bytes = h.total_bytes;
+    return 0;
+  } catch (const std::bad_alloc&) {
+    return 2;
+  } catch (...) {
+    return 3;
+  }
+}
+
+// Host twin of the GPU decoder.  Writes rows*cols words.  Returns 0, 1 bad arguments / malformed header,
+// 2 a stream that reads outside its segment or does not end in the canonical state.
+int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
+  try {
+    if (!img || !out || bytes < sizeof(bxr_header)) return 1;
+    bxr_header h;
+    std::memcpy(&h, img, sizeof h);
+    if (h.magic != BXR_MAGIC || h.total_bytes != bytes || !h.rows || !h.cols || h.mode > 1) return 1;
+    const auto* items = reinterpret_cast<const bxr_item*>(img + h.items_at);
+    const auto* index = reinterpret_cast<const uint32_t*>(img + h.blob_index_at);
+    auto put = [&](uint32_t row, uint32_t col, uint16_t w) {
+      if (row < h.rows && col < h.cols) out[size_t(row) * h.cols + col] = w;
+    };
+    if (h.mode == BXR_MODE_RAW) {
+      for (uint32_t rb = 0; rb < h.row_blocks; ++rb)
+        for (uint32_t c = 0; c < h.chunks; ++c) {
+          const uint8_t* blob = img + h.blobs_at + (uint64_t(index[size_t(rb) * h.chunks + c]) << 4);
+          for (uint32_t a = 0; a < 2; ++a)
+            for (uint32_t r = 0; r < BXR_ROWS; ++r)
+              for (uint32_t j = 0; j < 8; ++j) {
+                const auto* srcp = reinterpret_cast<const uint16_t*>(blob + a * 16384 + r * 128 + ((j ^ (r & 7)) * 16));
+                for (uint32_t e = 0; e < 8; ++e) put(rb * BXR_ROWS + r, c * BXR_COLS + a * 64 + j * 8 + e, srcp[e]);
+              }
+        }
+      return 0;
+    }
+    const auto* lut = reinterpret_cast<const uint64_t*>(img + h.lut_at);
+    const uint8_t* base = img + h.base_at;
+    const auto* states = reinterpret_cast<const uint32_t*>(img + h.states_at);
+    int status = 0;
+    for (uint32_t i = 0; i < h.items; ++i) {
+      const bxr_item& it = items[i];
+      std::vector<uint32_t> x(states + size_t(i) * BXR_STREAMS, states + size_t(i + 1) * BXR_STREAMS);
+      for (uint32_t c = it.chunk_begin; c < it.chunk_end; ++c) {
+        const size_t bi = size_t(it.row_block) * h.chunks + c;
+        const uint8_t* blob = img + h.blobs_at + (uint64_t(index[bi]) << 4);
+        const uint64_t blob_bytes = uint64_t(index[bi + 1] - index[bi]) << 4;
+        const auto* words = reinterpret_cast<const uint16_t*>(blob + BXR_WORDS_AT);
+        const int64_t nwords = (int64_t(blob_bytes) - BXR_WORDS_AT) / 2;
+        uint32_t start[BXR_SEGMENTS + 1];
+        start[0] = 0;
+        for (uint32_t g = 0; g < BXR_SEGMENTS; ++g) start[g + 1] = start[g] + blob[g];
+        if (int64_t(start[BXR_SEGMENTS]) > nwords) return 2;
+        for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
+          const uint32_t q = sid / BXR_ROWS, r = sid % BXR_ROWS, g = (q / 2) * BXR_ROWS + r;
+          const bool backward = q & 1;
+          int64_t cur = backward ? int64_t(start[g + 1]) - 1 : int64_t(start[g]);
+          const int step = backward ? -1 : 1;
+          uint32_t s = x[sid];
+          auto refill = [&] {
+            if (s < BXR_STATE_LOW) {
+              if (cur < int64_t(start[g]) || cur >= int64_t(start[g + 1])) { status = 2; return; }
+              s = (s << 16) | words[cur];
+              cur += step;
+            }
+          };
+          const uint32_t row = it.row_block * BXR_ROWS + r, b = base[row];
+          for (uint32_t j = 0; j < 2; ++j) {
+            const uint8_t* piece = blob + BXR_COUNT_BYTES + (size_t(q * 2 + j) * BXR_ROWS + r) * 16;
+            for (uint32_t t = 0; t < 8; ++t) {
+              const uint64_t rec = lut[s & (BXR_PROB_TOTAL - 1)];
+              const uint32_t lo = uint32_t(rec), hi = uint32_t(rec >> 32);
+              s = (lo & BXR_LUT_FREQ_MASK) * (s >> BXR_PROB_BITS) + (lo >> 16);
+              refill();
+              uint32_t e0 = ((hi >> 7) & 0xFF) + b, e1 = ((hi >> 23) & 0xFF) + b;
+              if (lo & BXR_LUT_ESC0) { e0 = s & 0xFF; s >>= 8; refill(); }
+              if (lo & BXR_LUT_ESC1) { e1 = s & 0xFF; s >>= 8; refill(); }
+              const uint32_t b0 = piece[2 * t], b1 = piece[2 * t + 1];
+              const uint32_t col = c * BXR_COLS + q * BXR_PHASE_COLS + j * 16 + 2 * t;
+              put(row, col, uint16_t((b0 & 0x80) << 8 | (e0 & 0xFF) << 7 | (b0 & 0x7F)));
+              put(row, col + 1, uint16_t((b1 & 0x80) << 8 | (e1 & 0xFF) << 7 | (b1 & 0x7F)));
+            }
+          }
+          x[sid] = s;
+          if (status) return status;
+        }
+      }
+      for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid)
+        if (x[sid] != BXR_STATE_LOW) return 2;
+    }
+    return 0;
+  } catch (...) {
+    return 3;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,566 @@
+// Fused kernels over the BXR1 resident layout (bxr_format.h): one persistent CTA per worker walks its
+// share of (row block, chunk) units.  A chunk blob arrives in shared memory by one bulk copy; 16 warps
+// decode it (one rANS stream per lane, two weights per step) and the reconstructed BF16 words go
+//   * kDense : to global memory (the decode twin used by decode() and by the parity tests),
+//   * kGemv  : into FP32 FMA chains against up to 8 activation rows (CUDA cores), or
+//   * kUmma  : into a 128-byte-swizzled K-major operand tile consumed by tcgen05.mma with the FP32
+//              accumulator in TMEM (weights are the M=128 operand, the batch is N).
+// They stand where the reference runs decode_words + F.linear
+// (context-runtime/georefine_context_runtime/bitexact_context_gpu.py:130-157,
+// bitexact_context_serving.py:365-376) and its fused MIV / BI linears (glc_serve/miv_gemv.py:125-191,
+// glc_serve/bi_csrc/bi_gemm.cuh:797-916).  The reduction order of every output element depends only on
+// the image (shape, worker count), never on the batch size.
+#pragma once
+#include <cuda.h>
+
+#include "bxr_format.h"
+#include "device_utils.cuh"
+
+namespace grb {
+
+enum BxrMode { kDense = 0, kGemv = 1, kUmma = 2 };
+
+constexpr int kDecoderWarps = 16;
+constexpr int kWarpLoader = 16;    // bulk copies of chunk blobs
+constexpr int kWarpScanner = 17;   // segment offsets (and FP32 activations for the GEMV)
+constexpr int kWarpMma = 18;       // TMEM owner and MMA issuer
+constexpr int kWarpXLoader = 19;   // TMA loads of activation tiles
+constexpr int kWarpEpilogue = 20;  // 4 warps, TMEM lane quarter = warp % 4
+constexpr int kThreadsUmma = 24 * 32;
+constexpr int kThreadsSimt = 18 * 32;
+
+constexpr uint32_t kLutBytes = 8 * BXR_PROB_TOTAL;
+constexpr uint32_t kSegOffBytes = 528;  // u16[257] rounded up
+constexpr uint32_t kAtomBytes = 16384;  // 128 rows x 64 BF16
+constexpr uint32_t kInGuard = 128;      // a corrupt stream may read up to 96 bytes past its slot
+constexpr int kGemvMaxM = 8;
+
+struct BxrArgs {
+  // image
+  const uint64_t* lut;
+  const uint8_t* base;
+  const bxr_item* items;
+  const uint32_t* worker_items;
+  const uint32_t* states;
+  const uint32_t* blob_index;
+  const uint8_t* blobs;
+  uint32_t rows, cols, row_blocks, chunks, workers;
+  // call
+  uint32_t m;                  // activation rows in this launch (<= NB, <= 8 for the GEMV)
+  const __nv_bfloat16* x;      // GEMV only (the UMMA path reads x through the tensor map)
+  long long ldx;
+  __nv_bfloat16* y;
+  long long ldy;
+  const __nv_bfloat16* bias;   // optional, one per weight row
+  float* partials;             // FP32 [partial_slots][NB][128]
+  uint32_t* counters;          // [row_blocks], zero between calls
+  uint16_t* dense;             // kDense: rows x cols words
+  uint32_t* status;
+};
+
+template <int MODE, int NB>
+struct BxrSmem {
+  static constexpr int kIn = (MODE == kUmma && NB >= 128) ? 3 : 4;
+  static constexpr int kOp = (MODE == kUmma) ? ((NB >= 64) ? 3 : 4) : 0;
+  static constexpr uint32_t kOpStage = kAtomBytes + NB * 128;
+  static constexpr uint32_t kXStage = (MODE == kGemv) ? kGemvMaxM * BXR_COLS * 4 : 0;  // FP32 activations per chunk
+  static constexpr uint32_t lut = 0;
+  static constexpr uint32_t op = lut + kLutBytes;
+  static constexpr uint32_t in = op + kOp * kOpStage;
+  static constexpr uint32_t segoff = in + kIn * BXR_BLOB_MAX + kInGuard;
+  static constexpr uint32_t xf32 = segoff + kIn * kSegOffBytes;
+  static constexpr uint32_t bars = (xf32 + kIn * kXStage + 15) & ~15u;
+  // barrier order: in_full, in_ready, in_empty [kIn each]; op_full, op_empty [kOp each]; acc_full, acc_empty [2 each]
+  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4;
+  static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, reduce flag, spare
+  static constexpr uint32_t red = misc + 16;          // GEMV: FP32 [4 phases][128 rows][8]
+  static constexpr uint32_t total = red + (MODE == kGemv ? 4 * 128 * kGemvMaxM * 4 : 0);
+  static constexpr uint32_t alloc = total + 1024;     // slack to align the base to 1024
+  static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
+};
+
+struct RoleCtx {
+  uint32_t smem;       // aligned base (shared address)
+  uint32_t bars;
+  uint32_t abort_addr; // shared address of the abort flag
+  uint32_t* status;
+  __device__ __forceinline__ bool aborted() const {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(abort_addr));
+    return v != 0;
+  }
+  __device__ __forceinline__ void abort(uint32_t bits) const {
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_addr), "r"(1u) : "memory");
+    atomicOr(status, bits);
+  }
+  // Bounded wait; on expiry marks the CTA aborted.
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) const {
+    if (mbar_wait(bar, parity)) return true;
+    abort(kStatusTimeout);
+    return false;
+  }
+};
+
+// One rANS step of a lane: returns the exponent bits of two weights, positioned for a packed BF16 pair
+// (bits 7..14 and 23..30) and relative to the row base unless an escape replaced them.
+struct LaneDecoder {
+  uint32_t x;      // rANS state
+  uint32_t wp;     // shared address of the next 16-bit word of this stream
+  int wstep;       // +2 forward, -2 backward
+  uint32_t lut;    // shared address of the slot records
+  uint32_t base2;  // row base replicated into both exponent fields
+
+  __device__ __forceinline__ void refill() {
+    if (x < BXR_STATE_LOW) {
+      x = (x << 16) | lds_u16(wp);
+      wp += wstep;
+    }
+  }
+  __device__ __forceinline__ uint32_t step() {
+    const uint2 rec = lds64(lut + ((x & (BXR_PROB_TOTAL - 1)) << 3));
+    x = (rec.x & BXR_LUT_FREQ_MASK) * (x >> BXR_PROB_BITS) + (rec.x >> 16);
+    refill();
+    uint32_t e = rec.y;
+    if (rec.x & (BXR_LUT_ESC0 | BXR_LUT_ESC1)) {  // rare: an exponent outside the row window
+      const uint32_t b = (base2 >> 7) & 0xFFu;
+      uint32_t e0 = ((e >> 7) & 0xFFu) + b, e1 = ((e >> 23) & 0xFFu) + b;
+      if (rec.x & BXR_LUT_ESC0) { e0 = x & 0xFFu; x >>= 8; refill(); }
+      if (rec.x & BXR_LUT_ESC1) { e1 = x & 0xFFu; x >>= 8; refill(); }
+      e = ((e0 << 7) | (e1 << 23)) - base2;
+    }
+    return e + base2;
+  }
+};
+
+// Two raw bytes (sign << 7 | mantissa) and two exponents -> two BF16 words in one register.
+__device__ __forceinline__ uint32_t join_pair(uint32_t raw4, uint32_t selector, uint32_t expo) {
+  return (__byte_perm(raw4, 0, selector) & 0x807F807Fu) | expo;
+}
+
+// Decodes 8 consecutive weights of the lane's row from two raw registers (8 bytes).
+__device__ __forceinline__ uint4 decode8(LaneDecoder& d, uint32_t raw_lo, uint32_t raw_hi) {
+  uint4 w;
+  w.x = join_pair(raw_lo, 0x1100, d.step());
+  w.y = join_pair(raw_lo, 0x3322, d.step());
+  w.z = join_pair(raw_hi, 0x1100, d.step());
+  w.w = join_pair(raw_hi, 0x3322, d.step());
+  return w;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
+
+template <int MODE, int NB>
+__global__ void __launch_bounds__(MODE == kUmma ? kThreadsUmma : kThreadsSimt, 1)
+bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
+  using L = BxrSmem<MODE, NB>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t worker = blockIdx.x;
+
+  RoleCtx ctx;
+  ctx.smem = smem;
+  ctx.bars = smem + L::bars;
+  ctx.abort_addr = smem + L::misc + 4;
+  ctx.status = args.status;
+  const uint32_t bar_in_full = ctx.bars, bar_in_ready = bar_in_full + 8 * L::kIn, bar_in_empty = bar_in_ready + 8 * L::kIn;
+  const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
+  const uint32_t bar_acc_full = bar_op_empty + 8 * L::kOp, bar_acc_empty = bar_acc_full + 16;
+  constexpr uint32_t kTmemCols = (2 * NB < 32) ? 32 : 2 * NB;
+  constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;  // ring length of the operand stages (unused outside kUmma)
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < L::kIn; ++i) {
+      mbar_init(bar_in_full + 8 * i, 1);
+      mbar_init(bar_in_ready + 8 * i, 1);
+      mbar_init(bar_in_empty + 8 * i, kDecoderWarps);
+    }
+    for (int i = 0; i < L::kOp; ++i) {
+      mbar_init(bar_op_full + 8 * i, kDecoderWarps / 2 + 1);
+      mbar_init(bar_op_empty + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      // GEMV: pair 0 guards the cross-phase reduction buffer (filled by 16 warps, drained by 4)
+      mbar_init(bar_acc_full + 8 * i, MODE == kGemv ? kDecoderWarps : 1);
+      mbar_init(bar_acc_empty + 8 * i, 4);
+    }
+    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc), "r"(0u) : "memory");
+    mbar_fence_init();
+  }
+  if (MODE == kUmma && warp == kWarpMma) {
+    tmem_alloc(smem + L::misc, kTmemCols);
+    tmem_relinquish();
+  }
+  // the slot-record table: 32 KB, copied cooperatively (L2 hits after the first CTA)
+  for (uint32_t i = threadIdx.x; i < kLutBytes / 16; i += blockDim.x)
+    sts128(smem + L::lut + i * 16, __ldg(reinterpret_cast<const uint4*>(args.lut) + i));
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  uint32_t tmem_base = 0;
+  if (MODE == kUmma) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(smem + L::misc));
+
+  const uint32_t item_begin = args.worker_items[worker], item_end = args.worker_items[worker + 1];
+  const uint64_t units = uint64_t(args.row_blocks) * args.chunks;
+  const uint32_t unit_begin = uint32_t(units * worker / args.workers);
+  const uint32_t unit_count = uint32_t(units * (worker + 1) / args.workers) - unit_begin;
+
+  if (warp < kDecoderWarps) {
+    // ------------------------------------------------------------------ decoders: one stream per lane
+    const uint32_t q = warp >> 2, r = (warp & 3) * 32 + lane;
+    const uint32_t backward = q & 1, seg = (q >> 1) * BXR_ROWS + r, atom = q >> 1;
+    LaneDecoder d;
+    d.lut = smem + L::lut;
+    d.wstep = backward ? -2 : 2;
+    uint32_t u = 0;
+    bool live = true;
+    for (uint32_t it = item_begin; it < item_end && live; ++it) {
+      const bxr_item item = args.items[it];
+      const uint32_t row = item.row_block * BXR_ROWS + r;
+      d.x = args.states[size_t(it) * BXR_STREAMS + q * BXR_ROWS + r];
+      d.base2 = uint32_t(args.base[row]) * 0x00800080u;
+      float acc[MODE == kGemv ? kGemvMaxM : 1];
+#pragma unroll
+      for (int m = 0; m < (MODE == kGemv ? kGemvMaxM : 1); ++m) acc[m] = 0.f;
+      for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c, ++u) {
+        const uint32_t s = u % L::kIn, ph = (u / L::kIn) & 1;
+        if (ctx.aborted() || !ctx.wait(bar_in_full + 8 * s, ph) || !ctx.wait(bar_in_ready + 8 * s, ph)) { live = false; break; }
+        const uint32_t blob = smem + L::in + s * BXR_BLOB_MAX;
+        const uint32_t off = lds_u16(smem + L::segoff + s * kSegOffBytes + 2 * (seg + backward)) - backward;
+        d.wp = blob + BXR_WORDS_AT + 2 * off;
+        uint32_t a_tile = 0;
+        if (MODE == kUmma) {
+          const uint32_t hs = 2 * u + atom, so = hs % kOpN, pho = (hs / kOpN) & 1;
+          if (!ctx.wait(bar_op_empty + 8 * so, pho ^ 1)) { live = false; break; }
+          a_tile = smem + L::op + so * L::kOpStage + r * 128;
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint4 raw = lds128(blob + BXR_COUNT_BYTES + ((q * 2 + j) * BXR_ROWS + r) * 16);
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const uint4 w = decode8(d, k ? raw.z : raw.x, k ? raw.w : raw.y);
+            const uint32_t col = c * BXR_COLS + q * BXR_PHASE_COLS + j * 16 + k * 8;
+            if (MODE == kUmma) {
+              const uint32_t cidx = (q & 1) * 4 + j * 2 + k;
+              sts128(a_tile + ((cidx ^ (r & 7)) << 4), w);
+            } else if (MODE == kDense) {
+              if (row < args.rows) {
+                uint16_t* dst = args.dense + size_t(row) * args.cols + col;
+                if (col + 8 <= args.cols && (args.cols & 7) == 0) {
+                  *reinterpret_cast<uint4*>(dst) = w;
+                } else {
+                  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+                  for (int e = 0; e < 8; ++e)
+                    if (col + e < args.cols) dst[e] = uint16_t(ww[e >> 1] >> (16 * (e & 1)));
+                }
+              }
+            } else {
+              const float wf[8] = {bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y),
+                                   bf16_lo(w.z), bf16_hi(w.z), bf16_lo(w.w), bf16_hi(w.w)};
+              const uint32_t xs = smem + L::xf32 + s * L::kXStage + (q * BXR_PHASE_COLS + j * 16 + k * 8) * 4;
+#pragma unroll
+              for (int m = 0; m < kGemvMaxM; ++m) {
+                if (m < NB) {  // NB carries the batch size for the GEMV instantiations
+                  const uint4 x0 = lds128(xs + m * BXR_COLS * 4), x1 = lds128(xs + m * BXR_COLS * 4 + 16);
+                  float a = acc[m];
+                  a = __fmaf_rn(__uint_as_float(x0.x), wf[0], a);
+                  a = __fmaf_rn(__uint_as_float(x0.y), wf[1], a);
+                  a = __fmaf_rn(__uint_as_float(x0.z), wf[2], a);
+                  a = __fmaf_rn(__uint_as_float(x0.w), wf[3], a);
+                  a = __fmaf_rn(__uint_as_float(x1.x), wf[4], a);
+                  a = __fmaf_rn(__uint_as_float(x1.y), wf[5], a);
+                  a = __fmaf_rn(__uint_as_float(x1.z), wf[6], a);
+                  a = __fmaf_rn(__uint_as_float(x1.w), wf[7], a);
+                  acc[m] = a;
+                }
+              }
+            }
+          }
+        }
+        if (MODE == kUmma) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_op_full + 8 * ((2 * u + atom) % kOpN));
+        } else {
+          __syncwarp();
+        }
+        if (lane == 0) mbar_arrive(bar_in_empty + 8 * s);
+      }
+      if (!live) break;
+      if (d.x != BXR_STATE_LOW) atomicOr(args.status, kStatusCheckpoint);
+      if (MODE == kGemv) {
+        // phases of a row are added in phase order, parts of a row block in part order
+        const uint32_t red = smem + L::red;
+        const uint32_t n_item = it - item_begin;
+        if (!ctx.wait(bar_acc_empty, (n_item & 1) ^ 1)) break;  // previous item's sums have been read
+#pragma unroll
+        for (int m = 0; m < kGemvMaxM; ++m)
+          if (m < NB) asm volatile("st.shared.f32 [%0], %1;" ::"r"(red + ((q * BXR_ROWS + r) * kGemvMaxM + m) * 4), "f"(acc[m]) : "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_full);
+        bool last_part = item.parts == 1;
+        if (q == 0) {
+          if (!ctx.wait(bar_acc_full, n_item & 1)) break;
+          float tot[kGemvMaxM];
+#pragma unroll
+          for (int m = 0; m < kGemvMaxM; ++m) {
+            tot[m] = 0.f;
+            if (m < NB) {
+              float t;
+              asm volatile("ld.shared.f32 %0, [%1];" : "=f"(t) : "r"(red + ((0 * BXR_ROWS + r) * kGemvMaxM + m) * 4));
+#pragma unroll
+              for (int p = 1; p < BXR_PHASES; ++p) {
+                float v;
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(red + ((p * BXR_ROWS + r) * kGemvMaxM + m) * 4));
+                t = __fadd_rn(t, v);
+              }
+              tot[m] = t;
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty);
+          if (item.parts > 1) {
+#pragma unroll
+            for (int m = 0; m < kGemvMaxM; ++m)
+              if (m < NB) args.partials[(size_t(item.slot) * kGemvMaxM + m) * BXR_ROWS + r] = tot[m];
+            __threadfence();
+          }
+          named_barrier(3, 128);
+          if (item.parts > 1) {
+            uint32_t prev = 0;
+            if (warp == 0 && lane == 0) prev = atomicAdd(args.counters + item.row_block, 1u);
+            prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
+            // warps 1..3 learn the verdict through shared memory
+            if (warp == 0 && lane == 0) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(prev) : "memory");
+            named_barrier(3, 128);
+            asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
+            last_part = prev == item.parts - 1;
+            if (last_part) {
+              __threadfence();
+              const uint32_t first = item.slot - item.part;
+#pragma unroll
+              for (int m = 0; m < kGemvMaxM; ++m)
+                if (m < NB) {
+                  float t = __ldcg(args.partials + (size_t(first) * kGemvMaxM + m) * BXR_ROWS + r);
+                  for (uint32_t p = 1; p < item.parts; ++p)
+                    t = __fadd_rn(t, __ldcg(args.partials + (size_t(first + p) * kGemvMaxM + m) * BXR_ROWS + r));
+                  tot[m] = t;
+                }
+              if (warp == 0 && lane == 0) args.counters[item.row_block] = 0;
+            }
+          }
+          if (last_part && row < args.rows) {
+            const float b = args.bias ? __bfloat162float(args.bias[row]) : 0.f;
+#pragma unroll
+            for (int m = 0; m < kGemvMaxM; ++m)
+              if (m < NB && m < int(args.m))
+                args.y[size_t(m) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(tot[m], b) : tot[m]);
+          }
+        }
+      }
+    }
+  } else if (warp == kWarpLoader) {
+    // ------------------------------------------------------------------ chunk blobs, one bulk copy each
+    uint32_t issued = 0;
+    for (uint32_t u0 = 0; u0 < unit_count; u0 += 32) {
+      const uint32_t mine = unit_begin + min(u0 + lane, unit_count - 1);
+      const uint32_t i0 = __ldg(args.blob_index + mine), i1 = __ldg(args.blob_index + mine + 1);
+      const uint32_t n = min(32u, unit_count - u0);
+      bool live = true;
+      for (uint32_t i = 0; i < n && live; ++i) {
+        const uint32_t u = u0 + i, s = u % L::kIn, ph = (u / L::kIn) & 1;
+        const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, i0, i), b1 = __shfl_sync(0xFFFFFFFFu, i1, i);
+        uint32_t bytes = (b1 - b0) << 4;
+        if (ctx.aborted() || !ctx.wait(bar_in_empty + 8 * s, ph ^ 1)) { live = false; break; }
+        if (b1 < b0 || bytes > BXR_BLOB_MAX || bytes < BXR_WORDS_AT) {
+          ctx.abort(kStatusBadArgument);
+          live = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar_in_full + 8 * s, bytes);
+          bulk_g2s(smem + L::in + s * BXR_BLOB_MAX, args.blobs + (size_t(b0) << 4), bytes, bar_in_full + 8 * s);
+        }
+        issued = u + 1;
+      }
+      if (!live) break;
+    }
+    // after an abort: give copies still in flight a bounded time to land before the CTA exits
+    if (ctx.aborted() && lane == 0)
+      for (uint32_t u = (issued > uint32_t(L::kIn) ? issued - L::kIn : 0); u < issued; ++u) mbar_wait(bar_in_full + 8 * (u % L::kIn), (u / L::kIn) & 1);
+  } else if (warp == kWarpScanner) {
+    // ------------------------------------------------------------------ segment offsets per chunk
+    uint32_t u = 0;
+    bool live = true;
+    for (uint32_t it = item_begin; it < item_end && live; ++it) {
+      const bxr_item item = args.items[it];
+      for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c, ++u) {
+        const uint32_t s = u % L::kIn, ph = (u / L::kIn) & 1;
+        if (ctx.aborted() || !ctx.wait(bar_in_full + 8 * s, ph)) { live = false; break; }
+        const uint32_t blob = smem + L::in + s * BXR_BLOB_MAX;
+        const uint2 cnt = lds64(blob + 8 * lane);
+        uint32_t pre[8];
+        uint32_t run = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          pre[e] = run;
+          run += ((e < 4 ? cnt.x : cnt.y) >> (8 * (e & 3))) & 0xFFu;
+        }
+        uint32_t incl = run;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+          if (lane >= o) incl += v;
+        }
+        const uint32_t excl = incl - run;
+        const uint32_t total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        if (total > BXR_WORDS_MAX) {  // cannot come from the builder; refuse rather than read elsewhere
+          ctx.abort(kStatusBadArgument);
+          live = false;
+          break;
+        }
+        uint4 o4;
+        o4.x = (excl + pre[0]) | (excl + pre[1]) << 16;
+        o4.y = (excl + pre[2]) | (excl + pre[3]) << 16;
+        o4.z = (excl + pre[4]) | (excl + pre[5]) << 16;
+        o4.w = (excl + pre[6]) | (excl + pre[7]) << 16;
+        sts128(smem + L::segoff + s * kSegOffBytes + 16 * lane, o4);
+        if (lane == 31) asm volatile("st.shared.u16 [%0], %1;" ::"r"(smem + L::segoff + s * kSegOffBytes + 512), "h"(uint16_t(total)) : "memory");
+        if (MODE == kGemv) {
+          // activations of this chunk as FP32: [m][128]
+          const uint32_t xs = smem + L::xf32 + s * L::kXStage;
+          for (int m = 0; m < kGemvMaxM; ++m)
+            if (m < NB) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const uint32_t col = c * BXR_COLS + e * 32 + lane;
+                float v = 0.f;
+                if (m < int(args.m) && col < args.cols) v = __bfloat162float(args.x[size_t(m) * args.ldx + col]);
+                asm volatile("st.shared.f32 [%0], %1;" ::"r"(xs + (m * BXR_COLS + e * 32 + lane) * 4), "f"(v) : "memory");
+              }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_in_ready + 8 * s);
+      }
+    }
+  } else if (MODE == kUmma && warp == kWarpXLoader) {
+    // ------------------------------------------------------------------ activation half-tiles by TMA
+    if (lane == 0) {
+      uint32_t u = 0;
+      bool live = true;
+      for (uint32_t it = item_begin; it < item_end && live; ++it) {
+        const bxr_item item = args.items[it];
+        for (uint32_t c = item.chunk_begin; c < item.chunk_end && live; ++c, ++u)
+          for (uint32_t a = 0; a < 2; ++a) {
+            const uint32_t hs = 2 * u + a, so = hs % kOpN, pho = (hs / kOpN) & 1;
+            if (ctx.aborted() || !ctx.wait(bar_op_empty + 8 * so, pho ^ 1)) { live = false; break; }
+            mbar_arrive_expect_tx(bar_op_full + 8 * so, NB * 128);
+            tma_load_2d(smem + L::op + so * L::kOpStage + kAtomBytes, &tmap_x, int(c * BXR_COLS + a * 64), 0, bar_op_full + 8 * so);
+          }
+      }
+    }
+  } else if (MODE == kUmma && warp == kWarpMma) {
+    // ------------------------------------------------------------------ MMA issue
+    constexpr uint32_t idesc = umma_idesc_bf16(NB);
+    uint32_t u = 0, n_item = 0;
+    bool live = true;
+    for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
+      const bxr_item item = args.items[it];
+      const uint32_t buf = n_item & 1;
+      if (ctx.aborted() || !ctx.wait(bar_acc_empty + 8 * buf, ((n_item >> 1) & 1) ^ 1)) { live = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * NB;
+      uint32_t first = 1;
+      for (uint32_t c = item.chunk_begin; c < item.chunk_end && live; ++c, ++u)
+        for (uint32_t a = 0; a < 2; ++a) {
+          const uint32_t hs = 2 * u + a, so = hs % kOpN, pho = (hs / kOpN) & 1;
+          if (ctx.aborted() || !ctx.wait(bar_op_full + 8 * so, pho)) { live = false; break; }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t stage = smem + L::op + so * L::kOpStage;
+            const uint64_t adesc = umma_desc_sw128(stage), bdesc = umma_desc_sw128(stage + kAtomBytes);
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+              umma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, first ? 0u : 1u);
+              first = 0;
+            }
+            umma_commit(bar_op_empty + 8 * so);
+          }
+          __syncwarp();
+        }
+      if (live && lane == 0) umma_commit(bar_acc_full + 8 * buf);
+      __syncwarp();
+    }
+  } else if (MODE == kUmma && warp >= kWarpEpilogue) {
+    // ------------------------------------------------------------------ TMEM -> y, or -> FP32 partial tile
+    const uint32_t e = warp - kWarpEpilogue;  // == warp % 4: the TMEM lane quarter this warp may read
+    const uint32_t r = e * 32 + lane;
+    const uint32_t mcols = (args.m + 7) & ~7u;
+    uint32_t n_item = 0;
+    bool live = true;
+    for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
+      const bxr_item item = args.items[it];
+      const uint32_t buf = n_item & 1;
+      if (ctx.aborted() || !ctx.wait(bar_acc_full + 8 * buf, (n_item >> 1) & 1)) { live = false; break; }
+      tc_fence_after();
+      const uint32_t row = item.row_block * BXR_ROWS + r;
+      const uint32_t taddr = tmem_base + ((e * 32) << 16) + buf * NB;
+      const float b = (args.bias && row < args.rows) ? __bfloat162float(args.bias[row]) : 0.f;
+      for (uint32_t m0 = 0; m0 < mcols; m0 += 8) {
+        uint32_t v[8];
+        tmem_ld8(taddr + m0, v);
+        tmem_ld_wait();
+        if (item.parts == 1) {
+          if (row < args.rows)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (m0 + i < args.m) {
+                const float f = __uint_as_float(v[i]);
+                args.y[size_t(m0 + i) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(f, b) : f);
+              }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) args.partials[(size_t(item.slot) * NB + m0 + i) * BXR_ROWS + r] = __uint_as_float(v[i]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+      if (item.parts > 1) {
+        __threadfence();
+        named_barrier(1, 128);
+        if (e == 0 && lane == 0) {
+          const uint32_t prev = atomicAdd(args.counters + item.row_block, 1u);
+          asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(prev) : "memory");
+        }
+        named_barrier(1, 128);
+        uint32_t prev;
+        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
+        if (prev == item.parts - 1) {  // every partial tile of this row block is in memory: add them in K order
+          __threadfence();
+          const uint32_t first = item.slot - item.part;
+          if (row < args.rows)
+            for (uint32_t m = 0; m < args.m; ++m) {
+              float t = __ldcg(args.partials + (size_t(first) * NB + m) * BXR_ROWS + r);
+              for (uint32_t p = 1; p < item.parts; ++p) t = __fadd_rn(t, __ldcg(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r));
+              args.y[size_t(m) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(t, b) : t);
+            }
+          if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
+        }
+        named_barrier(1, 128);  // the verdict word may be rewritten
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (MODE == kUmma && warp == kWarpMma) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace grb

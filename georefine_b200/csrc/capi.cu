@@ -1,0 +1,254 @@
+// extern "C" device entry points: argument validation, launch geometry, the activation tensor map.
+// No allocation and no host synchronisation happen here; errors are returned, never thrown.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "../../include/georefine_b200.h"
+#include "bctx_decode.cuh"
+#include "bxr_kernels.cuh"
+
+namespace {
+
+using namespace grb;
+
+int cuda_status(cudaError_t e) { return e == cudaSuccess ? GRB_OK : GRB_ERR_CUDA + int(e); }
+
+uint32_t batch_tile(uint32_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+
+uint64_t counter_bytes(const bxr_header* h) { return (uint64_t(h->row_blocks) * 4 + 255) & ~uint64_t(255); }
+
+bool header_ok(const bxr_header* h) {
+  return h && h->magic == BXR_MAGIC && h->rows && h->cols && h->workers && h->mode <= 1 &&
+         h->row_blocks == (h->rows + BXR_ROWS - 1) / BXR_ROWS && h->chunks == (h->cols + BXR_COLS - 1) / BXR_COLS;
+}
+
+BxrArgs view_of(const void* image, const bxr_header* h) {
+  const auto* p = static_cast<const uint8_t*>(image);
+  BxrArgs a{};
+  a.lut = reinterpret_cast<const uint64_t*>(p + h->lut_at);
+  a.base = p + h->base_at;
+  a.items = reinterpret_cast<const bxr_item*>(p + h->items_at);
+  a.worker_items = reinterpret_cast<const uint32_t*>(p + h->worker_items_at);
+  a.states = reinterpret_cast<const uint32_t*>(p + h->states_at);
+  a.blob_index = reinterpret_cast<const uint32_t*>(p + h->blob_index_at);
+  a.blobs = p + h->blobs_at;
+  a.rows = h->rows;
+  a.cols = h->cols;
+  a.row_blocks = h->row_blocks;
+  a.chunks = h->chunks;
+  a.workers = h->workers;
+  return a;
+}
+
+// Opt every instantiation into its dynamic shared memory once per process and device.
+template <int MODE, int NB>
+cudaError_t prepare() {
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(bxr_kernel<MODE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BxrSmem<MODE, NB>::alloc));
+  if (e == cudaSuccess && dev < 64) done[dev] = true;
+  return e;
+}
+
+template <int MODE, int NB>
+int launch(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
+  cudaError_t e = prepare<MODE, NB>();
+  if (e != cudaSuccess) return cuda_status(e);
+  const int threads = MODE == kUmma ? kThreadsUmma : kThreadsSimt;
+  bxr_kernel<MODE, NB><<<a.workers, threads, BxrSmem<MODE, NB>::alloc, stream>>>(a, tmap);
+  return cuda_status(cudaGetLastError());
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// x viewed as [m rows][cols] BF16 with row stride ldx; box = 64 columns x tile rows, 128-byte swizzle, zeros
+// outside the tensor (rows beyond m and columns beyond cols contribute nothing).
+int make_x_map(CUtensorMap* map, const void* x, int64_t ldx, uint32_t m, uint32_t cols, uint32_t tile) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return GRB_ERR_UNSUPPORTED;
+  const cuuint64_t dims[2] = {cols, m};
+  const cuuint64_t strides[1] = {cuuint64_t(ldx) * 2};
+  const cuuint32_t box[2] = {64, tile};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? GRB_OK : GRB_ERR_ARGUMENT;
+}
+
+template <int NB>
+int gemm_tile(BxrArgs a, const void* x, int64_t ldx, cudaStream_t stream) {
+  CUtensorMap map;
+  const int st = make_x_map(&map, x, ldx, a.m, a.cols, NB);
+  if (st) return st;
+  return launch<kUmma, NB>(a, map, stream);
+}
+
+template <int M>
+int gemv_m(const BxrArgs& a, cudaStream_t stream) {
+  CUtensorMap none{};
+  return launch<kGemv, M>(a, none, stream);
+}
+
+}  // namespace
+
+extern "C" {
+
+uint64_t grb_bxr_workspace_bytes(const bxr_header* h, uint32_t max_m) {
+  if (!header_ok(h) || !max_m) return 0;
+  const uint64_t tile = batch_tile(max_m > 128 ? 128 : max_m);
+  return counter_bytes(h) + uint64_t(h->partial_slots) * tile * BXR_ROWS * 4;
+}
+
+int grb_bctx_decode_words(const grb_bctx_tensor* t, const int64_t* block_ids, uint64_t count, uint16_t* out,
+                          uint32_t* status, void* cuda_stream) {
+  if (!t || !out || !status || !t->row_class || !t->col_class || !t->main_stream || !t->main_states || !t->main_offsets ||
+      !t->main_cum || !t->main_bucket || !t->residual_stream || !t->stride || !t->cols || !t->rows ||
+      t->n != uint64_t(t->rows) * t->cols || (t->mode != 0 && t->mode != 128))
+    return GRB_ERR_ARGUMENT;
+  if (t->mode == 128 && (!t->residual_states || !t->residual_offsets || !t->residual_cum || !t->residual_bucket))
+    return GRB_ERR_ARGUMENT;
+  if (count == 0) return GRB_OK;
+  if (count > (uint64_t(1) << 37)) return GRB_ERR_ARGUMENT;
+  BctxArgs a{};
+  a.main_s = {t->main_stream, t->main_bytes, t->main_states, t->main_offsets, t->main_cum, t->main_bucket};
+  a.resid_s = {t->residual_stream, t->residual_bytes, t->residual_states, t->residual_offsets, t->residual_cum,
+               t->residual_bucket};
+  a.row_class = t->row_class;
+  a.col_class = t->col_class;
+  a.n = t->n;
+  a.cols = t->cols;
+  a.nc = t->nc;
+  a.stride = t->stride;
+  a.raw6 = t->mode == 0;
+  a.main_contexts = t->nr * t->nc;
+  a.block_ids = reinterpret_cast<const long long*>(block_ids);
+  a.count = count;
+  a.out = out;
+  a.status = status;
+  const unsigned grid = unsigned((count + 63) / 64);
+  bctx_decode_kernel<<<grid, 64, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
+int grb_bxr_decode(const void* image, const bxr_header* h, uint16_t* out, uint32_t* status, void* cuda_stream) {
+  if (!image || !header_ok(h) || !out || !status) return GRB_ERR_ARGUMENT;
+  if (h->mode != BXR_MODE_CODED) return GRB_ERR_UNSUPPORTED;
+  BxrArgs a = view_of(image, h);
+  a.dense = out;
+  a.status = status;
+  CUtensorMap none{};
+  return launch<kDense, 8>(a, none, static_cast<cudaStream_t>(cuda_stream));
+}
+
+static int check_linear(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
+                        void* ws, uint64_t ws_bytes, uint32_t* status, uint32_t tile_m) {
+  if (!image || !header_ok(h) || !x || !y || !status || !m) return GRB_ERR_ARGUMENT;
+  if (h->mode != BXR_MODE_CODED) return GRB_ERR_UNSUPPORTED;
+  if (ldx < int64_t(h->cols) || ldy < int64_t(h->rows) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15))
+    return GRB_ERR_ARGUMENT;
+  const uint64_t need = counter_bytes(h) + uint64_t(h->partial_slots) * tile_m * BXR_ROWS * 4;
+  if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 15)) return GRB_ERR_WORKSPACE;
+  return GRB_OK;
+}
+
+int grb_bxr_gemm(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
+                 const void* bias, void* ws, uint64_t ws_bytes, uint32_t* status, void* cuda_stream) {
+  const uint32_t tile = batch_tile(m > 128 ? 128 : m);
+  int st = check_linear(image, h, x, ldx, m, y, ldy, ws, ws_bytes, status, tile);
+  if (st) return st;
+  const auto stream = static_cast<cudaStream_t>(cuda_stream);
+  BxrArgs a = view_of(image, h);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.counters = static_cast<uint32_t*>(ws);
+  a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + counter_bytes(h));
+  a.status = status;
+  a.ldx = ldx;
+  a.ldy = ldy;
+  // Batches above one tile are processed as consecutive tiles: one pass over the weights per 128 rows.
+  for (uint32_t m0 = 0; m0 < m; m0 += 128) {
+    a.m = m - m0 < 128 ? m - m0 : 128;
+    const auto* xt = static_cast<const __nv_bfloat16*>(x) + size_t(m0) * ldx;
+    a.y = static_cast<__nv_bfloat16*>(y) + size_t(m0) * ldy;
+    switch (batch_tile(a.m)) {
+      case 16: st = gemm_tile<16>(a, xt, ldx, stream); break;
+      case 32: st = gemm_tile<32>(a, xt, ldx, stream); break;
+      case 64: st = gemm_tile<64>(a, xt, ldx, stream); break;
+      default: st = gemm_tile<128>(a, xt, ldx, stream); break;
+    }
+    if (st) return st;
+  }
+  return GRB_OK;
+}
+
+int grb_bxr_gemv(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
+                 const void* bias, void* ws, uint64_t ws_bytes, uint32_t* status, void* cuda_stream) {
+  if (m > uint32_t(kGemvMaxM)) return GRB_ERR_UNSUPPORTED;
+  int st = check_linear(image, h, x, ldx, m, y, ldy, ws, ws_bytes, status, kGemvMaxM);
+  if (st) return st;
+  BxrArgs a = view_of(image, h);
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.ldx = ldx;
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.ldy = ldy;
+  a.m = m;
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.counters = static_cast<uint32_t*>(ws);
+  a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(ws) + counter_bytes(h));
+  a.status = status;
+  const auto stream = static_cast<cudaStream_t>(cuda_stream);
+  switch (m) {
+    case 1: return gemv_m<1>(a, stream);
+    case 2: return gemv_m<2>(a, stream);
+    case 3: return gemv_m<3>(a, stream);
+    case 4: return gemv_m<4>(a, stream);
+    case 5: return gemv_m<5>(a, stream);
+    case 6: return gemv_m<6>(a, stream);
+    case 7: return gemv_m<7>(a, stream);
+    default: return gemv_m<8>(a, stream);
+  }
+}
+
+int grb_kernel_attributes(int which, int out[5]) {
+  if (!out) return GRB_ERR_ARGUMENT;
+  cudaFuncAttributes fa{};
+  cudaError_t e;
+  switch (which) {
+    case 0: e = cudaFuncGetAttributes(&fa, bctx_decode_kernel); break;
+    case 1: e = cudaFuncGetAttributes(&fa, bxr_kernel<kDense, 8>); break;
+    case 2: e = cudaFuncGetAttributes(&fa, bxr_kernel<kGemv, 1>); break;
+    case 3: e = cudaFuncGetAttributes(&fa, bxr_kernel<kUmma, 16>); break;
+    case 4: e = cudaFuncGetAttributes(&fa, bxr_kernel<kUmma, 128>); break;
+    default: return GRB_ERR_ARGUMENT;
+  }
+  if (e != cudaSuccess) return cuda_status(e);
+  out[0] = fa.numRegs;
+  out[1] = int(fa.localSizeBytes);
+  out[2] = int(fa.sharedSizeBytes);
+  out[3] = fa.maxDynamicSharedSizeBytes;
+  out[4] = fa.maxThreadsPerBlock;
+  return GRB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,203 @@
+"""Indexed CUDA decoding of BCTX frames and the fused linear over their resident image.
+
+Mirrors ``context-runtime/georefine_context_runtime/bitexact_context_gpu.py``: ``checkpoints`` (:51-63),
+``index_frame`` (:66-106) and ``CudaContextTensor`` (:109-168) keep their names, arguments, attributes and
+errors.  The tensor gains ``linear(x, out=None)`` / ``__call__(x, y)``: the seam the reference reserves for "a
+backend with a fused GEMM" (bitexact_context_serving.py:3-5).  Everything that touches the GPU goes through
+the C ABI of libgeorefine_b200.so; there is no other path.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import math
+
+import numpy as np
+
+from . import _native
+from . import codec as base
+from .resident import ResidentWeight
+
+
+def _p(a, t):
+    return a.ctypes.data_as(ctypes.POINTER(t))
+
+
+def checkpoints(stream, freq, rows, columns, shape, nr, nc, stride, main=None):
+    """(states, offsets, symbols) of one stream: the decoder state and byte offset before every stride-th symbol."""
+    n = math.prod(shape)
+    data = np.frombuffer(bytes(stream), dtype=np.uint8).copy() if len(stream) else np.zeros(1, dtype=np.uint8)
+    states = np.empty((n + stride - 1) // stride, dtype=np.uint32)
+    offsets = np.empty_like(states)
+    out = np.empty(n, dtype=np.uint16)
+    freq = np.ascontiguousarray(freq, dtype="<u4")
+    rows = np.ascontiguousarray(rows, dtype=np.uint8)
+    columns = np.ascontiguousarray(columns, dtype=np.uint8)
+    context = _native.U16P() if main is None else _p(np.ascontiguousarray(main, dtype=np.uint16), ctypes.c_uint16)
+    status = _native.lib().bcx_checkpoint(_p(data, ctypes.c_uint8), len(stream), n, *shape, _p(rows, ctypes.c_uint8),
+                                          _p(columns, ctypes.c_uint8), nr, nc, int(main is not None), context,
+                                          _p(freq, ctypes.c_uint32), stride, _p(states, ctypes.c_uint32),
+                                          _p(offsets, ctypes.c_uint32), _p(out, ctypes.c_uint16))
+    if status:
+        raise base.CodecError(f"checkpoint validation failed ({status})")
+    return states, offsets, out
+
+
+def index_frame(frame: bytes, stride: int = 1024, *, keep_words: bool = False):
+    """Host index of a frame: labels, tables, streams and their restart points; the walk is bound to the
+    frame's source digest.  ``keep_words`` also returns the decoded words (key ``words``)."""
+    if not isinstance(stride, int) or not 1 <= stride <= 65536:
+        raise base.CodecError("invalid checkpoint stride")
+    if len(frame) < base.HEADER.size + 32 or hashlib.sha256(frame[:-32]).digest() != frame[-32:]:
+        raise base.CodecError("invalid frame checksum/length")
+    f = base.parse(frame)
+    r, c = f["shape"]
+    n = r * c
+    out = {"shape": (r, c), "mode": f["mode"], "nr": f["nr"], "nc": f["nc"], "stride": stride,
+           "source_sha256": f["digest"].hex(), "frame_sha256": hashlib.sha256(bytes(frame)).hexdigest(),
+           "frame_bytes": len(frame)}
+    if f["mode"] == 1:
+        out["raw"] = f["raw"]
+        if keep_words:
+            out["words"] = f["raw"].reshape(r, c)
+        return out
+    nr, nc = f["nr"], f["nc"]
+    sf = np.frombuffer(f["main_table"], dtype="<u4").copy().reshape(nr * nc, 1024)
+    states, offsets, main = checkpoints(f["main_stream"], sf, f["rows"], f["columns"], (r, c), nr, nc, stride)
+    out.update(rows=f["rows"], columns=f["columns"], main_freq=sf,
+               main_stream=np.frombuffer(f["main_stream"], dtype=np.uint8).copy(), main_states=states,
+               main_offsets=offsets, residual_stream=np.frombuffer(f["residual_stream"], dtype=np.uint8).copy())
+    if f["mode"] == 128:
+        rf = np.frombuffer(f["residual_table"], dtype="<u4").copy().reshape(1024, 64)
+        rstates, roffsets, residual = checkpoints(f["residual_stream"], rf, f["rows"], f["columns"], (r, c), nr, nc,
+                                                  stride, main)
+        out.update(residual_freq=rf, residual_states=rstates, residual_offsets=roffsets)
+    else:
+        residual = base._unpack6(_native.lib(), f["residual_stream"], n)
+    words = base.join_words(main, residual)
+    if hashlib.sha256(words.tobytes()).digest() != f["digest"]:
+        raise base.CodecError("indexed source checksum mismatch")
+    if keep_words:
+        out["words"] = words.reshape(r, c)
+    return out
+
+
+def _lookup_tables(freq):
+    nctx, vocab = freq.shape
+    cum = np.empty((nctx, vocab + 1), dtype=np.uint32)
+    bucket = np.empty((nctx, 4096), dtype=np.uint16)
+    f = np.ascontiguousarray(freq, dtype="<u4")
+    status = _native.lib().grb_bctx_build_lookup(_p(f, ctypes.c_uint32), nctx, vocab, _p(cum, ctypes.c_uint32),
+                                                 _p(bucket, ctypes.c_uint16))
+    if status:
+        raise base.CodecError(f"invalid frequency tables ({status})")
+    return cum, bucket
+
+
+class CudaContextTensor:
+    """A BCTX frame resident on one GPU: the unchanged streams with their restart index (for ``decode`` and
+    ``gather_rows``) and, for rank-2 weights, the resident image the fused linear streams.
+
+    ``resident_bytes`` counts every device allocation made here, the image and its scratch included.
+    ``fused=False`` skips the image (embedding tables that are only gathered).
+    """
+
+    def __init__(self, frame: bytes, *, stride: int = 1024, device="cuda:0", fused: bool = True, max_m: int = 128):
+        import torch
+
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA is required")
+        indexed = index_frame(frame, stride, keep_words=fused)
+        self.shape = indexed["shape"]
+        self.n = math.prod(self.shape)
+        self.stride = stride
+        self.mode, self.nr, self.nc = indexed["mode"], indexed["nr"], indexed["nc"]
+        self.source_sha256 = indexed["source_sha256"]
+        self.frame_sha256 = indexed["frame_sha256"]
+        self.frame_bytes = indexed["frame_bytes"]
+        self.device = torch.device(device)
+        self.buffers = {}
+        words = indexed.pop("words", None)
+        for name, array in indexed.items():
+            if isinstance(array, np.ndarray):
+                self.buffers[name] = torch.from_numpy(array).to(self.device)
+        for name in ("main", "residual"):
+            if name + "_freq" in indexed:
+                cum, bucket = _lookup_tables(indexed[name + "_freq"])
+                self.buffers[name + "_cum"] = torch.from_numpy(cum).to(self.device)
+                self.buffers[name + "_bucket"] = torch.from_numpy(bucket).to(self.device)
+        self.error = torch.zeros((), device=self.device, dtype=torch.int32)
+        self.resident = None
+        if fused and words is not None:
+            self.resident = ResidentWeight.from_words(words, device=self.device, source_sha256=bytes.fromhex(self.source_sha256),
+                                                      max_m=max_m)
+        self.resident_bytes = sum(t.numel() * t.element_size() for t in self.buffers.values()) + self.error.element_size()
+        if self.resident is not None:
+            self.resident_bytes += self.resident.resident_bytes
+        self._descriptor = None if self.mode == 1 else self._make_descriptor()
+
+    def _make_descriptor(self):
+        b = self.buffers
+        t = _native.BctxTensor()
+        t.n, t.rows, t.cols = self.n, self.shape[0], self.shape[1]
+        t.nr, t.nc, t.mode, t.stride = self.nr, self.nc, self.mode, self.stride
+        t.row_class, t.col_class = b["rows"].data_ptr(), b["columns"].data_ptr()
+        t.main_stream, t.main_bytes = b["main_stream"].data_ptr(), b["main_stream"].numel()
+        t.main_states, t.main_offsets = b["main_states"].data_ptr(), b["main_offsets"].data_ptr()
+        t.main_cum, t.main_bucket = b["main_cum"].data_ptr(), b["main_bucket"].data_ptr()
+        t.residual_stream, t.residual_bytes = b["residual_stream"].data_ptr(), b["residual_stream"].numel()
+        if self.mode == 128:
+            t.residual_states, t.residual_offsets = b["residual_states"].data_ptr(), b["residual_offsets"].data_ptr()
+            t.residual_cum, t.residual_bucket = b["residual_cum"].data_ptr(), b["residual_bucket"].data_ptr()
+        return t
+
+    def _decode_blocks(self, blocks=None, *, check=True):
+        import torch
+
+        if blocks is None:
+            count, ids = (self.n + self.stride - 1) // self.stride, None
+        else:
+            blocks = blocks.to(device=self.device, dtype=torch.int64).contiguous().reshape(-1)
+            count, ids = blocks.numel(), blocks.data_ptr()
+        result = torch.empty(count * self.stride, device=self.device, dtype=torch.uint16)
+        self.error.zero_()
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            status = _native.lib().grb_bctx_decode_words(ctypes.byref(self._descriptor), ids, count, result.data_ptr(),
+                                                         self.error.data_ptr(), stream)
+        _native.check(status, "grb_bctx_decode_words")
+        if check and self.error.item() != 0:
+            raise base.CodecError("CUDA decoder checkpoint mismatch")
+        return result.view(torch.bfloat16)
+
+    def decode(self, *, check=True):
+        """Dense BF16 [rows, cols], decoded from the unchanged streams (transient: the caller owns it)."""
+        import torch
+
+        if self.mode == 1:
+            return self.buffers["raw"].view(torch.bfloat16).reshape(self.shape)
+        return self._decode_blocks(check=check)[:self.n].reshape(self.shape)
+
+    def gather_rows(self, ids, *, check=True):
+        import torch
+
+        ids = ids.to(device=self.device, dtype=torch.int64)
+        if ids.numel() == 0:
+            return torch.empty((*ids.shape, self.shape[1]), device=self.device, dtype=torch.bfloat16)
+        if torch.any((ids < 0) | (ids >= self.shape[0])).item():
+            raise IndexError("embedding row outside tensor")
+        if self.mode == 1 or self.shape[1] % self.stride:
+            return self.decode(check=check)[ids]
+        per_row = self.shape[1] // self.stride
+        blocks = (ids.reshape(-1, 1) * per_row + torch.arange(per_row, device=self.device)).reshape(-1)
+        return self._decode_blocks(blocks, check=check).reshape(*ids.shape, self.shape[1])
+
+    # -- fused linear --------------------------------------------------------------------------------
+    def linear(self, x, out=None, bias=None):
+        """y = x @ W.T (+ bias) with W decoded inside the kernel; x [..., cols] BF16 -> y [..., rows] BF16."""
+        if self.resident is None:
+            raise RuntimeError("this tensor was indexed without a resident image (fused=False)")
+        return self.resident.linear(x, out=out, bias=bias)
+
+    def __call__(self, x, y):
+        self.resident(x, y)

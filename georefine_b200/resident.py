@@ -1,0 +1,185 @@
+"""The resident image of a weight (layout: csrc/bxr_format.h) and the fused entry points over it.
+
+``ResidentWeight`` follows the descriptor protocol of the reference's serving engines
+(``glc_serve/fastdec.py:172-188`` ``Lin``, ``glc_serve/tbe_desc.py:127-157`` ``TBELin``,
+``glc_serve/bigemm.py:468-507`` ``BILin``): attributes ``kind``, ``N``, ``K``, ``bytes``, ``coded_bytes`` and
+``__call__(x[M,K], y[M,N])`` writing into a preallocated ``y`` with no allocation and no host
+synchronisation, so a call can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+
+import numpy as np
+
+from . import _native
+
+GEMV_MAX_M = 8
+
+
+def sm_count(device) -> int:
+    import torch
+
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def build_image(words, workers: int, *, threads: int = 0, force_raw: bool = False, source_sha256: bytes | None = None):
+    """Host: BF16 words [rows, cols] -> (image bytes as uint8 array, header)."""
+    a = np.ascontiguousarray(words, dtype=np.uint16)
+    if a.ndim != 2 or not all(a.shape):
+        raise ValueError("expected a non-empty 2-D uint16 array")
+    if source_sha256 is None:
+        source_sha256 = hashlib.sha256(a.astype("<u2").tobytes()).digest()
+    digest = (ctypes.c_uint8 * 32).from_buffer_copy(source_sha256)
+    ptr, size = _native.U8P(), ctypes.c_uint64()
+    lib = _native.lib()
+    status = lib.bxr_build(a.ctypes.data_as(_native.U16P), a.shape[0], a.shape[1], int(workers), int(threads),
+                           int(force_raw), digest, ctypes.byref(ptr), ctypes.byref(size))
+    if status:
+        raise RuntimeError(f"bxr_build failed ({status})")
+    try:
+        image = np.ctypeslib.as_array(ptr, shape=(size.value,)).copy()
+    finally:
+        lib.bxr_free(ptr)
+    return image, header_of(image)
+
+
+def header_of(image) -> _native.BxrHeader:
+    return _native.BxrHeader.from_buffer_copy(image[:ctypes.sizeof(_native.BxrHeader)].tobytes())
+
+
+def decode_image_host(image) -> np.ndarray:
+    """Host twin of the GPU decoder; used to bind an image to its source digest before upload."""
+    h = header_of(image)
+    out = np.empty((h.rows, h.cols), dtype=np.uint16)
+    status = _native.lib().bxr_decode_host(image.ctypes.data_as(_native.U8P), image.size, out.ctypes.data_as(_native.U16P))
+    if status:
+        raise ValueError(f"resident image is malformed ({status})")
+    return out
+
+
+class ResidentWeight:
+    kind = "bctx"
+
+    def __init__(self, image: np.ndarray, device, *, max_m: int = 128, verify: bool = True):
+        import torch
+
+        self.header = header_of(image)
+        h = self.header
+        if verify:
+            words = decode_image_host(image)
+            if hashlib.sha256(words.astype("<u2").tobytes()).digest() != bytes(h.source_sha256):
+                raise ValueError("resident image does not reproduce its source digest")
+        self.device = torch.device(device)
+        self.N, self.K = int(h.rows), int(h.cols)
+        self.mode = int(h.mode)
+        self.image = torch.from_numpy(image).to(self.device)
+        self.status = torch.zeros(1, device=self.device, dtype=torch.int32)
+        self.max_m = 0
+        self.workspace = None
+        self.reserve(max_m)
+
+    @classmethod
+    def from_words(cls, words, device, *, source_sha256=None, max_m=128, workers=None, force_raw=False, verify=True):
+        workers = sm_count(device) if workers is None else workers
+        image, _ = build_image(words, workers, force_raw=force_raw, source_sha256=source_sha256)
+        return cls(image, device, max_m=max_m, verify=verify)
+
+    # -- bookkeeping (the numerators of the roofline) ----------------------------------------------------
+    @property
+    def bytes(self) -> int:
+        return int(self.header.total_bytes)
+
+    @property
+    def coded_bytes(self) -> int:
+        """Bytes one pass of a fused kernel streams from HBM: chunk blobs, restart states, blob index."""
+        return int(self.header.coded_bytes)
+
+    @property
+    def resident_bytes(self) -> int:
+        ws = 0 if self.workspace is None else self.workspace.numel()
+        return self.bytes + ws + 4
+
+    def backend_identity(self):
+        h = self.header
+        return {"format": "BXR1", "mode": self.mode, "workers": int(h.workers), "items": int(h.items),
+                "partial_slots": int(h.partial_slots), "library": str(_native.library_path().name)}
+
+    def reserve(self, max_m: int) -> None:
+        """Scratch for batches up to max_m rows (FP32 partial tiles + counters); zero-filled once."""
+        import torch
+
+        max_m = max(int(max_m), GEMV_MAX_M)
+        if max_m <= self.max_m:
+            return
+        need = int(_native.lib().grb_bxr_workspace_bytes(ctypes.byref(self.header), max_m))
+        need = max(need, int(_native.lib().grb_bxr_workspace_bytes(ctypes.byref(self.header), GEMV_MAX_M)))
+        self.workspace = torch.zeros(max(need, 256), device=self.device, dtype=torch.uint8)
+        self.max_m = max_m
+
+    # -- device entry points -------------------------------------------------------------------------
+    def _stream(self):
+        import torch
+
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def decode(self, *, check=True):
+        """Dense BF16 [N, K] decoded from the image by the decode twin of the fused kernels."""
+        import torch
+
+        out = torch.empty((self.N, self.K), device=self.device, dtype=torch.bfloat16)
+        self.status.zero_()
+        with torch.cuda.device(self.device):
+            st = _native.lib().grb_bxr_decode(self.image.data_ptr(), ctypes.byref(self.header), out.data_ptr(),
+                                              self.status.data_ptr(), self._stream())
+        _native.check(st, "grb_bxr_decode")
+        if check and self.status.item() != 0:
+            raise ValueError(f"resident decode reported status {self.status.item()}")
+        return out
+
+    def _run(self, entry, x, y, bias):
+        import torch
+
+        if x.dim() != 2 or y.dim() != 2 or x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16:
+            raise ValueError("x and y must be 2-D BF16 tensors")
+        m = x.shape[0]
+        if x.shape[1] != self.K or y.shape != (m, self.N) or x.stride(1) != 1 or y.stride(1) != 1:
+            raise ValueError("shape mismatch: x [M, K], y [M, N], unit inner stride")
+        if m == 0:
+            return
+        if m > self.max_m and min(m, 128) > min(self.max_m, 128):
+            raise ValueError(f"batch of {m} rows exceeds the reserved scratch ({self.max_m}); call reserve() first")
+        with torch.cuda.device(self.device):
+            st = entry(self.image.data_ptr(), ctypes.byref(self.header), x.data_ptr(), x.stride(0), m, y.data_ptr(),
+                       y.stride(0), None if bias is None else bias.data_ptr(), self.workspace.data_ptr(),
+                       self.workspace.numel(), self.status.data_ptr(), self._stream())
+        _native.check(st, entry.__name__)
+
+    def gemm(self, x, y, bias=None):
+        """tcgen05 path, any M; rows of y are bitwise independent of M."""
+        self._run(_native.lib().grb_bxr_gemm, x, y, bias)
+
+    def gemv(self, x, y, bias=None):
+        """CUDA-core path, M <= 8; rows of y are bitwise independent of M within 1..8."""
+        self._run(_native.lib().grb_bxr_gemv, x, y, bias)
+
+    def __call__(self, x, y):
+        self.gemm(x, y)
+
+    def linear(self, x, out=None, bias=None):
+        import torch
+
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        y = torch.empty((x2.shape[0], self.N), device=self.device, dtype=torch.bfloat16) if out is None else out.reshape(-1, self.N)
+        if x2.shape[0] > self.max_m:
+            self.reserve(x2.shape[0])
+        self.gemm(x2, y, bias)
+        return y.reshape(*lead, self.N)
+
+    def check_status(self) -> int:
+        """Host read of the device status word (synchronises); 0 means every call since the last reset was clean."""
+        return int(self.status.item())

@@ -1,0 +1,175 @@
+/*
+ * georefine_b200 -- C ABI of the B200-native BCTX path: plain pointers and sizes, no torch types.
+ *
+ * One shared library (libgeorefine_b200.so) exports three groups of entry points:
+ *
+ *   1. bcx_*   host coder and restart index.  Same names, argument lists, status codes and ownership
+ *              rules as the reference's ctypes ABI, so existing bindings load this library unchanged.
+ *   2. grb_bctx_*  CUDA decode of unchanged BCTX streams from their restart index (replaces the launch of
+ *              the reference's Triton kernels).
+ *   3. bxr_* / grb_bxr_*  the resident layout and the fused decode-GEMV / decode-GEMM kernels over it
+ *              (replace the reference's decode + F.linear and its fused native linears).
+ *
+ * Reference paths below are relative to the reference project root;
+ * cr/ = context-runtime/georefine_context_runtime/, gs/ = context-runtime/glc_serve/.
+ *
+ * Device entry points take raw device pointers and a CUDA stream handle (cudaStream_t passed as void*),
+ * never allocate, never synchronise with the host, and return an int: 0 on success, GRB_ERR_* otherwise.
+ * Faults found while a kernel runs (corrupt stream, expired wait) are reported through a caller-owned
+ * 32-bit device status word (GRB_STATUS_* bits, OR-ed in); a nonzero word means the output must be discarded.
+ */
+#ifndef GEOREFINE_B200_H
+#define GEOREFINE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../georefine_b200/csrc/bxr_format.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------------------------------------
+ * 1. Host coder (CPU).  Status: 0 ok, 1 bad arguments, 2 malformed stream or tables / out of memory,
+ *    3 internal failure.  Outputs are untouched unless the call returns 0.  No global state; safe to call
+ *    from several threads.
+ * ------------------------------------------------------------------------------------------------- */
+
+/* Replaces bcx_encode, cr/bitexact_context_ans.cpp:235-266.  kind 0 codes the 10-bit main symbol under
+ * nr*nc (row class x column class) models, kind 1 the 6-bit residual under 1024 models selected by the main
+ * symbol.  freq receives nctx*vocab frequencies (each context sums to 65536).  *stream is malloc'ed: release
+ * it with bcx_free. */
+int bcx_encode(const uint16_t* words, uint64_t n, uint32_t rows, uint32_t cols, const uint8_t* row_class,
+               const uint8_t* col_class, uint32_t nr, uint32_t nc, uint32_t kind, uint32_t* freq, uint8_t** stream,
+               size_t* stream_bytes);
+
+/* Replaces bcx_frequencies, cr/bitexact_context_ans.cpp:267-290 (tables only, no stream). */
+int bcx_frequencies(const uint16_t* words, uint64_t n, uint32_t rows, uint32_t cols, const uint8_t* row_class,
+                    const uint8_t* col_class, uint32_t nr, uint32_t nc, uint32_t kind, uint32_t* freq);
+
+/* Replace bcx_decode / bcx_decode_compact, cr/bitexact_context_ans.cpp:291-326.  resctx (kind 1 only) holds
+ * the main symbol of every element.  Rejects anything but the canonical end of stream. */
+int bcx_decode(const uint8_t* stream, size_t stream_bytes, uint64_t n, uint32_t rows, uint32_t cols,
+               const uint8_t* row_class, const uint8_t* col_class, uint32_t nr, uint32_t nc, uint32_t kind,
+               const uint16_t* resctx, const uint32_t* freq, uint16_t* symbols);
+int bcx_decode_compact(const uint8_t* stream, size_t stream_bytes, uint64_t n, uint32_t rows, uint32_t cols,
+                       const uint8_t* row_class, const uint8_t* col_class, uint32_t nr, uint32_t nc, uint32_t kind,
+                       const uint16_t* resctx, const uint32_t* freq, uint16_t* symbols);
+
+/* Replaces bcx_free, cr/bitexact_context_ans.cpp:327. */
+void bcx_free(void* p);
+
+/* Replace bcx_pack6 / bcx_unpack6, cr/bitexact_context_ans.cpp:328-359: residuals, 6 bits each, most
+ * significant bit first; unpack6 wants exactly ceil(6n/8) bytes with zero padding bits (2 otherwise). */
+int bcx_pack6(const uint16_t* words, uint64_t n, uint8_t** out, size_t* bytes);
+int bcx_unpack6(const uint8_t* in, size_t bytes, uint64_t n, uint16_t* residuals);
+
+/* Replaces bcx_checkpoint, cr/bitexact_context_gpu_index.cpp:21-137.  Walks the stream once and records the
+ * decoder state and byte offset in front of every stride-th symbol (offsets count from the start of the
+ * stream, so the first pair is (initial state, 4)).  Status: 0 ok, 1 arguments or labels, 2 tables,
+ * 3 stream/state, 4 offset beyond 32 bits, 5 out of memory, 6 other. */
+int bcx_checkpoint(const uint8_t* stream, size_t stream_bytes, uint64_t n, uint32_t rows, uint32_t cols,
+                   const uint8_t* row_class, const uint8_t* col_class, uint32_t nr, uint32_t nc, uint32_t kind,
+                   const uint16_t* resctx, const uint32_t* freq, uint32_t stride, uint32_t* states,
+                   uint32_t* offsets, uint16_t* symbols);
+
+/* Tables for grb_bctx_decode_words: cum = u32[nctx][vocab+1] prefix sums, bucket = u16[nctx][4096] symbol
+ * owning the first slot of each 16-slot bucket.  Takes the place of the cumulative tables the reference
+ * builds in CudaContextTensor.__init__, cr/bitexact_context_gpu.py:120-125.  0 ok, 1 arguments, 2 tables. */
+int grb_bctx_build_lookup(const uint32_t* freq, uint32_t nctx, uint32_t vocab, uint32_t* cum, uint16_t* bucket);
+
+/* ---------------------------------------------------------------------------------------------------
+ * 2. CUDA decode of unchanged BCTX streams.
+ * ------------------------------------------------------------------------------------------------- */
+
+#define GRB_OK 0
+#define GRB_ERR_ARGUMENT 1      /* null pointer, bad size, misaligned buffer */
+#define GRB_ERR_UNSUPPORTED 2   /* e.g. batch larger than the entry point handles, raw-mode image */
+#define GRB_ERR_WORKSPACE 3     /* workspace too small */
+#define GRB_ERR_CUDA 100        /* + cudaError_t of the failing runtime call */
+
+#define GRB_STATUS_BAD_SYMBOL 1u
+#define GRB_STATUS_OVERRUN 2u
+#define GRB_STATUS_LOW_STATE 4u
+#define GRB_STATUS_CHECKPOINT 8u
+#define GRB_STATUS_TIMEOUT 16u
+#define GRB_STATUS_BAD_ARGUMENT 32u
+
+/* Device pointers of one indexed frame: the arrays CudaContextTensor keeps in .buffers
+ * (cr/bitexact_context_gpu.py:109-128) plus the lookup tables above. */
+typedef struct grb_bctx_tensor {
+  uint64_t n;                 /* rows * cols */
+  uint32_t rows, cols;
+  uint32_t nr, nc;
+  uint32_t mode;              /* 0 raw6 residual, 128 conditional residual stream */
+  uint32_t stride;            /* words per restart block */
+  const uint8_t* row_class;   /* u8[rows] */
+  const uint8_t* col_class;   /* u8[cols] */
+  const uint8_t* main_stream; uint64_t main_bytes;
+  const uint32_t* main_states; const uint32_t* main_offsets;   /* u32[ceil(n/stride)] */
+  const uint32_t* main_cum;   const uint16_t* main_bucket;
+  const uint8_t* residual_stream; uint64_t residual_bytes;     /* raw6 bytes or the conditional stream */
+  const uint32_t* residual_states; const uint32_t* residual_offsets;  /* mode 128 only */
+  const uint32_t* residual_cum;    const uint16_t* residual_bucket;   /* mode 128 only */
+} grb_bctx_tensor;
+
+/* Replaces the launch of decode_words, cr/bitexact_context_gpu.py:130-152 / bitexact_context_gpu_kernels.py:
+ * 114-169.  block_ids == NULL decodes blocks 0..count-1, otherwise the listed blocks (gather).  out receives
+ * count*stride words, block-major.  *status is OR-ed with GRB_STATUS_* bits; the caller zeroes it. */
+int grb_bctx_decode_words(const grb_bctx_tensor* tensor, const int64_t* block_ids, uint64_t count, uint16_t* out,
+                          uint32_t* status, void* cuda_stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * 3. Resident layout (bxr_format.h) and the fused kernels.
+ * ------------------------------------------------------------------------------------------------- */
+
+/* Host: re-codes decoded BF16 words into a resident image for `workers` persistent CTAs (the SM count of the
+ * target GPU).  Stands where the reference transcodes a frame into its runtime formats at load
+ * (gs/bctx_v21_transcode.py:59-560; gs/tbe_desc.py:42-51).  force_raw != 0 stores plain tiles.
+ * source_sha256 (optional, 32 bytes) is copied into the header.  *image is malloc'ed: release with bxr_free.
+ * 0 ok, 1 arguments, 2 out of memory, 3 other. */
+int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t workers, uint32_t host_threads,
+              uint32_t force_raw, const uint8_t* source_sha256, uint8_t** image, uint64_t* image_bytes);
+void bxr_free(void* p);
+
+/* Host twin of the GPU decoder, used to bind an image to its source digest before upload (the check the
+ * reference makes at cr/bitexact_context_gpu.py:104-105).  0 ok, 1 malformed image, 2 corrupt stream. */
+int bxr_decode_host(const uint8_t* image, uint64_t image_bytes, uint16_t* words);
+
+/* Bytes of caller-owned device scratch the fused entry points need for this image and batch tile:
+ * FP32 partial tiles of row blocks shared by several CTAs, preceded by one counter per row block.
+ * The scratch must be zero-filled once after allocation; the kernels leave the counters at zero. */
+uint64_t grb_bxr_workspace_bytes(const bxr_header* header, uint32_t max_m);
+
+/* Decode twin: writes rows*cols BF16 words.  Replaces CudaContextTensor.decode() for a resident image,
+ * cr/bitexact_context_gpu.py:154-157. */
+int grb_bxr_decode(const void* device_image, const bxr_header* header, uint16_t* out, uint32_t* status,
+                   void* cuda_stream);
+
+/* y[m, n] = bf16( sum_k x[m, k] * W[n, k] (+ bias[n]) ), FP32 accumulation, W decoded on the fly.
+ *   x: BF16 [m, cols], row stride ldx elements, 16-byte aligned, ldx % 8 == 0;  y: BF16 [m, rows], stride ldy.
+ *
+ * grb_bxr_gemm (any m; tcgen05/TMEM) replaces bi_gemm_dense, gs/bi_csrc/bi_api.h:55-57 and the simple path
+ * BctxLinear.forward, cr/bitexact_context_serving.py:365-376.  Rows of y do not depend on m.
+ * grb_bxr_gemv (m <= 8; CUDA cores) replaces miv_tbe_gemv, gs/miv_tbe_csrc/miv_tbe.h:57-65, and
+ * miv_gemv_out, gs/miv_gemv.py:125-191, with the same M-invariance among m = 1..8.
+ * The two entry points use different reduction orders; a caller that needs bitwise equal rows across batch
+ * sizes must stay with one of them. */
+int grb_bxr_gemm(const void* device_image, const bxr_header* header, const void* x, int64_t ldx, uint32_t m, void* y,
+                 int64_t ldy, const void* bias, void* workspace, uint64_t workspace_bytes, uint32_t* status,
+                 void* cuda_stream);
+int grb_bxr_gemv(const void* device_image, const bxr_header* header, const void* x, int64_t ldx, uint32_t m, void* y,
+                 int64_t ldy, const void* bias, void* workspace, uint64_t workspace_bytes, uint32_t* status,
+                 void* cuda_stream);
+
+/* Registers, spills and shared memory of the compiled kernels, for tuning records (the reference reads the
+ * same from its card in bi_kernel_attrs, gs/bi_csrc/bi_gemm.cuh:1104-1121).  which: 0 BCTX decode, 1 BXR
+ * decode, 2 GEMV (m=1), 3 GEMM (N tile 16), 4 GEMM (N tile 128).  out = {registers, local bytes, static smem,
+ * max dynamic smem, max threads}. */
+int grb_kernel_attributes(int which, int out[5]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
