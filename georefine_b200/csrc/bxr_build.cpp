@@ -211,7 +211,7 @@ void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, con
   const uint32_t nch = it.chunk_end - it.chunk_begin;
   std::vector<uint16_t> rev;
   for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
-    const uint32_t q = sid / BXR_ROWS, r = sid % BXR_ROWS;
+    const uint32_t piece = sid / BXR_ROWS, r = sid % BXR_ROWS;  // piece = 2q + d: 16 columns of the chunk
     const uint32_t row = it.row_block * BXR_ROWS + r;
     const uint32_t b = base[row];
     rev.clear();
@@ -222,7 +222,7 @@ void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, con
     for (uint32_t c = it.chunk_end; c-- > it.chunk_begin;) {
       const size_t before = rev.size();
       for (int t = BXR_STEPS - 1; t >= 0; --t) {
-        const uint32_t col = c * BXR_COLS + q * BXR_PHASE_COLS + 2 * uint32_t(t);
+        const uint32_t col = c * BXR_COLS + piece * BXR_STREAM_COLS + 2 * uint32_t(t);
         const uint32_t e0 = exponent_of(src.padded(row, col, base)), e1 = exponent_of(src.padded(row, col + 1, base));
         const uint32_t n0 = nibble_of(e0, b), n1 = nibble_of(e1, b);
         if (n1 == BXR_ESCAPE) coder.put_byte(e1);
@@ -231,7 +231,7 @@ void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, con
         coder.put_symbol(freq[sym], cum[sym]);
       }
       const size_t used = rev.size() - before;
-      // At most 3 words per step (one symbol, two escape bytes), so 48 per chunk; 255 flags an overflow.
+      // At most 3 words per step (one symbol, two escape bytes), so 24 per chunk; 255 flags an overflow.
       counts[c - it.chunk_begin] = used > 120 ? uint8_t(255) : uint8_t(used);
     }
     code.state[sid] = coder.x;
@@ -262,7 +262,8 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     const uint32_t nitems = uint32_t(plan.items.size());
 
     std::vector<uint8_t> base(rows_pad, 0);
-    std::vector<uint64_t> lut(BXR_PROB_TOTAL, 0);
+    std::vector<uint32_t> lut(BXR_PROB_TOTAL, 0);
+    uint32_t esc_slot = BXR_PROB_TOTAL;
     std::vector<std::vector<uint8_t>> blobs(nblobs);
     std::vector<uint32_t> states(size_t(nitems) * BXR_STREAMS, BXR_STATE_LOW);
     bool raw_mode = force_raw != 0;
@@ -287,18 +288,22 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
       std::vector<uint64_t> counts(256, 0);
       for (auto& l : local)
         for (int s = 0; s < 256; ++s) counts[s] += l[s];
-      uint32_t freq[256], cum[257];
+      uint32_t freq[256], cum[256];
       quantise_pairs(counts, freq);
-      cum[0] = 0;
-      for (int s = 0; s < 256; ++s) cum[s + 1] = cum[s] + freq[s];
+      // A record has 12 bits for the frequency: a symbol that owns every slot cedes one to an unused symbol.
       for (uint32_t s = 0; s < 256; ++s)
-        for (uint32_t slot = cum[s]; slot < cum[s + 1]; ++slot) {
-          const uint32_t n0 = s & 15, n1 = s >> 4;
-          const uint32_t lo = freq[s] | (n0 == BXR_ESCAPE ? BXR_LUT_ESC0 : 0) | (n1 == BXR_ESCAPE ? BXR_LUT_ESC1 : 0) |
-                              (slot - cum[s]) << 16;
-          const uint32_t hi = (n0 == BXR_ESCAPE ? 0 : n0) << 7 | (n1 == BXR_ESCAPE ? 0 : n1) << 23;
-          lut[slot] = uint64_t(lo) | uint64_t(hi) << 32;
-        }
+        if (freq[s] == BXR_PROB_TOTAL) { freq[s] -= 1; freq[s ? 0 : 1] += 1; }
+      // Slot order: symbols without an escape first, then the ones with an escape nibble.
+      auto has_escape = [](uint32_t s) { return (s & 15) == BXR_ESCAPE || (s >> 4) == BXR_ESCAPE; };
+      uint32_t run = 0;
+      for (int pass = 0; pass < 2; ++pass) {
+        if (pass == 1) esc_slot = run;
+        for (uint32_t s = 0; s < 256; ++s)
+          if (has_escape(s) == (pass == 1)) { cum[s] = run; run += freq[s]; }
+      }
+      for (uint32_t s = 0; s < 256; ++s)
+        for (uint32_t slot = cum[s]; slot < cum[s] + freq[s]; ++slot)
+          lut[slot] = freq[s] | (s & 15) << 12 | (slot - cum[s]) << 16 | (s >> 4) << 28;
 
       std::atomic<bool> overflow{false};
       parallel_for(nitems, threads, [&](uint32_t i) {
@@ -320,18 +325,17 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
           std::vector<uint8_t>& blob = blobs[size_t(it.row_block) * plan.chunks + c];
           blob.assign(size_t(align16(BXR_WORDS_AT + 2ull * total)), 0);
           uint8_t* raw = blob.data() + BXR_COUNT_BYTES;
-          for (uint32_t q = 0; q < BXR_PHASES; ++q)
-            for (uint32_t j = 0; j < 2; ++j)
-              for (uint32_t r = 0; r < BXR_ROWS; ++r) {
-                uint8_t* piece = raw + (size_t(q * 2 + j) * BXR_ROWS + r) * 16;
-                const uint32_t row = it.row_block * BXR_ROWS + r, col = c * BXR_COLS + q * BXR_PHASE_COLS + j * 16;
-                for (uint32_t e = 0; e < 16; ++e) piece[e] = raw_byte_of(src.padded(row, col + e, base.data()));
-              }
+          for (uint32_t piece = 0; piece < 2 * BXR_PHASES; ++piece)
+            for (uint32_t r = 0; r < BXR_ROWS; ++r) {
+              uint8_t* dst = raw + (size_t(piece) * BXR_ROWS + r) * 16;
+              const uint32_t row = it.row_block * BXR_ROWS + r, col = c * BXR_COLS + piece * BXR_STREAM_COLS;
+              for (uint32_t e = 0; e < 16; ++e) dst[e] = raw_byte_of(src.padded(row, col + e, base.data()));
+            }
           uint16_t* w = reinterpret_cast<uint16_t*>(blob.data() + BXR_WORDS_AT);
           uint32_t at = 0;
           for (uint32_t g = 0; g < BXR_SEGMENTS; ++g) {
-            const uint32_t h = g / BXR_ROWS, r = g % BXR_ROWS;
-            const uint32_t fwd = (2 * h) * BXR_ROWS + r, bwd = (2 * h + 1) * BXR_ROWS + r;
+            const uint32_t q = g / BXR_ROWS, r = g % BXR_ROWS;
+            const uint32_t fwd = (2 * q) * BXR_ROWS + r, bwd = (2 * q + 1) * BXR_ROWS + r;
             const uint32_t nf = code->per_chunk[fwd][k], nb = code->per_chunk[bwd][k];
             blob[g] = uint8_t(nf + nb);
             for (uint32_t e = 0; e < nf; ++e) w[at + e] = code->words[fwd][cursor[fwd] + e];
@@ -371,9 +375,10 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     h.workers = workers;
     h.items = nitems;
     h.partial_slots = plan.partial_slots;
+    h.esc_slot = esc_slot;
     uint64_t at = align16(sizeof(bxr_header));
     at = (at + 255) & ~uint64_t(255);
-    h.lut_at = at;            at += raw_mode ? 0 : sizeof(uint64_t) * BXR_PROB_TOTAL;
+    h.lut_at = at;            at += raw_mode ? 0 : sizeof(uint32_t) * BXR_PROB_TOTAL;
     h.base_at = at;           at = align16(at + rows_pad);
     h.items_at = at;          at = align16(at + sizeof(bxr_item) * nitems);
     h.worker_items_at = at;   at = align16(at + 4ull * (workers + 1));
@@ -393,7 +398,7 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     auto* img = static_cast<uint8_t*>(std::calloc(size_t(h.total_bytes), 1));
     if (!img) return 2;
     std::memcpy(img, &h, sizeof h);
-    if (!raw_mode) std::memcpy(img + h.lut_at, lut.data(), sizeof(uint64_t) * BXR_PROB_TOTAL);
+    if (!raw_mode) std::memcpy(img + h.lut_at, lut.data(), sizeof(uint32_t) * BXR_PROB_TOTAL);
     std::memcpy(img + h.base_at, base.data(), rows_pad);
     std::memcpy(img + h.items_at, plan.items.data(), sizeof(bxr_item) * nitems);
     std::memcpy(img + h.worker_items_at, plan.worker_items.data(), 4ull * (workers + 1));
@@ -438,7 +443,7 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
         }
       return 0;
     }
-    const auto* lut = reinterpret_cast<const uint64_t*>(img + h.lut_at);
+    const auto* lut = reinterpret_cast<const uint32_t*>(img + h.lut_at);
     const uint8_t* base = img + h.base_at;
     const auto* states = reinterpret_cast<const uint32_t*>(img + h.states_at);
     int status = 0;
@@ -456,8 +461,8 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
         for (uint32_t g = 0; g < BXR_SEGMENTS; ++g) start[g + 1] = start[g] + blob[g];
         if (int64_t(start[BXR_SEGMENTS]) > nwords) return 2;
         for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
-          const uint32_t q = sid / BXR_ROWS, r = sid % BXR_ROWS, g = (q / 2) * BXR_ROWS + r;
-          const bool backward = q & 1;
+          const uint32_t piece = sid / BXR_ROWS, r = sid % BXR_ROWS, g = (piece / 2) * BXR_ROWS + r;
+          const bool backward = piece & 1;
           int64_t cur = backward ? int64_t(start[g + 1]) - 1 : int64_t(start[g]);
           const int step = backward ? -1 : 1;
           uint32_t s = x[sid];
@@ -469,21 +474,22 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
             }
           };
           const uint32_t row = it.row_block * BXR_ROWS + r, b = base[row];
-          for (uint32_t j = 0; j < 2; ++j) {
-            const uint8_t* piece = blob + BXR_COUNT_BYTES + (size_t(q * 2 + j) * BXR_ROWS + r) * 16;
-            for (uint32_t t = 0; t < 8; ++t) {
-              const uint64_t rec = lut[s & (BXR_PROB_TOTAL - 1)];
-              const uint32_t lo = uint32_t(rec), hi = uint32_t(rec >> 32);
-              s = (lo & BXR_LUT_FREQ_MASK) * (s >> BXR_PROB_BITS) + (lo >> 16);
-              refill();
-              uint32_t e0 = ((hi >> 7) & 0xFF) + b, e1 = ((hi >> 23) & 0xFF) + b;
-              if (lo & BXR_LUT_ESC0) { e0 = s & 0xFF; s >>= 8; refill(); }
-              if (lo & BXR_LUT_ESC1) { e1 = s & 0xFF; s >>= 8; refill(); }
-              const uint32_t b0 = piece[2 * t], b1 = piece[2 * t + 1];
-              const uint32_t col = c * BXR_COLS + q * BXR_PHASE_COLS + j * 16 + 2 * t;
-              put(row, col, uint16_t((b0 & 0x80) << 8 | (e0 & 0xFF) << 7 | (b0 & 0x7F)));
-              put(row, col + 1, uint16_t((b1 & 0x80) << 8 | (e1 & 0xFF) << 7 | (b1 & 0x7F)));
+          const uint8_t* bytes16 = blob + BXR_COUNT_BYTES + (size_t(piece) * BXR_ROWS + r) * 16;
+          for (uint32_t t = 0; t < BXR_STEPS; ++t) {
+            const uint32_t slot = s & (BXR_PROB_TOTAL - 1);
+            const uint32_t rec = lut[slot];
+            s = (rec & BXR_LUT_FREQ_MASK) * (s >> BXR_PROB_BITS) + ((rec >> 16) & BXR_LUT_FREQ_MASK);
+            refill();
+            const uint32_t n0 = (rec >> 12) & 15, n1 = rec >> 28;
+            uint32_t e0 = n0 + b, e1 = n1 + b;
+            if (slot >= h.esc_slot) {
+              if (n0 == BXR_ESCAPE) { e0 = s & 0xFF; s >>= 8; refill(); }
+              if (n1 == BXR_ESCAPE) { e1 = s & 0xFF; s >>= 8; refill(); }
             }
+            const uint32_t b0 = bytes16[2 * t], b1 = bytes16[2 * t + 1];
+            const uint32_t col = c * BXR_COLS + piece * BXR_STREAM_COLS + 2 * t;
+            put(row, col, uint16_t((b0 & 0x80) << 8 | (e0 & 0xFF) << 7 | (b0 & 0x7F)));
+            put(row, col + 1, uint16_t((b1 & 0x80) << 8 | (e1 & 0xFF) << 7 | (b1 & 0x7F)));
           }
           x[sid] = s;
           if (status) return status;

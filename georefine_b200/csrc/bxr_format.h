@@ -12,20 +12,22 @@
 //               exponent follows in the same stream at probability 1/256)
 //   symbol   = n(col 2t) | n(col 2t+1) << 4                one rANS step decodes two weights
 //   rANS     : 32-bit state, lower bound 2^16, 16-bit words, 12-bit probabilities, one static table
-//              per tensor stored as 4096 slot records {freq | esc flags | bias, exponent bits}
+//              per tensor stored as 4096 32-bit slot records {freq, n0, bias, n1}; symbols that contain
+//              an escape own the highest slots, so "slot >= esc_slot" is the whole escape test
 //
 // Geometry.  Rows are grouped in row blocks of 128 (one UMMA M tile), columns in chunks of 128.  Inside a
-// chunk every row has 4 independent streams ("phases"), phase q coding columns [32q, 32q+32) of the chunk
-// in 16 steps.  A stream runs through consecutive chunks of one work item without being flushed; a lane
-// owns one stream, so 16 warps decode a chunk of a row block in lock step without ever communicating.
-// The words consumed by a stream while it decodes one chunk are stored with that chunk: streams 2h and
-// 2h+1 of a row share one segment, the even one reading forward from the segment's first word, the odd
-// one backward from its last, so one byte (the segment's word count) locates both.
+// chunk every row has 8 independent streams of 16 columns (8 steps) each.  A stream runs through the
+// consecutive chunks of one work item without being flushed.  Streams 2q and 2q+1 of a row (columns
+// [32q, 32q+16) and [32q+16, 32q+32) of the chunk) belong to one lane, which decodes them interleaved: two
+// independent dependency chains per lane.  The words the two streams consume while they decode one chunk
+// are stored with that chunk in one segment: the even stream reads forward from the segment's first word,
+// the odd one backward from its last, so one byte (the segment's word count) locates both.  16 warps
+// decode a chunk of a row block in lock step without ever communicating.
 //
-// Chunk blob (size = multiple of 16 bytes, at most kBlobMax):
-//   [0,256)          u8  count[256]         words in segment g = h*128 + r           (h = phase / 2)
-//   [256,16640)      u8  raw[4][2][128][16] piece (q, j, r) = raw bytes of row r, chunk columns 32q+16j..+15
-//   [16640, ...)     u16 words              segments in order g, then zero padding
+// Chunk blob (size = multiple of 16 bytes, at most BXR_BLOB_MAX):
+//   [0,512)          u8  count[512]         words in segment g = q*128 + r
+//   [512,16896)      u8  raw[8][128][16]    piece (s, r) = raw bytes of row r, chunk columns 16s..16s+15
+//   [16896, ...)     u16 words              segments in order g, then zero padding
 //
 // Work items.  The K range of every row block is cut so that `workers` CTAs get equal numbers of chunks
 // (a contiguous range of the (row block, chunk) sequence each).  An item is the part of one row block
@@ -38,12 +40,12 @@
 #define BXR_MAGIC 0x31525842u /* "BXR1" */
 #define BXR_ROWS 128
 #define BXR_COLS 128
-#define BXR_PHASES 4
-#define BXR_PHASE_COLS 32
-#define BXR_STEPS 16
-#define BXR_STREAMS 512  /* per row block: phase * 128 + row */
-#define BXR_SEGMENTS 256 /* per chunk: (phase / 2) * 128 + row */
-#define BXR_COUNT_BYTES 256
+#define BXR_PHASES 4       /* lanes per row: phase q owns chunk columns [32q, 32q+32) */
+#define BXR_STREAM_COLS 16
+#define BXR_STEPS 8        /* two weights per step */
+#define BXR_STREAMS 1024   /* per row block: (2q + d) * 128 + row, d = 0 forward / 1 backward reader */
+#define BXR_SEGMENTS 512   /* per chunk: q * 128 + row */
+#define BXR_COUNT_BYTES 512
 #define BXR_RAW_BYTES 16384
 #define BXR_WORDS_AT (BXR_COUNT_BYTES + BXR_RAW_BYTES)
 #define BXR_BLOB_MAX 24576 /* shared-memory slot per chunk blob */
@@ -56,11 +58,10 @@
 #define BXR_MODE_RAW 1 /* chunk blob = the 128x128 BF16 tile itself, already in UMMA operand order */
 #define BXR_RAW_TILE_BYTES 32768
 
-/* Slot record of the pair table: lo = freq[0,13) | esc0 << 13 | esc1 << 14 | bias << 16,
- * hi = n0 << 7 | n1 << 23 (escaped nibbles contribute 0). */
-#define BXR_LUT_ESC0 0x2000u
-#define BXR_LUT_ESC1 0x4000u
-#define BXR_LUT_FREQ_MASK 0x1FFFu
+/* Slot record of the pair table, 32 bits: freq[0,12) | n0[12,16) | bias[16,28) | n1[28,32), so that
+ * (record >> 5) & 0x07800780 is the pair of relative exponents in BF16 position.  freq <= 4095. */
+#define BXR_LUT_FREQ_MASK 0xFFFu
+#define BXR_LUT_EXP_MASK 0x07800780u
 
 typedef struct bxr_item {
   uint32_t row_block;  /* which 128-row block */
@@ -78,12 +79,12 @@ typedef struct bxr_header {
   uint32_t row_blocks, chunks;    /* padded shape / 128 */
   uint32_t workers, items;
   uint32_t partial_slots;         /* FP32 partial tiles the workspace must hold */
-  uint32_t reserved0;
-  uint64_t lut_at;                /* u64[4096] slot records (absent in raw mode) */
+  uint32_t esc_slot;              /* slots >= esc_slot decode to a symbol with at least one escape */
+  uint64_t lut_at;                /* u32[4096] slot records (absent in raw mode) */
   uint64_t base_at;               /* u8[row_blocks*128] exponent base per row */
   uint64_t items_at;              /* bxr_item[items] */
   uint64_t worker_items_at;       /* u32[workers+1]: items of worker w are [v[w], v[w+1]) */
-  uint64_t states_at;             /* u32[items][512] start state of every stream */
+  uint64_t states_at;             /* u32[items][1024] start state of every stream */
   uint64_t blob_index_at;         /* u32[row_blocks*chunks+1] blob offsets in 16-byte units from blobs_at */
   uint64_t blobs_at;
   uint64_t total_bytes;

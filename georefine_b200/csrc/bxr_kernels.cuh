@@ -29,15 +29,16 @@ constexpr int kWarpEpilogue = 20;  // 4 warps, TMEM lane quarter = warp % 4
 constexpr int kThreadsUmma = 24 * 32;
 constexpr int kThreadsSimt = 18 * 32;
 
-constexpr uint32_t kLutBytes = 8 * BXR_PROB_TOTAL;
-constexpr uint32_t kSegOffBytes = 528;  // u16[257] rounded up
+constexpr uint32_t kLutBytes = 4 * BXR_PROB_TOTAL;
+constexpr uint32_t kSegOffBytes = 1040;  // u16[513] rounded up
 constexpr uint32_t kAtomBytes = 16384;  // 128 rows x 64 BF16
-constexpr uint32_t kInGuard = 128;      // a corrupt stream may read up to 96 bytes past its slot
+constexpr uint32_t kInGuard = 128;      // a corrupt stream may read up to 48 bytes past its slot
 constexpr int kGemvMaxM = 8;
 
 struct BxrArgs {
   // image
-  const uint64_t* lut;
+  const uint32_t* lut;
+  uint32_t esc_slot;
   const uint8_t* base;
   const bxr_item* items;
   const uint32_t* worker_items;
@@ -101,34 +102,45 @@ struct RoleCtx {
   }
 };
 
-// One rANS step of a lane: returns the exponent bits of two weights, positioned for a packed BF16 pair
-// (bits 7..14 and 23..30) and relative to the row base unless an escape replaced them.
+// The two rANS streams of a lane (the forward and the backward reader of one segment), advanced together
+// so that their dependency chains overlap.  A step of a stream yields the exponent bits of two weights in
+// packed-BF16 position (bits 7..14 and 23..30).
 struct LaneDecoder {
-  uint32_t x;      // rANS state
-  uint32_t wp;     // shared address of the next 16-bit word of this stream
-  int wstep;       // +2 forward, -2 backward
-  uint32_t lut;    // shared address of the slot records
-  uint32_t base2;  // row base replicated into both exponent fields
+  uint32_t xf, xb;   // rANS states
+  uint32_t wf, wb;   // shared addresses of the next 16-bit word of each stream
+  uint32_t lut;      // shared address of the slot records
+  uint32_t base2;    // row base replicated into both exponent fields
+  uint32_t esc_slot;
 
-  __device__ __forceinline__ void refill() {
-    if (x < BXR_STATE_LOW) {
-      x = (x << 16) | lds_u16(wp);
-      wp += wstep;
+  // rare: an exponent outside the row window follows in the stream as a raw byte
+  __device__ __forceinline__ uint32_t escape(uint32_t rec, uint32_t& x, uint32_t& wp, int wstep) const {
+    const uint32_t b = (base2 >> 7) & 0xFFu;
+    uint32_t e0 = ((rec >> 12) & 15u) + b, e1 = (rec >> 28) + b;
+    if (((rec >> 12) & 15u) == BXR_ESCAPE) {
+      e0 = x & 0xFFu;
+      x >>= 8;
+      if (x < BXR_STATE_LOW) { x = (x << 16) | lds_u16(wp); wp += wstep; }
     }
+    if ((rec >> 28) == BXR_ESCAPE) {
+      e1 = x & 0xFFu;
+      x >>= 8;
+      if (x < BXR_STATE_LOW) { x = (x << 16) | lds_u16(wp); wp += wstep; }
+    }
+    return (e0 << 7) | (e1 << 23);
   }
-  __device__ __forceinline__ uint32_t step() {
-    const uint2 rec = lds64(lut + ((x & (BXR_PROB_TOTAL - 1)) << 3));
-    x = (rec.x & BXR_LUT_FREQ_MASK) * (x >> BXR_PROB_BITS) + (rec.x >> 16);
-    refill();
-    uint32_t e = rec.y;
-    if (rec.x & (BXR_LUT_ESC0 | BXR_LUT_ESC1)) {  // rare: an exponent outside the row window
-      const uint32_t b = (base2 >> 7) & 0xFFu;
-      uint32_t e0 = ((e >> 7) & 0xFFu) + b, e1 = ((e >> 23) & 0xFFu) + b;
-      if (rec.x & BXR_LUT_ESC0) { e0 = x & 0xFFu; x >>= 8; refill(); }
-      if (rec.x & BXR_LUT_ESC1) { e1 = x & 0xFFu; x >>= 8; refill(); }
-      e = ((e0 << 7) | (e1 << 23)) - base2;
+  __device__ __forceinline__ void step(uint32_t& ef, uint32_t& eb) {
+    const uint32_t sf = xf & (BXR_PROB_TOTAL - 1), sb = xb & (BXR_PROB_TOTAL - 1);
+    const uint32_t rf = lds32(lut + (sf << 2)), rb = lds32(lut + (sb << 2));
+    xf = (rf & BXR_LUT_FREQ_MASK) * (xf >> BXR_PROB_BITS) + ((rf >> 16) & BXR_LUT_FREQ_MASK);
+    xb = (rb & BXR_LUT_FREQ_MASK) * (xb >> BXR_PROB_BITS) + ((rb >> 16) & BXR_LUT_FREQ_MASK);
+    if (xf < BXR_STATE_LOW) { xf = (xf << 16) | lds_u16(wf); wf += 2; }
+    if (xb < BXR_STATE_LOW) { xb = (xb << 16) | lds_u16(wb); wb -= 2; }
+    ef = ((rf >> 5) & BXR_LUT_EXP_MASK) + base2;
+    eb = ((rb >> 5) & BXR_LUT_EXP_MASK) + base2;
+    if (max(sf, sb) >= esc_slot) {
+      if (sf >= esc_slot) ef = escape(rf, xf, wf, 2);
+      if (sb >= esc_slot) eb = escape(rb, xb, wb, -2);
     }
-    return e + base2;
   }
 };
 
@@ -137,14 +149,22 @@ __device__ __forceinline__ uint32_t join_pair(uint32_t raw4, uint32_t selector, 
   return (__byte_perm(raw4, 0, selector) & 0x807F807Fu) | expo;
 }
 
-// Decodes 8 consecutive weights of the lane's row from two raw registers (8 bytes).
-__device__ __forceinline__ uint4 decode8(LaneDecoder& d, uint32_t raw_lo, uint32_t raw_hi) {
-  uint4 w;
-  w.x = join_pair(raw_lo, 0x1100, d.step());
-  w.y = join_pair(raw_lo, 0x3322, d.step());
-  w.z = join_pair(raw_hi, 0x1100, d.step());
-  w.w = join_pair(raw_hi, 0x3322, d.step());
-  return w;
+// Decodes 8 consecutive weights of each of the lane's two streams from 8 raw bytes per stream.
+__device__ __forceinline__ void decode8x2(LaneDecoder& d, uint32_t f_lo, uint32_t f_hi, uint32_t b_lo, uint32_t b_hi,
+                                          uint4& wf, uint4& wb) {
+  uint32_t ef, eb;
+  d.step(ef, eb);
+  wf.x = join_pair(f_lo, 0x1100, ef);
+  wb.x = join_pair(b_lo, 0x1100, eb);
+  d.step(ef, eb);
+  wf.y = join_pair(f_lo, 0x3322, ef);
+  wb.y = join_pair(b_lo, 0x3322, eb);
+  d.step(ef, eb);
+  wf.z = join_pair(f_hi, 0x1100, ef);
+  wb.z = join_pair(b_hi, 0x1100, eb);
+  d.step(ef, eb);
+  wf.w = join_pair(f_hi, 0x3322, ef);
+  wb.w = join_pair(b_hi, 0x3322, eb);
 }
 
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
@@ -192,7 +212,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     tmem_alloc(smem + L::misc, kTmemCols);
     tmem_relinquish();
   }
-  // the slot-record table: 32 KB, copied cooperatively (L2 hits after the first CTA)
+  // the slot-record table: 16 KB, copied cooperatively (L2 hits after the first CTA)
   for (uint32_t i = threadIdx.x; i < kLutBytes / 16; i += blockDim.x)
     sts128(smem + L::lut + i * 16, __ldg(reinterpret_cast<const uint4*>(args.lut) + i));
   tc_fence_before();
@@ -207,18 +227,19 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   const uint32_t unit_count = uint32_t(units * (worker + 1) / args.workers) - unit_begin;
 
   if (warp < kDecoderWarps) {
-    // ------------------------------------------------------------------ decoders: one stream per lane
+    // ------------------------------------------------------------------ decoders: one segment (2 streams) per lane
     const uint32_t q = warp >> 2, r = (warp & 3) * 32 + lane;
-    const uint32_t backward = q & 1, seg = (q >> 1) * BXR_ROWS + r, atom = q >> 1;
+    const uint32_t seg = q * BXR_ROWS + r, atom = q >> 1;
     LaneDecoder d;
     d.lut = smem + L::lut;
-    d.wstep = backward ? -2 : 2;
+    d.esc_slot = args.esc_slot;
     uint32_t u = 0;
     bool live = true;
     for (uint32_t it = item_begin; it < item_end && live; ++it) {
       const bxr_item item = args.items[it];
       const uint32_t row = item.row_block * BXR_ROWS + r;
-      d.x = args.states[size_t(it) * BXR_STREAMS + q * BXR_ROWS + r];
+      d.xf = args.states[size_t(it) * BXR_STREAMS + (2 * q) * BXR_ROWS + r];
+      d.xb = args.states[size_t(it) * BXR_STREAMS + (2 * q + 1) * BXR_ROWS + r];
       d.base2 = uint32_t(args.base[row]) * 0x00800080u;
       float acc[MODE == kGemv ? kGemvMaxM : 1];
 #pragma unroll
@@ -227,23 +248,28 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         const uint32_t s = u % L::kIn, ph = (u / L::kIn) & 1;
         if (ctx.aborted() || !ctx.wait(bar_in_full + 8 * s, ph) || !ctx.wait(bar_in_ready + 8 * s, ph)) { live = false; break; }
         const uint32_t blob = smem + L::in + s * BXR_BLOB_MAX;
-        const uint32_t off = lds_u16(smem + L::segoff + s * kSegOffBytes + 2 * (seg + backward)) - backward;
-        d.wp = blob + BXR_WORDS_AT + 2 * off;
+        const uint32_t bounds = lds32_unaligned_pair(smem + L::segoff + s * kSegOffBytes + 2 * seg);
+        d.wf = blob + BXR_WORDS_AT + 2 * (bounds & 0xFFFFu);
+        d.wb = blob + BXR_WORDS_AT + 2 * (bounds >> 16) - 2;
         uint32_t a_tile = 0;
         if (MODE == kUmma) {
           const uint32_t hs = 2 * u + atom, so = hs % kOpN, pho = (hs / kOpN) & 1;
           if (!ctx.wait(bar_op_empty + 8 * so, pho ^ 1)) { live = false; break; }
           a_tile = smem + L::op + so * L::kOpStage + r * 128;
         }
+        const uint4 raw_f = lds128(blob + BXR_COUNT_BYTES + ((2 * q) * BXR_ROWS + r) * 16);
+        const uint4 raw_b = lds128(blob + BXR_COUNT_BYTES + ((2 * q + 1) * BXR_ROWS + r) * 16);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint4 raw = lds128(blob + BXR_COUNT_BYTES + ((q * 2 + j) * BXR_ROWS + r) * 16);
+        for (int k = 0; k < 2; ++k) {
+          uint4 w2[2];
+          decode8x2(d, k ? raw_f.z : raw_f.x, k ? raw_f.w : raw_f.y, k ? raw_b.z : raw_b.x, k ? raw_b.w : raw_b.y, w2[0], w2[1]);
 #pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const uint4 w = decode8(d, k ? raw.z : raw.x, k ? raw.w : raw.y);
-            const uint32_t col = c * BXR_COLS + q * BXR_PHASE_COLS + j * 16 + k * 8;
+          for (int dir = 0; dir < 2; ++dir) {
+            const uint4 w = w2[dir];
+            const uint32_t cin = (2 * q + dir) * BXR_STREAM_COLS + k * 8;  // column inside the chunk
+            const uint32_t col = c * BXR_COLS + cin;
             if (MODE == kUmma) {
-              const uint32_t cidx = (q & 1) * 4 + j * 2 + k;
+              const uint32_t cidx = (q & 1) * 4 + dir * 2 + k;
               sts128(a_tile + ((cidx ^ (r & 7)) << 4), w);
             } else if (MODE == kDense) {
               if (row < args.rows) {
@@ -259,7 +285,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
             } else {
               const float wf[8] = {bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y),
                                    bf16_lo(w.z), bf16_hi(w.z), bf16_lo(w.w), bf16_hi(w.w)};
-              const uint32_t xs = smem + L::xf32 + s * L::kXStage + (q * BXR_PHASE_COLS + j * 16 + k * 8) * 4;
+              const uint32_t xs = smem + L::xf32 + s * L::kXStage + cin * 4;
 #pragma unroll
               for (int m = 0; m < kGemvMaxM; ++m) {
                 if (m < NB) {  // NB carries the batch size for the GEMV instantiations
@@ -289,7 +315,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         if (lane == 0) mbar_arrive(bar_in_empty + 8 * s);
       }
       if (!live) break;
-      if (d.x != BXR_STATE_LOW) atomicOr(args.status, kStatusCheckpoint);
+      if (d.xf != BXR_STATE_LOW || d.xb != BXR_STATE_LOW) atomicOr(args.status, kStatusCheckpoint);
       if (MODE == kGemv) {
         // phases of a row are added in phase order, parts of a row block in part order
         const uint32_t red = smem + L::red;
@@ -400,13 +426,14 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         const uint32_t s = u % L::kIn, ph = (u / L::kIn) & 1;
         if (ctx.aborted() || !ctx.wait(bar_in_full + 8 * s, ph)) { live = false; break; }
         const uint32_t blob = smem + L::in + s * BXR_BLOB_MAX;
-        const uint2 cnt = lds64(blob + 8 * lane);
-        uint32_t pre[8];
+        const uint4 cnt = lds128(blob + 16 * lane);  // this lane's 16 segment counts
+        const uint32_t cw[4] = {cnt.x, cnt.y, cnt.z, cnt.w};
+        uint32_t pre[16];
         uint32_t run = 0;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < 16; ++e) {
           pre[e] = run;
-          run += ((e < 4 ? cnt.x : cnt.y) >> (8 * (e & 3))) & 0xFFu;
+          run += (cw[e >> 2] >> (8 * (e & 3))) & 0xFFu;
         }
         uint32_t incl = run;
 #pragma unroll
@@ -421,13 +448,16 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           live = false;
           break;
         }
-        uint4 o4;
-        o4.x = (excl + pre[0]) | (excl + pre[1]) << 16;
-        o4.y = (excl + pre[2]) | (excl + pre[3]) << 16;
-        o4.z = (excl + pre[4]) | (excl + pre[5]) << 16;
-        o4.w = (excl + pre[6]) | (excl + pre[7]) << 16;
-        sts128(smem + L::segoff + s * kSegOffBytes + 16 * lane, o4);
-        if (lane == 31) asm volatile("st.shared.u16 [%0], %1;" ::"r"(smem + L::segoff + s * kSegOffBytes + 512), "h"(uint16_t(total)) : "memory");
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint4 o4;
+          o4.x = (excl + pre[8 * h + 0]) | (excl + pre[8 * h + 1]) << 16;
+          o4.y = (excl + pre[8 * h + 2]) | (excl + pre[8 * h + 3]) << 16;
+          o4.z = (excl + pre[8 * h + 4]) | (excl + pre[8 * h + 5]) << 16;
+          o4.w = (excl + pre[8 * h + 6]) | (excl + pre[8 * h + 7]) << 16;
+          sts128(smem + L::segoff + s * kSegOffBytes + 32 * lane + 16 * h, o4);
+        }
+        if (lane == 31) asm volatile("st.shared.u16 [%0], %1;" ::"r"(smem + L::segoff + s * kSegOffBytes + 1024), "h"(uint16_t(total)) : "memory");
         if (MODE == kGemv) {
           // activations of this chunk as FP32: [m][128]
           const uint32_t xs = smem + L::xf32 + s * L::kXStage;
@@ -542,12 +572,47 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         if (prev == item.parts - 1) {  // every partial tile of this row block is in memory: add them in K order
           __threadfence();
           const uint32_t first = item.slot - item.part;
-          if (row < args.rows)
-            for (uint32_t m = 0; m < args.m; ++m) {
-              float t = __ldcg(args.partials + (size_t(first) * NB + m) * BXR_ROWS + r);
-              for (uint32_t p = 1; p < item.parts; ++p) t = __fadd_rn(t, __ldcg(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r));
-              args.y[size_t(m) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(t, b) : t);
+          // warp e takes batch rows e, e+4, ...; a lane takes 4 consecutive weight rows (one float4 per
+          // partial tile), eight batch rows at a time so that 8 x parts loads are in flight
+          const uint32_t r4 = lane * 4, row4 = item.row_block * BXR_ROWS + r4;
+          float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+          if (args.bias)
+            for (int i = 0; i < 4; ++i)
+              if (row4 + i < args.rows) bias4[i] = __bfloat162float(args.bias[row4 + i]);
+          for (uint32_t m0 = e; m0 < args.m; m0 += 32) {
+            float4 t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t m = m0 + 4 * j;
+              t[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first) * NB + m) * BXR_ROWS + r4))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+            for (uint32_t p = 1; p < item.parts; ++p) {
+              float4 v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t m = m0 + 4 * j;
+                v[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                t[j].x = __fadd_rn(t[j].x, v[j].x);
+                t[j].y = __fadd_rn(t[j].y, v[j].y);
+                t[j].z = __fadd_rn(t[j].z, v[j].z);
+                t[j].w = __fadd_rn(t[j].w, v[j].w);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t m = m0 + 4 * j;
+              if (m >= args.m) continue;
+              const float f[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
+              __nv_bfloat16* dst = args.y + size_t(m) * args.ldy + row4;
+              for (int i = 0; i < 4; ++i)
+                if (row4 + i < args.rows) dst[i] = __float2bfloat16_rn(args.bias ? __fadd_rn(f[i], bias4[i]) : f[i]);
+            }
+          }
           if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
         }
         named_barrier(1, 128);  // the verdict word may be rewritten

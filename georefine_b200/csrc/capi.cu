@@ -27,7 +27,8 @@ bool header_ok(const bxr_header* h) {
 BxrArgs view_of(const void* image, const bxr_header* h) {
   const auto* p = static_cast<const uint8_t*>(image);
   BxrArgs a{};
-  a.lut = reinterpret_cast<const uint64_t*>(p + h->lut_at);
+  a.lut = reinterpret_cast<const uint32_t*>(p + h->lut_at);
+  a.esc_slot = h->esc_slot;
   a.base = p + h->base_at;
   a.items = reinterpret_cast<const bxr_item*>(p + h->items_at);
   a.worker_items = reinterpret_cast<const uint32_t*>(p + h->worker_items_at);

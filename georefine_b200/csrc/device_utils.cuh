@@ -80,6 +80,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---- shared memory by address -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
 __device__ __forceinline__ uint2 lds64(uint32_t a) {
   uint2 v;
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
@@ -95,6 +100,8 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
   asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
   return v;
 }
+// Two consecutive 16-bit values at a 2-byte aligned address, as lo | hi << 16.
+__device__ __forceinline__ uint32_t lds32_unaligned_pair(uint32_t a) { return lds_u16(a) | (lds_u16(a + 2) << 16); }
 __device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }

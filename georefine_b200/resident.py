@@ -86,6 +86,16 @@ class ResidentWeight:
         image, _ = build_image(words, workers, force_raw=force_raw, source_sha256=source_sha256)
         return cls(image, device, max_m=max_m, verify=verify)
 
+    def clone(self):
+        """A second copy of the image in device memory (benchmarks rotate over copies to defeat the L2)."""
+        import copy
+
+        other = copy.copy(self)
+        other.image = self.image.clone()
+        other.status = self.status.clone()
+        other.workspace = self.workspace.clone()
+        return other
+
     # -- bookkeeping (the numerators of the roofline) ----------------------------------------------------
     @property
     def bytes(self) -> int:

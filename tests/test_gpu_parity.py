@@ -1,0 +1,219 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (needs a B200)."""
+import hashlib
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+FRAME_TAGS = ["special", "uniform13x17", "constant", "synthetic64x512", "synthetic48x320.r4c1", "conditional96x160"]
+REL_TOL = 1e-2  # BF16 output, FP32 accumulation: relative to the largest reference magnitude of the call
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from georefine_b200 import _native
+
+    _native.lib()  # the extension must load; nothing below has another path
+    return torch.device("cuda:0")
+
+
+def _u16(t):
+    return t.contiguous().view(torch.uint16).cpu().numpy()
+
+
+def _reference_product(words, x):
+    w = torch.from_numpy(words.view(np.int16)).view(torch.bfloat16).to(x.device).float()
+    return x.float() @ w.T
+
+
+# ---------------------------------------------------------------- unchanged BCTX streams
+@pytest.mark.parametrize("tag", FRAME_TAGS)
+@pytest.mark.parametrize("stride", [1, 7, 128, 1024])
+def test_indexed_decode_is_bit_exact(golden, oracle_coder, dev, tag, stride):
+    from georefine_b200.gpu import CudaContextTensor
+
+    frame = golden[tag + ".frame"].tobytes()
+    t = CudaContextTensor(frame, stride=stride, device=dev, fused=False)
+    expect = oracle_coder.decode(frame)
+    assert t.shape == expect.shape and t.source_sha256 == hashlib.sha256(expect.tobytes()).hexdigest()
+    assert np.array_equal(_u16(t.decode()), expect)
+    if t.mode != 1:
+        assert t.buffers["main_states"].numel() == (expect.size + stride - 1) // stride
+        assert t.resident_bytes >= sum(v.numel() * v.element_size() for v in t.buffers.values())
+
+
+@pytest.mark.parametrize("nr,nc", [(1, 1), (16, 4), (64, 16)])
+def test_indexed_decode_class_configurations_and_gather(orc, oracle_coder, dev, nr, nc):
+    from georefine_b200.gpu import CudaContextTensor
+
+    words = orc.synthetic_weight_words(96, 2048, 11)
+    frame = oracle_coder.encode(words, row_classes=nr, col_classes=nc)
+    t = CudaContextTensor(frame, stride=1024, device=dev, fused=False)
+    assert np.array_equal(_u16(t.decode()), words)
+    ids = torch.tensor([[5, 95, 0], [5, 17, 64]])
+    assert np.array_equal(_u16(t.gather_rows(ids)), words[ids.numpy()])
+    assert t.gather_rows(torch.empty(0, dtype=torch.int64)).shape == (0, 2048)
+    with pytest.raises(IndexError):
+        t.gather_rows(torch.tensor([96]))
+    # a stride that does not divide the row length falls back to a full decode + index
+    t2 = CudaContextTensor(frame, stride=1000, device=dev, fused=False)
+    assert np.array_equal(_u16(t2.gather_rows(ids)), words[ids.numpy()])
+
+
+def test_indexed_decode_reports_corruption_without_faulting(orc, oracle_coder, dev):
+    from georefine_b200 import codec
+    from georefine_b200.gpu import CudaContextTensor
+
+    words = orc.synthetic_weight_words(64, 1024, 12)
+    t = CudaContextTensor(oracle_coder.encode(words), stride=256, device=dev, fused=False)
+    good = t.buffers["main_states"].clone()
+    t.buffers["main_states"].view(torch.int32)[3] += 0x55   # host-injected: a wrong restart state
+    with pytest.raises(codec.CodecError):
+        t.decode()
+    assert int(t.error.item()) != 0
+    t.buffers["main_states"].copy_(good)
+    t.buffers["main_stream"][100:140] = 255      # host-injected: damaged bytes in the middle of the stream
+    with pytest.raises(codec.CodecError):
+        t.decode()
+    t.decode(check=False)                        # still returns, status says discard
+    assert int(t.error.item()) != 0
+
+
+# ---------------------------------------------------------------- resident image: decode twin
+@pytest.mark.parametrize("shape,seed", [((128, 128), 0), ((256, 512), 1), ((300, 200), 2), ((64, 67), 3),
+                                        ((1000, 1536), 4), ((4096, 4096), 0)])
+def test_resident_decode_is_bit_exact(orc, oracle_coder, dev, shape, seed):
+    from georefine_b200.gpu import CudaContextTensor
+
+    words = orc.synthetic_weight_words(*shape, seed)
+    frame = oracle_coder.encode(words)
+    t = CudaContextTensor(frame, device=dev)
+    assert np.array_equal(oracle_coder.decode(frame), words)
+    assert np.array_equal(_u16(t.resident.decode()), words)      # image walked by the fused kernels' decoder
+    assert np.array_equal(_u16(t.decode()), words)               # unchanged streams
+    assert t.resident.check_status() == 0
+
+
+def test_resident_decode_special_words(dev):
+    from georefine_b200.resident import ResidentWeight
+
+    special = np.resize(np.array([0, 0x8000, 0x7F80, 0xFF80, 0x7FC1, 0xFFE5, 1, 0x8001], dtype=np.uint16), (64, 67))
+    r = ResidentWeight.from_words(special, dev)
+    assert np.array_equal(_u16(r.decode()), special)
+    every = np.arange(65536, dtype=np.uint16).reshape(256, 256)   # every BF16 pattern once
+    r = ResidentWeight.from_words(every, dev)
+    if r.mode == 0:
+        assert np.array_equal(_u16(r.decode()), every)
+
+
+def test_resident_decode_flags_a_corrupt_image(orc, dev):
+    from georefine_b200.resident import ResidentWeight, build_image
+
+    words = orc.synthetic_weight_words(256, 512, 21)
+    image, h = build_image(words, 148)
+    image[h.states_at + 8] ^= 0x40                                # host-injected: one stream starts from a wrong state
+    r = ResidentWeight(image, dev, verify=False)
+    with pytest.raises(ValueError):
+        r.decode()
+    assert r.check_status() & 8
+
+
+# ---------------------------------------------------------------- fused linears
+SHAPES = [((128, 128), 0), ((256, 512), 1), ((300, 200), 2), ((1024, 4096), 3), ((4096, 4096), 0), ((2048, 5120), 1)]
+
+
+@pytest.mark.parametrize("shape,seed", SHAPES)
+def test_gemm_matches_reference_and_rows_do_not_depend_on_batch(orc, dev, shape, seed):
+    from georefine_b200.resident import ResidentWeight
+
+    words = orc.synthetic_weight_words(*shape, seed)
+    r = ResidentWeight.from_words(words, dev, max_m=256)
+    n, k = shape
+    g = torch.Generator(device="cpu").manual_seed(100 + seed)
+    xfull = torch.randn(200, k, generator=g).to(torch.bfloat16).to(dev)
+    rows = {}
+    for m in (1, 5, 16, 17, 64, 128, 200):
+        x = xfull[:m].contiguous()
+        y = torch.full((m, n), float("nan"), device=dev, dtype=torch.bfloat16)
+        r.gemm(x, y)
+        assert r.check_status() == 0
+        ref = _reference_product(words, x)
+        assert not torch.isnan(y.float()).any()
+        assert ((y.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
+        rows[m] = _u16(y)
+    for m, got in rows.items():                                    # bitwise identical rows across M
+        assert np.array_equal(got, rows[200][:m]), f"rows differ between M={m} and M=200"
+
+
+@pytest.mark.parametrize("shape,seed", SHAPES)
+def test_gemv_matches_reference_and_is_m_invariant(orc, dev, shape, seed):
+    from georefine_b200.resident import ResidentWeight
+
+    words = orc.synthetic_weight_words(*shape, seed)
+    r = ResidentWeight.from_words(words, dev)
+    n, k = shape
+    g = torch.Generator(device="cpu").manual_seed(200 + seed)
+    xfull = torch.randn(8, k, generator=g).to(torch.bfloat16).to(dev)
+    w64 = torch.from_numpy(words.view(np.int16)).view(torch.bfloat16).double()
+    exact = (xfull.cpu().double() @ w64.T)
+    y8 = None
+    for m in range(8, 0, -1):
+        y = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
+        r.gemv(xfull[:m].contiguous(), y)
+        assert r.check_status() == 0
+        if y8 is None:
+            y8 = _u16(y)
+        assert np.array_equal(_u16(y), y8[:m])
+        # at most one BF16 ulp away from the correctly rounded float64 result (relative to the call's scale)
+        got = y.cpu().double()
+        ulp = exact[:m].abs().clamp_min(1e-30).log2().floor().sub(7).exp2()
+        assert ((got - exact[:m]).abs() <= 1.01 * ulp + 2e-3 * exact[:m].abs().max()).all()
+    with pytest.raises(RuntimeError):
+        r.gemv(torch.zeros(9, k, device=dev, dtype=torch.bfloat16), torch.empty(9, n, device=dev, dtype=torch.bfloat16))
+
+
+def test_bias_strided_input_and_module_contract(orc, oracle_coder, dev):
+    from georefine_b200.gpu import CudaContextTensor
+    from georefine_b200.serving import BctxLinear
+
+    words = orc.synthetic_weight_words(384, 256, 31)
+    t = CudaContextTensor(oracle_coder.encode(words), device=dev)
+    bias = torch.nn.Parameter(torch.randn(384, device=dev).to(torch.bfloat16), requires_grad=False)
+    layer = BctxLinear(t, bias)
+    assert (layer.out_features, layer.in_features) == (384, 256) and "weight" not in layer.state_dict()
+    x = torch.randn(4, 9, 512, device=dev).to(torch.bfloat16)[..., ::2]      # strided batched input
+    y = layer(x)
+    assert y.shape == (4, 9, 384) and layer.forward_calls == 1 and layer.weight_materializations == 0
+    ref = _reference_product(words, x.reshape(-1, 256)) + bias.float()
+    assert ((y.reshape(-1, 384).float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
+    assert np.array_equal(_u16(layer.weight), words) and layer.weight_materializations == 1
+    yv = torch.empty(3, 384, device=dev, dtype=torch.bfloat16)
+    t.resident.gemv(x.reshape(-1, 256)[:3].contiguous(), yv, bias)
+    assert ((yv.float() - ref[:3]).abs().max() / ref.abs().max()).item() <= REL_TOL
+    # descriptor protocol: preallocated output, nothing returned
+    out = torch.empty(36, 384, device=dev, dtype=torch.bfloat16)
+    assert t(x.reshape(-1, 256).contiguous(), out) is None
+    assert t.resident.kind == "bctx" and t.resident.coded_bytes < 2 * words.size + 40000
+
+
+def test_linearity_round_trip_at_full_size(orc, dev):
+    """Size-independent property at a benchmark shape: W(x1 + x2) == W x1 + W x2 within rounding, and the
+    decode twin reproduces the source digest."""
+    from georefine_b200.resident import ResidentWeight
+
+    words = orc.synthetic_weight_words(7168, 5120, 1)
+    r = ResidentWeight.from_words(words, dev, verify=False)
+    assert hashlib.sha256(_u16(r.decode()).tobytes()).digest() == bytes(r.header.source_sha256)
+    x = torch.randn(2, 5120, device=dev).to(torch.bfloat16)
+    xs = (x[0].float() + x[1].float()).to(torch.bfloat16)[None]
+    y = torch.empty(2, 7168, device=dev, dtype=torch.bfloat16)
+    ys = torch.empty(1, 7168, device=dev, dtype=torch.bfloat16)
+    r.gemm(x, y)
+    r.gemm(xs, ys)
+    ref = _reference_product(words, xs)
+    assert ((ys.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
+    assert ((y[0].float() + y[1].float() - ys[0].float()).abs().max() / ref.abs().max()).item() <= 3 * REL_TOL
