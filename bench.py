@@ -1,0 +1,371 @@
+"""Benchmark of the fused decode-GEMM path on the hybrid-decoder linear shapes (hidden 5120).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = the four linears of a decoder layer (QKV 5120->7168, O 5120->5120, gate|up 5120->2x17408,
+down 17408->5120), each at batch M = 1, 64 and 128: twelve fused decode-GEMM launches over synthetic
+weights N(0, 0.02) x LogNormal(0, 0.25) per row (seed 1) held in HBM as compressed resident images.
+The coded working set (~440 MB) is larger than the L2, so no flush is needed between iterations.
+
+metric  fused decode-GEMM effective BF16 weight bandwidth: dense BF16 bytes of the weights the step
+        multiplies by (2*N*K per launch) divided by the step time, GB/s, whole job.
+value   inputs resident in HBM, CUDA events, max over ranks.
+e2e     the same step through ResidentWeight.linear with activations in pinned host memory copied in and
+        the down-projection outputs copied back every step.
+With --gpus N (torchrun) the layer is tensor-parallel: QKV and gate|up split by weight rows (no traffic), O
+and down by weight columns followed by an NCCL all-reduce of the BF16 partials; total work is fixed
+(strong scaling).  --impl reference times the reference's own CPU decode + matmul on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "fused_decode_gemm_effective_bf16_weight_bandwidth"
+UNIT = "GB/s"
+HIDDEN, FFN = 5120, 17408
+# name, N (weight rows), K, parallel kind, members of the fused group
+LINEARS = [("qkv", 7168, HIDDEN, "col", [5120, 1024, 1024]), ("o", HIDDEN, HIDDEN, "row", None),
+           ("gate_up", 2 * FFN, HIDDEN, "col", [FFN, FFN]), ("down", HIDDEN, FFN, "row", None)]
+BATCHES = (1, 64, 128)
+SEED = 1
+# dram__bytes_read+write over algorithmic bytes of one launch, from the ncu capture summarised in
+# profiles/bxr_kernel_gemm_m1_down_5120x17408.md (121.7 MB read + 3.5 MB written for 121.9 MB algorithmic)
+DRAM_TRAFFIC_RATIO = 1.03
+FALLBACK_HBM_GBS = 6650.0
+
+
+def synthetic_words(generator, rows, cols):
+    """BF16 bit patterns of N(0, 0.02) weights with a LogNormal(0, 0.25) scale per row."""
+    import torch
+
+    w = torch.randn(rows, cols, generator=generator) * 0.02
+    w = w * torch.exp(0.25 * torch.randn(rows, 1, generator=generator))
+    return w.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+def all_weights():
+    import torch
+
+    g = torch.Generator().manual_seed(SEED)
+    return {name: synthetic_words(g, n, k) for name, n, k, _, _ in LINEARS}
+
+
+def measured_hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples taken while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"], "samples": 0}
+        busy = [v for v in sm if v >= 0.5 * max(sm)] or sm
+        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_reference_run(sample_rows, steps, warmup, threads):
+    """The reference's CPU path on slabs of the benchmark weights: decode every frame, then F.linear at every
+    batch size.  Returns (value in GB/s, description).  Uses oracle/_ref (the reference's coder compiled from
+    its sources) when it was built, else the plain-C oracle port."""
+    import torch
+    import torch.nn.functional as F
+
+    from oracle import bcx_oracle as orc
+
+    kind = "reference" if orc.ref_available() else "port"
+    coder = orc.Coder("ref" if kind == "reference" else "oracle")
+    g = torch.Generator().manual_seed(SEED)
+    slab = 128
+    frames = []
+    for name, n, k, _, _ in LINEARS:
+        rows = min(n, sample_rows)
+        words = synthetic_words(g, rows, k)
+        for lo in range(0, rows, slab):
+            frames.append((k, coder.encode(np.ascontiguousarray(words[lo:lo + slab]))))
+    xs = {(m, k): torch.randn(m, k, generator=g).to(torch.bfloat16) for m in BATCHES for k in (HIDDEN, FFN)}
+    dense_bytes = sum(2 * min(n, sample_rows) * k for _, n, k, _, _ in LINEARS) * len(BATCHES)
+    torch.set_num_threads(1)
+
+    def one(job):
+        k, frame = job
+        total = 0.0
+        for m in BATCHES:
+            w = torch.from_numpy(coder.decode(frame).view(np.int16)).view(torch.bfloat16)
+            total += float(F.linear(xs[(m, k)], w).float().abs().sum())
+        return total
+
+    def step():
+        with ThreadPoolExecutor(threads) as pool:
+            return sum(pool.map(one, frames))
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    sample = f"first {sample_rows} rows of each of the four weights as {slab}-row BCTX frames, decode + F.linear at M=1,64,128"
+    return dense_bytes / dt / 1e9, dt, {"kind": kind, "cores": threads, "sample": sample}
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+class Layer:
+    """The four linears of one decoder layer on this rank, as resident images (tensor-parallel when world > 1)."""
+
+    def __init__(self, rank, world, device):
+        import torch
+
+        from georefine_b200 import tp
+        from georefine_b200.resident import ResidentWeight
+
+        self.rank, self.world, self.device = rank, world, device
+        weights = all_weights()
+        self.entries = []
+        for name, n, k, kind, members in LINEARS:
+            w = weights.pop(name)
+            if kind == "col":
+                local = np.concatenate([w[lo:hi] for lo, hi in tp.column_parallel_rows(members, rank, world)], axis=0)
+                k0, k1 = 0, k
+            else:
+                k0, k1 = tp.row_range(k, rank, world, tp.CHUNK)
+                local = w[:, k0:k1]
+            res = ResidentWeight.from_words(np.ascontiguousarray(local), device, max_m=max(BATCHES), verify=False)
+            self.entries.append({"name": name, "kind": kind, "n": n, "k": k, "k0": k0, "k1": k1, "res": res,
+                                 "y": {m: torch.empty(m, res.N, device=device, dtype=torch.bfloat16) for m in BATCHES}})
+            del w, local
+        g = torch.Generator().manual_seed(SEED + 1)
+        self.x_host = {(m, k): torch.randn(m, k, generator=g).to(torch.bfloat16).pin_memory() for m in BATCHES for k in (HIDDEN, FFN)}
+        self.x = {key: v.to(device) for key, v in self.x_host.items()}
+        self.y_host = {m: torch.empty(m, HIDDEN, dtype=torch.bfloat16).pin_memory() for m in BATCHES}
+        self.launches_per_step = len(LINEARS) * len(BATCHES)
+
+    def dense_bytes_per_step(self):
+        return sum(2 * n * k for _, n, k, _, _ in LINEARS) * len(BATCHES)
+
+    def algorithmic_bytes(self, e, m):
+        """What one launch must move: the coded image once, the activations in, the outputs out."""
+        return e["res"].coded_bytes + 2 * m * (e["k1"] - e["k0"]) + 2 * m * e["res"].N
+
+    def call(self, e, m, x):
+        import torch.distributed as dist
+
+        y = e["y"][m]
+        e["res"].gemm(x[:, e["k0"]:e["k1"]], y)
+        if e["kind"] == "row" and self.world > 1:
+            dist.all_reduce(y)
+        return y
+
+    def step(self):
+        for m in BATCHES:
+            for e in self.entries:
+                self.call(e, m, self.x[(m, e["k"])])
+
+    def step_e2e(self):
+        """Host buffers in, host buffers out, through the public linear() call."""
+        import torch
+        import torch.distributed as dist
+
+        for m in BATCHES:
+            xd = {k: self.x_host[(m, k)].to(self.device, non_blocking=True) for k in (HIDDEN, FFN)}
+            for e in self.entries:
+                y = e["res"].linear(xd[e["k"]][:, e["k0"]:e["k1"]])
+                if e["kind"] == "row" and self.world > 1:
+                    dist.all_reduce(y)
+            self.y_host[m].copy_(y, non_blocking=True)   # the down projection's output
+        torch.cuda.current_stream().synchronize()
+
+    def status(self):
+        return sum(e["res"].check_status() for e in self.entries)
+
+
+def timed(fn, steps, warmup, world):
+    import torch
+    import torch.distributed as dist
+
+    for _ in range(warmup):
+        fn()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def kernel_times(layer, steps):
+    """Per-launch durations of the fused kernel (CUDA events around every launch on the launching stream)."""
+    import torch
+
+    per = {}
+    for _ in range(steps):
+        for m in BATCHES:
+            for e in layer.entries:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                x = layer.x[(m, e["k"])][:, e["k0"]:e["k1"]]
+                a.record()
+                e["res"].gemm(x, e["y"][m])
+                b.record()
+                per.setdefault((e["name"], m), []).append((a, b))
+    torch.cuda.synchronize()
+    return {key: float(np.mean([a.elapsed_time(b) for a, b in evs])) for key, evs in per.items()}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fused path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    layer = Layer(rank, world, device)
+
+    with ClockSampler(local) as clocks:
+        ms = timed(layer.step, args.steps, args.warmup, world)
+    ms_e2e = timed(layer.step_e2e, args.steps, args.warmup, world)
+    ktimes = kernel_times(layer, max(2, min(args.steps, 10)))
+    status = layer.status()
+
+    dense = layer.dense_bytes_per_step()
+    peak, peak_kind = measured_hbm_peak()
+    algo = sum(layer.algorithmic_bytes(e, m) for m in BATCHES for e in layer.entries)
+    ksum = sum(ktimes.values())
+    achieved = algo / (ksum * 1e-3) / 1e9
+    per_m = {}
+    for m in BATCHES:
+        t = sum(ktimes[(e["name"], m)] for e in layer.entries)
+        coded = sum(layer.algorithmic_bytes(e, m) for e in layer.entries)
+        per_m[str(m)] = {"kernel_ms": round(t, 4), "effective_bf16_GBps": round(dense / len(BATCHES) / world / t / 1e6, 1),
+                         "coded_GBps": round(coded / t / 1e6, 1), "frac_of_hbm_peak": round(coded / t / 1e6 / peak, 4),
+                         "linears_only_tok_s_64_layers": round(m / (64 * t * 1e-3), 1)}
+    top = max(ktimes, key=ktimes.get)
+    top_e = next(e for e in layer.entries if e["name"] == top[0])
+    top_bytes = layer.algorithmic_bytes(top_e, top[1])
+    line = {
+        "metric": METRIC, "value": round(dense / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "hybrid-decoder linears hidden=5120 (QKV 7168x5120, O 5120x5120, gate|up 34816x5120, down 5120x17408), "
+                               "seed 1, fused decode-GEMM at M=1,64,128", "parallelism": f"tp{world}",
+                   "l2": "coded working set ~440 MB exceeds the 126 MB L2; no flush between iterations",
+                   "resident_format": "BXR1", "status_word": status},
+        "e2e": {"value": round(dense / (ms_e2e * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms_e2e, 4),
+                "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES)},
+        "gpu_launches": layer.launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO), "peak_source": peak_kind,
+                     "kernel": "bxr_kernel<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
+                     "top_launch": {"linear": top[0], "m": top[1], "ms": round(ktimes[top], 4), "algorithmic_bytes": top_bytes,
+                                    "GBps": round(top_bytes / ktimes[top] / 1e6, 1)}},
+        "per_m": per_m, "clocks": clocks.summary(),
+    }
+    if rank == 0 and world == 1:
+        value, dt, info = cpu_reference_run(sample_rows=2048, steps=1, warmup=0, threads=os.cpu_count() or 1)
+        line["cpu_baseline"] = {"value": round(value, 4), "unit": UNIT, **info, "seconds": round(dt, 2)}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    value, dt, info = cpu_reference_run(sample_rows=2048, steps=args.steps, warmup=min(args.warmup, 1), threads=threads)
+    line = {"impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "hybrid-decoder linears hidden=5120, seed 1, CPU decode + F.linear at M=1,64,128 on a bounded sample"},
+            "cpu_baseline": {"value": round(value, 4), "unit": UNIT, **info},
+            "e2e": {"value": round(value, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
