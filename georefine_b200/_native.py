@@ -23,6 +23,7 @@ EXPORTS = (
     "bcx_encode", "bcx_frequencies", "bcx_decode", "bcx_decode_compact", "bcx_free", "bcx_pack6", "bcx_unpack6",
     "bcx_checkpoint", "grb_bctx_build_lookup", "grb_bctx_decode_words", "bxr_build", "bxr_free", "bxr_decode_host",
     "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_kernel_attributes",
+    "grb_static_scratch_bytes", "grb_bxr_gemv_static",
 )
 
 
@@ -76,8 +77,12 @@ def _declare(lib):
     lib.grb_bxr_gemm.argtypes = linear
     lib.grb_bxr_gemv.argtypes = linear
     lib.grb_kernel_attributes.argtypes = [ci, ctypes.POINTER(ci * 5)]
+    lib.grb_static_scratch_bytes.argtypes = []
+    lib.grb_static_scratch_bytes.restype = u64
+    lib.grb_bxr_gemv_static.argtypes = [VOIDP, ctypes.POINTER(BxrHeader), VOIDP, ctypes.c_int64, u32, VOIDP, ctypes.c_int64,
+                                        VOIDP, VOIDP, VOIDP]
     for name in EXPORTS:
-        if name not in ("bcx_free", "bxr_free", "grb_bxr_workspace_bytes"):
+        if name not in ("bcx_free", "bxr_free", "grb_bxr_workspace_bytes", "grb_static_scratch_bytes"):
             getattr(lib, name).restype = ci
 
 

@@ -231,6 +231,48 @@ int grb_bxr_gemv(const void* image, const bxr_header* h, const void* x, int64_t 
   }
 }
 
+// ---- allocation-free variant ----------------------------------------------------------------------
+// Scratch for grb_bxr_gemv_static: one array per GPU that loads this library, held until the process exits.
+// In host code the name below is only a handle; the device address comes from cudaGetSymbolAddress.
+constexpr uint64_t kStaticScratchBytes = 4ull << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+uint64_t grb_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+// Device address of the array on the current device, looked up once per device.
+static int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* address[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (dev < 0 || dev >= 64) return GRB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!address[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess) return cuda_status(e);
+    if (!p) return GRB_ERR_UNSUPPORTED;
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return GRB_OK;
+}
+
+int grb_bxr_gemv_static(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
+                        const void* bias, uint32_t* status, void* cuda_stream) {
+  if (!header_ok(h)) return GRB_ERR_ARGUMENT;
+  const uint64_t need = counter_bytes(h) + uint64_t(h->partial_slots) * kGemvMaxM * BXR_ROWS * 4;
+  if (need > kStaticScratchBytes) return GRB_ERR_STATIC_LIMIT;
+  void* scratch = nullptr;
+  int st = static_scratch_address(&scratch);
+  if (st) return st;
+  // The array keeps whatever the previous call left: the per-row-block counters must start at zero.
+  const cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes(h), static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return cuda_status(e);
+  return grb_bxr_gemv(image, h, x, ldx, m, y, ldy, bias, scratch, kStaticScratchBytes, status, cuda_stream);
+}
+
 int grb_kernel_attributes(int which, int out[5]) {
   if (!out) return GRB_ERR_ARGUMENT;
   cudaFuncAttributes fa{};

@@ -87,6 +87,7 @@ int grb_bctx_build_lookup(const uint32_t* freq, uint32_t nctx, uint32_t vocab, u
 #define GRB_ERR_ARGUMENT 1      /* null pointer, bad size, misaligned buffer */
 #define GRB_ERR_UNSUPPORTED 2   /* e.g. batch larger than the entry point handles, raw-mode image */
 #define GRB_ERR_WORKSPACE 3     /* workspace too small */
+#define GRB_ERR_STATIC_LIMIT 4  /* the image needs more scratch than the built-in array of grb_bxr_gemv_static */
 #define GRB_ERR_CUDA 100        /* + cudaError_t of the failing runtime call */
 
 #define GRB_STATUS_BAD_SYMBOL 1u
@@ -162,6 +163,30 @@ int grb_bxr_gemm(const void* device_image, const bxr_header* header, const void*
 int grb_bxr_gemv(const void* device_image, const bxr_header* header, const void* x, int64_t ldx, uint32_t m, void* y,
                  int64_t ldy, const void* bias, void* workspace, uint64_t workspace_bytes, uint32_t* status,
                  void* cuda_stream);
+
+/* grb_bxr_gemv without caller-provided scratch.  This entry point has no counterpart in the reference.
+ *
+ * It is for callers that are not in a position to allocate device memory at all: a plugin loaded into a
+ * serving process whose host has already handed every free byte of HBM to its own pool (KV cache, activations)
+ * and offers the plugin no allocator, or code that runs where a call into the driver's allocator is forbidden
+ * or may block (inside a latency-critical decode loop, while another thread holds the device for a capture).
+ * Such a caller passes only inputs and outputs; the FP32 partial sums and the per-row-block counters of the
+ * GEMV live in a fixed array that is part of the library image itself (grb_static_scratch_bytes() = 4 MiB per
+ * GPU that loads the library, held until the process exits).  The call makes no cudaMalloc, cudaFree or other
+ * allocating call.
+ *
+ *  - Limit: images whose GEMV scratch (one counter per 128-row block plus 4 KiB per shared partial tile)
+ *    exceeds the array are refused with GRB_ERR_STATIC_LIMIT and nothing is launched.  A 34816 x 5120 weight
+ *    built for 148 workers needs about 1.7 MiB.
+ *  - First use: the first call on each device looks up the array's device address (with that device current)
+ *    and keeps it; make that first call outside any stream capture.
+ *  - Sharing: every call on a device uses the same array.  The counters are cleared on the given stream at
+ *    the start of each call, so a call does not depend on what the previous one left behind, but two calls
+ *    that can overlap on the GPU (different streams, no dependency) race on it and must not be issued.
+ *  - Results are bitwise those of grb_bxr_gemv (same kernel, same reduction order); m <= 8. */
+uint64_t grb_static_scratch_bytes(void);
+int grb_bxr_gemv_static(const void* device_image, const bxr_header* header, const void* x, int64_t ldx, uint32_t m,
+                        void* y, int64_t ldy, const void* bias, uint32_t* status, void* cuda_stream);
 
 /* Registers, spills and shared memory of the compiled kernels, for tuning records (the reference reads the
  * same from its card in bi_kernel_attrs, gs/bi_csrc/bi_gemm.cuh:1104-1121).  which: 0 BCTX decode, 1 BXR
