@@ -5,6 +5,7 @@ There is no fallback: if the library is missing and cannot be built, importing a
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -87,7 +88,8 @@ def _declare(lib):
 
 
 def library_path() -> Path:
-    return _build.OUT
+    override = os.environ.get("GEOREFINE_B200_LIBRARY")
+    return Path(override) if override else _build.OUT
 
 
 def lib():
@@ -95,8 +97,9 @@ def lib():
     global _LIB
     with _LOCK:
         if _LIB is None:
-            path = _build.OUT
-            if _build.needs_build():
+            override = os.environ.get("GEOREFINE_B200_LIBRARY")
+            path = Path(override) if override else _build.OUT
+            if not override and _build.needs_build():
                 try:
                     path = _build.build()
                 except RuntimeError:

@@ -303,7 +303,7 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
       }
       for (uint32_t s = 0; s < 256; ++s)
         for (uint32_t slot = cum[s]; slot < cum[s] + freq[s]; ++slot)
-          lut[slot] = freq[s] | (s & 15) << 12 | (slot - cum[s]) << 16 | (s >> 4) << 28;
+          lut[slot] = (s & 15) | (slot - cum[s]) << 4 | (s >> 4) << 16 | freq[s] << 20;
 
       std::atomic<bool> overflow{false};
       parallel_for(nitems, threads, [&](uint32_t i) {
@@ -478,9 +478,9 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
           for (uint32_t t = 0; t < BXR_STEPS; ++t) {
             const uint32_t slot = s & (BXR_PROB_TOTAL - 1);
             const uint32_t rec = lut[slot];
-            s = (rec & BXR_LUT_FREQ_MASK) * (s >> BXR_PROB_BITS) + ((rec >> 16) & BXR_LUT_FREQ_MASK);
+            s = BXR_REC_FREQ(rec) * (s >> BXR_PROB_BITS) + BXR_REC_BIAS(rec);
             refill();
-            const uint32_t n0 = (rec >> 12) & 15, n1 = rec >> 28;
+            const uint32_t n0 = BXR_REC_N0(rec), n1 = BXR_REC_N1(rec);
             uint32_t e0 = n0 + b, e1 = n1 + b;
             if (slot >= h.esc_slot) {
               if (n0 == BXR_ESCAPE) { e0 = s & 0xFF; s >>= 8; refill(); }

@@ -12,7 +12,7 @@
 //               exponent follows in the same stream at probability 1/256)
 //   symbol   = n(col 2t) | n(col 2t+1) << 4                one rANS step decodes two weights
 //   rANS     : 32-bit state, lower bound 2^16, 16-bit words, 12-bit probabilities, one static table
-//              per tensor stored as 4096 32-bit slot records {freq, n0, bias, n1}; symbols that contain
+//              per tensor stored as 4096 32-bit slot records {n0, bias, n1, freq}; symbols that contain
 //              an escape own the highest slots, so "slot >= esc_slot" is the whole escape test
 //
 // Geometry.  Rows are grouped in row blocks of 128 (one UMMA M tile), columns in chunks of 128.  Inside a
@@ -58,10 +58,14 @@
 #define BXR_MODE_RAW 1 /* chunk blob = the 128x128 BF16 tile itself, already in UMMA operand order */
 #define BXR_RAW_TILE_BYTES 32768
 
-/* Slot record of the pair table, 32 bits: freq[0,12) | n0[12,16) | bias[16,28) | n1[28,32), so that
- * (record >> 5) & 0x07800780 is the pair of relative exponents in BF16 position.  freq <= 4095. */
-#define BXR_LUT_FREQ_MASK 0xFFFu
-#define BXR_LUT_EXP_MASK 0x07800780u
+/* Slot record of the pair table, 32 bits: n0[0,4) | bias[4,16) | n1[16,20) | freq[20,32).  freq <= 4095.
+ * (record & 0x000F000F) * 128 is the pair of relative exponents in packed-BF16 position, freq is the top
+ * field (one shift or one multiply-high), bias = (record << 16) >> 20. */
+#define BXR_LUT_NIBBLES 0x000F000Fu
+#define BXR_REC_FREQ(rec) ((rec) >> 20)
+#define BXR_REC_BIAS(rec) (((rec) >> 4) & 0xFFFu)
+#define BXR_REC_N0(rec) ((rec) & 15u)
+#define BXR_REC_N1(rec) (((rec) >> 16) & 15u)
 
 typedef struct bxr_item {
   uint32_t row_block;  /* which 128-row block */

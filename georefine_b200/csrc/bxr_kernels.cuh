@@ -32,13 +32,19 @@ constexpr int kThreadsSimt = 18 * 32;
 constexpr uint32_t kLutBytes = 4 * BXR_PROB_TOTAL;
 constexpr uint32_t kSegOffBytes = 1040;  // u16[513] rounded up
 constexpr uint32_t kAtomBytes = 16384;  // 128 rows x 64 BF16
-constexpr uint32_t kInGuard = 128;      // a corrupt stream may read up to 48 bytes past its slot
+constexpr uint32_t kInGuard = 128;      // a corrupt stream may read up to 50 bytes past its slot
 constexpr int kGemvMaxM = 8;
+
+// Powers of two passed as kernel parameters so the compiler cannot turn the multiplications back into shifts.
+struct BxrPowers {
+  uint32_t p2, p7, p12, p16, p20, m14;  // 4, 128, 2^12, 2^16, 2^20, -16384
+};
 
 struct BxrArgs {
   // image
   const uint32_t* lut;
   uint32_t esc_slot;
+  BxrPowers k;
   const uint8_t* base;
   const bxr_item* items;
   const uint32_t* worker_items;
@@ -72,7 +78,7 @@ struct BxrSmem {
   static constexpr uint32_t xf32 = segoff + kIn * kSegOffBytes;
   static constexpr uint32_t bars = (xf32 + kIn * kXStage + 15) & ~15u;
   // barrier order: in_full, in_ready, in_empty [kIn each]; op_full, op_empty [kOp each]; acc_full, acc_empty [2 each]
-  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4;
+  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4 + 1;  // + the table's arrival barrier (last)
   static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, reduce flag, spare
   static constexpr uint32_t red = misc + 16;          // GEMV: FP32 [4 phases][128 rows][8]
   static constexpr uint32_t total = red + (MODE == kGemv ? 4 * 128 * kGemvMaxM * 4 : 0);
@@ -107,39 +113,58 @@ struct RoleCtx {
 // packed-BF16 position (bits 7..14 and 23..30).
 struct LaneDecoder {
   uint32_t xf, xb;   // rANS states
-  uint32_t wf, wb;   // shared addresses of the next 16-bit word of each stream
+  uint32_t wf, wb;   // shared addresses of the NEXT 16-bit word of each stream
+  uint32_t nf, nb;   // that word, already loaded: a refill never waits for shared memory
   uint32_t lut;      // shared address of the slot records
   uint32_t base2;    // row base replicated into both exponent fields
-  uint32_t esc_slot;
+  uint32_t esc_addr; // shared address of the first slot record whose symbol contains an escape
+  BxrPowers k;
 
+  __device__ __forceinline__ void start_chunk(uint32_t first_f, uint32_t first_b) {
+    wf = first_f;
+    wb = first_b;
+    nf = lds_u16(wf);
+    nb = lds_u16(wb);
+  }
+  // (x << 16) | word as one multiply-add; the following word is fetched right away for the next refill.
+  __device__ __forceinline__ void refill_f() {
+    if (xf < BXR_STATE_LOW) { xf = xf * k.p16 + nf; wf += 2; nf = lds_u16(wf); }
+  }
+  __device__ __forceinline__ void refill_b() {
+    if (xb < BXR_STATE_LOW) { xb = xb * k.p16 + nb; wb -= 2; nb = lds_u16(wb); }
+  }
   // rare: an exponent outside the row window follows in the stream as a raw byte
-  __device__ __forceinline__ uint32_t escape(uint32_t rec, uint32_t& x, uint32_t& wp, int wstep) const {
+  template <bool FWD>
+  __device__ __forceinline__ uint32_t escape(uint32_t rec) {
+    uint32_t& x = FWD ? xf : xb;
     const uint32_t b = (base2 >> 7) & 0xFFu;
-    uint32_t e0 = ((rec >> 12) & 15u) + b, e1 = (rec >> 28) + b;
-    if (((rec >> 12) & 15u) == BXR_ESCAPE) {
+    uint32_t e0 = BXR_REC_N0(rec) + b, e1 = BXR_REC_N1(rec) + b;
+    if (BXR_REC_N0(rec) == BXR_ESCAPE) {
       e0 = x & 0xFFu;
       x >>= 8;
-      if (x < BXR_STATE_LOW) { x = (x << 16) | lds_u16(wp); wp += wstep; }
+      if (FWD) refill_f(); else refill_b();
     }
-    if ((rec >> 28) == BXR_ESCAPE) {
+    if (BXR_REC_N1(rec) == BXR_ESCAPE) {
       e1 = x & 0xFFu;
       x >>= 8;
-      if (x < BXR_STATE_LOW) { x = (x << 16) | lds_u16(wp); wp += wstep; }
+      if (FWD) refill_f(); else refill_b();
     }
     return (e0 << 7) | (e1 << 23);
   }
+  // One step of both streams.  The record layout keeps the integer-pipe work low: the frequency is the top
+  // field (one shift), the nibble pair becomes the exponent pair with one mask and one multiply-add.
   __device__ __forceinline__ void step(uint32_t& ef, uint32_t& eb) {
-    const uint32_t sf = xf & (BXR_PROB_TOTAL - 1), sb = xb & (BXR_PROB_TOTAL - 1);
-    const uint32_t rf = lds32(lut + (sf << 2)), rb = lds32(lut + (sb << 2));
-    xf = (rf & BXR_LUT_FREQ_MASK) * (xf >> BXR_PROB_BITS) + ((rf >> 16) & BXR_LUT_FREQ_MASK);
-    xb = (rb & BXR_LUT_FREQ_MASK) * (xb >> BXR_PROB_BITS) + ((rb >> 16) & BXR_LUT_FREQ_MASK);
-    if (xf < BXR_STATE_LOW) { xf = (xf << 16) | lds_u16(wf); wf += 2; }
-    if (xb < BXR_STATE_LOW) { xb = (xb << 16) | lds_u16(wb); wb -= 2; }
-    ef = ((rf >> 5) & BXR_LUT_EXP_MASK) + base2;
-    eb = ((rb >> 5) & BXR_LUT_EXP_MASK) + base2;
-    if (max(sf, sb) >= esc_slot) {
-      if (sf >= esc_slot) ef = escape(rf, xf, wf, 2);
-      if (sb >= esc_slot) eb = escape(rb, xb, wb, -2);
+    const uint32_t af = lut + ((xf & (BXR_PROB_TOTAL - 1)) << 2), ab = lut + ((xb & (BXR_PROB_TOTAL - 1)) << 2);
+    const uint32_t rf = lds32(af), rb = lds32(ab);
+    xf = BXR_REC_FREQ(rf) * (xf >> BXR_PROB_BITS) + BXR_REC_BIAS(rf);
+    xb = BXR_REC_FREQ(rb) * (xb >> BXR_PROB_BITS) + BXR_REC_BIAS(rb);
+    refill_f();
+    refill_b();
+    ef = (rf & BXR_LUT_NIBBLES) * k.p7 + base2;
+    eb = (rb & BXR_LUT_NIBBLES) * k.p7 + base2;
+    if (max(af, ab) >= esc_addr) {
+      if (af >= esc_addr) ef = escape<true>(rf);
+      if (ab >= esc_addr) eb = escape<false>(rb);
     }
   }
 };
@@ -186,7 +211,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   ctx.status = args.status;
   const uint32_t bar_in_full = ctx.bars, bar_in_ready = bar_in_full + 8 * L::kIn, bar_in_empty = bar_in_ready + 8 * L::kIn;
   const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
-  const uint32_t bar_acc_full = bar_op_empty + 8 * L::kOp, bar_acc_empty = bar_acc_full + 16;
+  const uint32_t bar_acc_full = bar_op_empty + 8 * L::kOp, bar_acc_empty = bar_acc_full + 16, bar_lut = bar_acc_empty + 16;
   constexpr uint32_t kTmemCols = (2 * NB < 32) ? 32 : 2 * NB;
   constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;  // ring length of the operand stages (unused outside kUmma)
 
@@ -205,6 +230,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       mbar_init(bar_acc_full + 8 * i, MODE == kGemv ? kDecoderWarps : 1);
       mbar_init(bar_acc_empty + 8 * i, 4);
     }
+    mbar_init(bar_lut, 1);
     asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc), "r"(0u) : "memory");
     mbar_fence_init();
   }
@@ -212,9 +238,6 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     tmem_alloc(smem + L::misc, kTmemCols);
     tmem_relinquish();
   }
-  // the slot-record table: 16 KB, copied cooperatively (L2 hits after the first CTA)
-  for (uint32_t i = threadIdx.x; i < kLutBytes / 16; i += blockDim.x)
-    sts128(smem + L::lut + i * 16, __ldg(reinterpret_cast<const uint4*>(args.lut) + i));
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -232,9 +255,10 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t seg = q * BXR_ROWS + r, atom = q >> 1;
     LaneDecoder d;
     d.lut = smem + L::lut;
-    d.esc_slot = args.esc_slot;
+    d.esc_addr = smem + L::lut + 4 * args.esc_slot;
+    d.k = args.k;
     uint32_t u = 0;
-    bool live = true;
+    bool live = ctx.wait(bar_lut, 0);  // the slot records arrive by a bulk copy the loader issued first
     for (uint32_t it = item_begin; it < item_end && live; ++it) {
       const bxr_item item = args.items[it];
       const uint32_t row = item.row_block * BXR_ROWS + r;
@@ -246,11 +270,11 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       for (int m = 0; m < (MODE == kGemv ? kGemvMaxM : 1); ++m) acc[m] = 0.f;
       for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c, ++u) {
         const uint32_t s = u % L::kIn, ph = (u / L::kIn) & 1;
-        if (ctx.aborted() || !ctx.wait(bar_in_full + 8 * s, ph) || !ctx.wait(bar_in_ready + 8 * s, ph)) { live = false; break; }
+        // in_ready is posted by the scanner after it has itself observed the blob's arrival (in_full)
+        if (!ctx.wait(bar_in_ready + 8 * s, ph)) { live = false; break; }
         const uint32_t blob = smem + L::in + s * BXR_BLOB_MAX;
         const uint32_t bounds = lds32_unaligned_pair(smem + L::segoff + s * kSegOffBytes + 2 * seg);
-        d.wf = blob + BXR_WORDS_AT + 2 * (bounds & 0xFFFFu);
-        d.wb = blob + BXR_WORDS_AT + 2 * (bounds >> 16) - 2;
+        d.start_chunk(blob + BXR_WORDS_AT + 2 * (bounds & 0xFFFFu), blob + BXR_WORDS_AT + 2 * (bounds >> 16) - 2);
         uint32_t a_tile = 0;
         if (MODE == kUmma) {
           const uint32_t hs = 2 * u + atom, so = hs % kOpN, pho = (hs / kOpN) & 1;
@@ -389,6 +413,10 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     }
   } else if (warp == kWarpLoader) {
     // ------------------------------------------------------------------ chunk blobs, one bulk copy each
+    if (lane == 0) {  // the 16 KB slot-record table (L2 hits after the first CTA)
+      mbar_arrive_expect_tx(bar_lut, kLutBytes);
+      bulk_g2s(smem + L::lut, args.lut, kLutBytes, bar_lut);
+    }
     uint32_t issued = 0;
     for (uint32_t u0 = 0; u0 < unit_count; u0 += 32) {
       const uint32_t mine = unit_begin + min(u0 + lane, unit_count - 1);
@@ -414,8 +442,10 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       if (!live) break;
     }
     // after an abort: give copies still in flight a bounded time to land before the CTA exits
-    if (ctx.aborted() && lane == 0)
+    if (ctx.aborted() && lane == 0) {
+      mbar_wait(bar_lut, 0);
       for (uint32_t u = (issued > uint32_t(L::kIn) ? issued - L::kIn : 0); u < issued; ++u) mbar_wait(bar_in_full + 8 * (u % L::kIn), (u / L::kIn) & 1);
+    }
   } else if (warp == kWarpScanner) {
     // ------------------------------------------------------------------ segment offsets per chunk
     uint32_t u = 0;
