@@ -290,8 +290,22 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     layer = Layer(rank, world, device)
 
+    # The timed step is replayed from a CUDA graph (the entry points neither allocate nor synchronise), so the
+    # host's launch cost is not part of `value`; the e2e figure below goes through the eager public API.
+    step_fn, launch = layer.step, "eager"
+    if not args.no_graph:
+        try:
+            for _ in range(2):
+                layer.step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                layer.step()
+            step_fn, launch = graph.replay, "cuda_graph"
+        except Exception as exc:  # noqa: BLE001
+            launch = f"eager (graph capture failed: {type(exc).__name__})"
     with ClockSampler(local) as clocks:
-        ms = timed(layer.step, args.steps, args.warmup, world)
+        ms = timed(step_fn, args.steps, args.warmup, world)
     ms_e2e = timed(layer.step_e2e, args.steps, args.warmup, world)
     ktimes = kernel_times(layer, max(2, min(args.steps, 10)))
     status = layer.status()
@@ -318,7 +332,7 @@ def run_ours(args):
         "config": {"workload": "hybrid-decoder linears hidden=5120 (QKV 7168x5120, O 5120x5120, gate|up 34816x5120, down 5120x17408), "
                                "seed 1, fused decode-GEMM at M=1,64,128", "parallelism": f"tp{world}",
                    "l2": "coded working set ~440 MB exceeds the 126 MB L2; no flush between iterations",
-                   "resident_format": "BXR1", "status_word": status},
+                   "resident_format": "BXR1", "launch": launch, "status_word": status},
         "e2e": {"value": round(dense / (ms_e2e * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms_e2e, 4),
                 "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES)},
         "gpu_launches": layer.launches_per_step * args.steps,
@@ -336,6 +350,32 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_case(args):
+    """One kernel on one synthetic weight, a few launches: the command the ncu summaries under profiles/ use."""
+    import torch
+
+    from georefine_b200.resident import ResidentWeight
+
+    kind, m, shape = args.case.split(":")
+    m, (n, k) = int(m), map(int, shape.lower().split("x"))
+    words = synthetic_words(torch.Generator().manual_seed(SEED), n, k)
+    w = ResidentWeight.from_words(words, torch.device("cuda:0"), verify=False, max_m=max(m, 8))
+    x = torch.randn(m, k, device="cuda:0").to(torch.bfloat16)
+    y = torch.empty(m, n, device="cuda:0", dtype=torch.bfloat16)
+    t0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(max(args.steps, 1)):
+        if i == max(args.steps, 1) - 1:
+            t0[0].record()
+        if kind == "decode":
+            w.decode(check=False)
+        else:
+            getattr(w, kind)(x, y)
+    t0[1].record()
+    torch.cuda.synchronize()
+    print(json.dumps({"case": args.case, "coded_bytes": w.coded_bytes, "last_launch_us": round(t0[0].elapsed_time(t0[1]) * 1e3, 2),
+                      "status_word": w.check_status()}))
 
 
 def run_reference(args):
@@ -359,7 +399,12 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
+    ap.add_argument("--case", default=None, help="profiling aid: KIND:M:NxK (KIND = gemm, gemv or decode) runs that one "
+                                                 "launch --steps times on a synthetic weight and exits")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

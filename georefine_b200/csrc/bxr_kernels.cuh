@@ -52,6 +52,7 @@ struct BxrArgs {
   const uint32_t* blob_index;
   const uint8_t* blobs;
   uint32_t rows, cols, row_blocks, chunks, workers;
+  uint32_t raw;                // image holds plain pre-swizzled tiles (BXR_MODE_RAW): kUmma only, no decoders
   // call
   uint32_t m;                  // activation rows in this launch (<= NB, <= 8 for the GEMV)
   const __nv_bfloat16* x;      // GEMV only (the UMMA path reads x through the tensor map)
@@ -222,7 +223,8 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       mbar_init(bar_in_empty + 8 * i, kDecoderWarps);
     }
     for (int i = 0; i < L::kOp; ++i) {
-      mbar_init(bar_op_full + 8 * i, kDecoderWarps / 2 + 1);
+      // coded image: 8 decoder warps + the activation TMA; raw image: the tile copy + the activation TMA
+      mbar_init(bar_op_full + 8 * i, args.raw ? 2 : kDecoderWarps / 2 + 1);
       mbar_init(bar_op_empty + 8 * i, 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -251,6 +253,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
 
   if (warp < kDecoderWarps) {
     // ------------------------------------------------------------------ decoders: one segment (2 streams) per lane
+    if (MODE == kUmma && args.raw) goto roles_done;  // nothing to decode
     const uint32_t q = warp >> 2, r = (warp & 3) * 32 + lane;
     const uint32_t seg = q * BXR_ROWS + r, atom = q >> 1;
     LaneDecoder d;
@@ -413,6 +416,22 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     }
   } else if (warp == kWarpLoader) {
     // ------------------------------------------------------------------ chunk blobs, one bulk copy each
+    if (MODE == kUmma && args.raw) {
+      // raw image: every chunk blob is the 128x128 BF16 tile already in operand order (two 16 KB atoms);
+      // copy each atom straight into its operand stage
+      if (lane == 0) {
+        bool live = true;
+        for (uint32_t u = 0; u < unit_count && live; ++u)
+          for (uint32_t a = 0; a < 2; ++a) {
+            const uint32_t hs = 2 * u + a, so = hs % kOpN, pho = (hs / kOpN) & 1;
+            if (ctx.aborted() || !ctx.wait(bar_op_empty + 8 * so, pho ^ 1)) { live = false; break; }
+            mbar_arrive_expect_tx(bar_op_full + 8 * so, kAtomBytes);
+            bulk_g2s(smem + L::op + so * L::kOpStage, args.blobs + (size_t(unit_begin + u) * 2 + a) * kAtomBytes, kAtomBytes,
+                     bar_op_full + 8 * so);
+          }
+      }
+      goto roles_done;
+    }
     if (lane == 0) {  // the 16 KB slot-record table (L2 hits after the first CTA)
       mbar_arrive_expect_tx(bar_lut, kLutBytes);
       bulk_g2s(smem + L::lut, args.lut, kLutBytes, bar_lut);
@@ -448,6 +467,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     }
   } else if (warp == kWarpScanner) {
     // ------------------------------------------------------------------ segment offsets per chunk
+    if (MODE == kUmma && args.raw) goto roles_done;
     uint32_t u = 0;
     bool live = true;
     for (uint32_t it = item_begin; it < item_end && live; ++it) {
@@ -650,6 +670,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     }
   }
 
+roles_done:
   tc_fence_before();
   __syncthreads();
   if (MODE == kUmma && warp == kWarpMma) {

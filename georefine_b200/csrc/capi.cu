@@ -41,6 +41,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   a.row_blocks = h->row_blocks;
   a.chunks = h->chunks;
   a.workers = h->workers;
+  a.raw = h->mode == BXR_MODE_RAW;
   return a;
 }
 
@@ -97,6 +98,23 @@ int make_x_map(CUtensorMap* map, const void* x, int64_t ldx, uint32_t m, uint32_
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? GRB_OK : GRB_ERR_ARGUMENT;
+}
+
+// Raw-mode image -> dense words: undo the operand-order tiling (two 64-column atoms per 128x128 tile, 16-byte
+// pieces XOR-swizzled by row).  One thread per 16-byte piece.
+__global__ void bxr_raw_decode_kernel(const uint8_t* blobs, uint32_t rows, uint32_t cols, uint32_t chunks, uint64_t pieces,
+                                      uint16_t* out) {
+  const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= pieces) return;
+  const uint32_t j = uint32_t(i & 7), r = uint32_t(i >> 3) & 127, a = uint32_t(i >> 10) & 1;
+  const uint64_t tile = i >> 11;
+  const uint32_t rb = uint32_t(tile / chunks), c = uint32_t(tile % chunks);
+  const uint32_t row = rb * BXR_ROWS + r, col = c * BXR_COLS + a * 64 + j * 8;
+  if (row >= rows) return;
+  const uint4 v = *reinterpret_cast<const uint4*>(blobs + tile * BXR_RAW_TILE_BYTES + a * 16384 + r * 128 + ((j ^ (r & 7)) * 16));
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  for (int e = 0; e < 8; ++e)
+    if (col + e < cols) out[size_t(row) * cols + col + e] = uint16_t(w[e >> 1] >> (16 * (e & 1)));
 }
 
 template <int NB>
@@ -156,7 +174,12 @@ int grb_bctx_decode_words(const grb_bctx_tensor* t, const int64_t* block_ids, ui
 
 int grb_bxr_decode(const void* image, const bxr_header* h, uint16_t* out, uint32_t* status, void* cuda_stream) {
   if (!image || !header_ok(h) || !out || !status) return GRB_ERR_ARGUMENT;
-  if (h->mode != BXR_MODE_CODED) return GRB_ERR_UNSUPPORTED;
+  if (h->mode == BXR_MODE_RAW) {
+    const uint64_t pieces = uint64_t(h->row_blocks) * h->chunks * 2048;
+    bxr_raw_decode_kernel<<<unsigned((pieces + 255) / 256), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+        static_cast<const uint8_t*>(image) + h->blobs_at, h->rows, h->cols, h->chunks, pieces, out);
+    return cuda_status(cudaGetLastError());
+  }
   BxrArgs a = view_of(image, h);
   a.dense = out;
   a.status = status;
@@ -167,7 +190,6 @@ int grb_bxr_decode(const void* image, const bxr_header* h, uint16_t* out, uint32
 static int check_linear(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
                         void* ws, uint64_t ws_bytes, uint32_t* status, uint32_t tile_m) {
   if (!image || !header_ok(h) || !x || !y || !status || !m) return GRB_ERR_ARGUMENT;
-  if (h->mode != BXR_MODE_CODED) return GRB_ERR_UNSUPPORTED;
   if (ldx < int64_t(h->cols) || ldy < int64_t(h->rows) || (ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15))
     return GRB_ERR_ARGUMENT;
   const uint64_t need = counter_bytes(h) + uint64_t(h->partial_slots) * tile_m * BXR_ROWS * 4;
@@ -207,6 +229,8 @@ int grb_bxr_gemm(const void* image, const bxr_header* h, const void* x, int64_t 
 int grb_bxr_gemv(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
                  const void* bias, void* ws, uint64_t ws_bytes, uint32_t* status, void* cuda_stream) {
   if (m > uint32_t(kGemvMaxM)) return GRB_ERR_UNSUPPORTED;
+  // A raw-mode image has nothing to decode: it is served by the tensor-core path whatever the batch size.
+  if (header_ok(h) && h->mode == BXR_MODE_RAW) return grb_bxr_gemm(image, h, x, ldx, m, y, ldy, bias, ws, ws_bytes, status, cuda_stream);
   int st = check_linear(image, h, x, ldx, m, y, ldy, ws, ws_bytes, status, kGemvMaxM);
   if (st) return st;
   BxrArgs a = view_of(image, h);

@@ -183,7 +183,12 @@ class ResidentWeight:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
         if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
-            x2 = x2.contiguous()
+            if self.K % 8:  # the kernels want a row stride that is a multiple of 16 bytes
+                padded = torch.zeros((x2.shape[0], (self.K + 7) // 8 * 8), device=self.device, dtype=torch.bfloat16)
+                padded[:, :self.K] = x2
+                x2 = padded[:, :self.K]
+            else:
+                x2 = x2.contiguous()
         y = torch.empty((x2.shape[0], self.N), device=self.device, dtype=torch.bfloat16) if out is None else out.reshape(-1, self.N)
         if x2.shape[0] > self.max_m:
             self.reserve(x2.shape[0])

@@ -85,7 +85,7 @@ int grb_bctx_build_lookup(const uint32_t* freq, uint32_t nctx, uint32_t vocab, u
 
 #define GRB_OK 0
 #define GRB_ERR_ARGUMENT 1      /* null pointer, bad size, misaligned buffer */
-#define GRB_ERR_UNSUPPORTED 2   /* e.g. batch larger than the entry point handles, raw-mode image */
+#define GRB_ERR_UNSUPPORTED 2   /* e.g. batch larger than the entry point handles */
 #define GRB_ERR_WORKSPACE 3     /* workspace too small */
 #define GRB_ERR_STATIC_LIMIT 4  /* the image needs more scratch than the built-in array of grb_bxr_gemv_static */
 #define GRB_ERR_CUDA 100        /* + cudaError_t of the failing runtime call */

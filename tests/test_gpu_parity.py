@@ -217,3 +217,43 @@ def test_linearity_round_trip_at_full_size(orc, dev):
     ref = _reference_product(words, xs)
     assert ((ys.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
     assert ((y[0].float() + y[1].float() - ys[0].float()).abs().max() / ref.abs().max()).item() <= 3 * REL_TOL
+
+
+def test_raw_mode_images_decode_and_multiply(orc, oracle_coder, golden, dev):
+    """Incompressible weights are kept as plain tiles; the tensor-core path multiplies them without decoders."""
+    from georefine_b200.gpu import CudaContextTensor
+    from georefine_b200.resident import ResidentWeight
+
+    noise = np.random.default_rng(3).integers(0, 65536, (300, 256), dtype=np.uint16)
+    noise = (noise & 0xBFFF).astype(np.uint16)                    # keep the exponents finite
+    r = ResidentWeight.from_words(noise, dev, max_m=256)
+    assert r.mode == 1
+    assert np.array_equal(_u16(r.decode()), noise)
+    forced = ResidentWeight.from_words(orc.synthetic_weight_words(256, 384, 8), dev, force_raw=True, max_m=256)
+    coded = ResidentWeight.from_words(orc.synthetic_weight_words(256, 384, 8), dev, max_m=256)
+    assert forced.mode == 1 and coded.mode == 0
+    x = torch.randn(200, 384, device=dev).to(torch.bfloat16)
+    ya, yb = torch.empty(200, 256, device=dev, dtype=torch.bfloat16), torch.empty(200, 256, device=dev, dtype=torch.bfloat16)
+    forced.gemm(x, ya)
+    coded.gemm(x, yb)
+    assert forced.check_status() == 0 and np.array_equal(_u16(ya), _u16(yb))   # same tiles, same arithmetic
+    rows = {}
+    for m in (1, 3, 64, 200):
+        xm = torch.randn(200, 256, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)[:m].contiguous()
+        y = torch.empty(m, 300, device=dev, dtype=torch.bfloat16)
+        (r.gemv if m == 3 else r.gemm)(xm, y)
+        assert r.check_status() == 0
+        ref = _reference_product(noise, xm)
+        assert ((y.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
+        rows[m] = _u16(y)
+    assert all(np.array_equal(v, rows[200][:m]) for m, v in rows.items())
+    # a raw BCTX frame (mode 1) with an odd column count: the resident image still reproduces it, and the
+    # linear pads the activation rows to the 16-byte stride the kernels want
+    t = CudaContextTensor(golden["uniform13x17.frame"].tobytes(), device=dev)
+    words = (golden["uniform13x17.words"] & 0xBFFF).astype(np.uint16)
+    assert t.mode == 1 and np.array_equal(_u16(t.resident.decode()), golden["uniform13x17.words"])
+    r17 = ResidentWeight.from_words(words, dev)
+    x17 = torch.randn(5, 17, device=dev).to(torch.bfloat16)
+    y17 = r17.linear(x17)
+    ref = _reference_product(words, x17)
+    assert r17.check_status() == 0 and ((y17.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
