@@ -275,9 +275,24 @@ def kernel_times(layer, steps):
     return {key: float(np.mean([a.elapsed_time(b) for a, b in evs])) for key, evs in per.items()}
 
 
+def _deadline(seconds):
+    """Ends the process if the whole run takes longer than `seconds`: a stuck collective must not hold GPUs."""
+    def fire():
+        sys.stderr.write(f"bench.py: no result after {seconds} s, giving up\n")
+        sys.stderr.flush()
+        os._exit(3)
+
+    t = threading.Timer(seconds, fire)
+    t.daemon = True
+    t.start()
+    return t
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
+
+    _deadline(300)
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -287,13 +302,17 @@ def run_ours(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     layer = Layer(rank, world, device)
 
     # The timed step is replayed from a CUDA graph (the entry points neither allocate nor synchronise), so the
     # host's launch cost is not part of `value`; the e2e figure below goes through the eager public API.
     step_fn, launch = layer.step, "eager"
-    if not args.no_graph:
+    # With more than one rank the step contains NCCL all-reduces; capturing those in a graph hung on this pool
+    # (twice, at two ranks), so multi-rank runs launch eagerly.
+    if not args.no_graph and world == 1:
         try:
             for _ in range(2):
                 layer.step()

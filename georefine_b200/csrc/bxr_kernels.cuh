@@ -35,9 +35,10 @@ constexpr uint32_t kAtomBytes = 16384;  // 128 rows x 64 BF16
 constexpr uint32_t kInGuard = 128;      // a corrupt stream may read up to 50 bytes past its slot
 constexpr int kGemvMaxM = 8;
 
-// Powers of two passed as kernel parameters so the compiler cannot turn the multiplications back into shifts.
+// Powers of two passed as kernel parameters so that the compiler keeps `x * 2^k + y` a multiply-add on the FMA
+// pipe instead of a shift and an add on the busier integer pipe.
 struct BxrPowers {
-  uint32_t p2, p7, p12, p16, p20, m14;  // 4, 128, 2^12, 2^16, 2^20, -16384
+  uint32_t p7, p16;  // 128, 65536
 };
 
 struct BxrArgs {

@@ -29,7 +29,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   BxrArgs a{};
   a.lut = reinterpret_cast<const uint32_t*>(p + h->lut_at);
   a.esc_slot = h->esc_slot;
-  a.k = BxrPowers{4u, 128u, 1u << 12, 1u << 16, 1u << 20, uint32_t(-16384)};
+  a.k = BxrPowers{128u, 1u << 16};
   a.base = p + h->base_at;
   a.items = reinterpret_cast<const bxr_item*>(p + h->items_at);
   a.worker_items = reinterpret_cast<const uint32_t*>(p + h->worker_items_at);

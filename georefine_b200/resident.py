@@ -160,11 +160,16 @@ class ResidentWeight:
             return
         if m > self.max_m and min(m, 128) > min(self.max_m, 128):
             raise ValueError(f"batch of {m} rows exceeds the reserved scratch ({self.max_m}); call reserve() first")
-        with torch.cuda.device(self.device):
-            st = entry(self.image.data_ptr(), ctypes.byref(self.header), x.data_ptr(), x.stride(0), m, y.data_ptr(),
-                       y.stride(0), None if bias is None else bias.data_ptr(), self.workspace.data_ptr(),
-                       self.workspace.numel(), self.status.data_ptr(), self._stream())
-        _native.check(st, entry.__name__)
+        args = (self.image.data_ptr(), ctypes.byref(self.header), x.data_ptr(), x.stride(0), m, y.data_ptr(), y.stride(0),
+                None if bias is None else bias.data_ptr(), self.workspace.data_ptr(), self.workspace.numel(),
+                self.status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream)
+        if torch.cuda.current_device() == self.device.index:   # the usual case: skip the device switch
+            st = entry(*args)
+        else:
+            with torch.cuda.device(self.device):
+                st = entry(*args)
+        if st:
+            _native.check(st, entry.__name__)
 
     def gemm(self, x, y, bias=None):
         """tcgen05 path, any M; rows of y are bitwise independent of M."""
