@@ -69,8 +69,8 @@ struct BxrArgs {
 
 template <int MODE, int NB>
 struct BxrSmem {
-  static constexpr int kIn = (MODE == kUmma && NB >= 128) ? 3 : 4;
-  static constexpr int kOp = (MODE == kUmma) ? ((NB >= 64) ? 3 : 4) : 0;
+  static constexpr int kIn = (MODE == kUmma && NB <= 32) ? 5 : 4;
+  static constexpr int kOp = (MODE == kUmma) ? ((NB >= 128) ? 3 : 4) : 0;
   static constexpr uint32_t kOpStage = kAtomBytes + NB * 128;
   static constexpr uint32_t kXStage = (MODE == kGemv) ? kGemvMaxM * BXR_COLS * 4 : 0;  // FP32 activations per chunk
   static constexpr uint32_t lut = 0;
@@ -115,8 +115,7 @@ struct RoleCtx {
 // packed-BF16 position (bits 7..14 and 23..30).
 struct LaneDecoder {
   uint32_t xf, xb;   // rANS states
-  uint32_t wf, wb;   // shared addresses of the NEXT 16-bit word of each stream
-  uint32_t nf, nb;   // that word, already loaded: a refill never waits for shared memory
+  uint32_t wf, wb;   // shared addresses of the next 16-bit word of each stream
   uint32_t lut;      // shared address of the slot records
   uint32_t base2;    // row base replicated into both exponent fields
   uint32_t esc_addr; // shared address of the first slot record whose symbol contains an escape
@@ -125,15 +124,13 @@ struct LaneDecoder {
   __device__ __forceinline__ void start_chunk(uint32_t first_f, uint32_t first_b) {
     wf = first_f;
     wb = first_b;
-    nf = lds_u16(wf);
-    nb = lds_u16(wb);
   }
-  // (x << 16) | word as one multiply-add; the following word is fetched right away for the next refill.
+  // (x << 16) | word, written as one multiply-add
   __device__ __forceinline__ void refill_f() {
-    if (xf < BXR_STATE_LOW) { xf = xf * k.p16 + nf; wf += 2; nf = lds_u16(wf); }
+    if (xf < BXR_STATE_LOW) { xf = xf * k.p16 + lds_u16(wf); wf += 2; }
   }
   __device__ __forceinline__ void refill_b() {
-    if (xb < BXR_STATE_LOW) { xb = xb * k.p16 + nb; wb -= 2; nb = lds_u16(wb); }
+    if (xb < BXR_STATE_LOW) { xb = xb * k.p16 + lds_u16(wb); wb -= 2; }
   }
   // rare: an exponent outside the row window follows in the stream as a raw byte
   template <bool FWD>
@@ -244,6 +241,11 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // The image (table, blobs, states) is never written by a kernel, so everything up to the first access to x,
+  // bias, y or the workspace may overlap the tail of the previous kernel in the stream; the roles that touch
+  // those call grid_dependency_wait() first.
+  grid_dependents_may_launch();
+  if (MODE == kDense) grid_dependency_wait();
   uint32_t tmem_base = 0;
   if (MODE == kUmma) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(smem + L::misc));
 
@@ -345,6 +347,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       if (!live) break;
       if (d.xf != BXR_STATE_LOW || d.xb != BXR_STATE_LOW) atomicOr(args.status, kStatusCheckpoint);
       if (MODE == kGemv) {
+        if (it == item_begin) grid_dependency_wait();  // y, partial sums and counters
         // phases of a row are added in phase order, parts of a row block in part order
         const uint32_t red = smem + L::red;
         const uint32_t n_item = it - item_begin;
@@ -510,6 +513,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         }
         if (lane == 31) asm volatile("st.shared.u16 [%0], %1;" ::"r"(smem + L::segoff + s * kSegOffBytes + 1024), "h"(uint16_t(total)) : "memory");
         if (MODE == kGemv) {
+          if (u == 0) grid_dependency_wait();  // x may be the previous kernel's output
           // activations of this chunk as FP32: [m][128]
           const uint32_t xs = smem + L::xf32 + s * L::kXStage;
           for (int m = 0; m < kGemvMaxM; ++m)
@@ -530,6 +534,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   } else if (MODE == kUmma && warp == kWarpXLoader) {
     // ------------------------------------------------------------------ activation half-tiles by TMA
     if (lane == 0) {
+      grid_dependency_wait();
       uint32_t u = 0;
       bool live = true;
       for (uint32_t it = item_begin; it < item_end && live; ++it) {
@@ -582,6 +587,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t mcols = (args.m + 7) & ~7u;
     uint32_t n_item = 0;
     bool live = true;
+    grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
       const bxr_item item = args.items[it];
       const uint32_t buf = n_item & 1;

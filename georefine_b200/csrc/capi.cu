@@ -65,8 +65,19 @@ int launch(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
   cudaError_t e = prepare<MODE, NB>();
   if (e != cudaSuccess) return cuda_status(e);
   const int threads = MODE == kUmma ? kThreadsUmma : kThreadsSimt;
-  bxr_kernel<MODE, NB><<<a.workers, threads, BxrSmem<MODE, NB>::alloc, stream>>>(a, tmap);
-  return cuda_status(cudaGetLastError());
+  // Programmatic stream serialisation: this kernel may begin (table and blob loads, decoding) while the tail of
+  // the previous kernel in the stream is still running; it waits in-kernel before touching x, y or the scratch.
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(a.workers);
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = BxrSmem<MODE, NB>::alloc;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, bxr_kernel<MODE, NB>, a, tmap));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,

@@ -153,6 +153,12 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+// Programmatic dependent launch.  grid_dependents_may_launch() lets the next kernel in the stream start its
+// own prologue on SMs this grid has left; grid_dependency_wait() returns once every kernel this one depends on
+// has completed and its memory is visible.  Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }

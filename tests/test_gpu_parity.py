@@ -123,7 +123,9 @@ def test_resident_decode_flags_a_corrupt_image(orc, dev):
 
 
 # ---------------------------------------------------------------- fused linears
-SHAPES = [((128, 128), 0), ((256, 512), 1), ((300, 200), 2), ((1024, 4096), 3), ((4096, 4096), 0), ((2048, 5120), 1)]
+# includes the reference's own MIV test shapes with a ragged K (777 x 1032) and a long K (64 x 17408)
+SHAPES = [((128, 128), 0), ((256, 512), 1), ((300, 200), 2), ((1024, 4096), 3), ((4096, 4096), 0), ((2048, 5120), 1),
+          ((777, 1032), 5), ((64, 17408), 6)]
 
 
 @pytest.mark.parametrize("shape,seed", SHAPES)
@@ -198,6 +200,19 @@ def test_bias_strided_input_and_module_contract(orc, oracle_coder, dev):
     out = torch.empty(36, 384, device=dev, dtype=torch.bfloat16)
     assert t(x.reshape(-1, 256).contiguous(), out) is None
     assert t.resident.kind == "bctx" and t.resident.coded_bytes < 2 * words.size + 40000
+
+
+@pytest.mark.parametrize("shape", [(34816, 5120), (5120, 17408)])
+def test_full_size_images_reproduce_their_source_digest(orc, dev, shape):
+    """Benchmark-size weights: the GPU decode of the resident image hashes to the digest of the source words."""
+    from georefine_b200.resident import ResidentWeight
+
+    words = orc.synthetic_weight_words(*shape, 1)
+    r = ResidentWeight.from_words(words, dev, verify=False)
+    got = _u16(r.decode())
+    assert r.check_status() == 0
+    assert hashlib.sha256(got.tobytes()).digest() == hashlib.sha256(words.tobytes()).digest()
+    assert 1.40 < 2 * words.size / r.coded_bytes < 1.55
 
 
 def test_linearity_round_trip_at_full_size(orc, dev):
