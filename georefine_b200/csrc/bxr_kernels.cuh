@@ -264,6 +264,14 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     d.esc_addr = smem + L::lut + 4 * args.esc_slot;
     d.k = args.k;
     uint32_t u = 0;
+    // ring positions advance by increments (no division in the chunk loop); per-lane offsets are fixed
+    uint32_t s = 0, ph = 0;                          // input ring slot of chunk u and its phase parity
+    uint32_t so = atom % kOpN, pho = 0;              // operand ring stage of half-stage 2u + atom
+    const uint32_t raw_at = BXR_COUNT_BYTES + ((2 * q) * BXR_ROWS + r) * 16;
+    const uint32_t seg_at = smem + L::segoff + 2 * seg;
+    uint32_t st_at[4];                               // swizzled 16-byte positions of this lane's four stores
+#pragma unroll
+    for (int i = 0; i < 4; ++i) st_at[i] = r * 128 + ((((q & 1) * 4 + i) ^ (r & 7)) << 4);
     bool live = ctx.wait(bar_lut, 0);  // the slot records arrive by a bulk copy the loader issued first
     for (uint32_t it = item_begin; it < item_end && live; ++it) {
       const bxr_item item = args.items[it];
@@ -275,20 +283,18 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
 #pragma unroll
       for (int m = 0; m < (MODE == kGemv ? kGemvMaxM : 1); ++m) acc[m] = 0.f;
       for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c, ++u) {
-        const uint32_t s = u % L::kIn, ph = (u / L::kIn) & 1;
         // in_ready is posted by the scanner after it has itself observed the blob's arrival (in_full)
         if (!ctx.wait(bar_in_ready + 8 * s, ph)) { live = false; break; }
         const uint32_t blob = smem + L::in + s * BXR_BLOB_MAX;
-        const uint32_t bounds = lds32_unaligned_pair(smem + L::segoff + s * kSegOffBytes + 2 * seg);
+        const uint32_t bounds = lds32_unaligned_pair(seg_at + s * kSegOffBytes);
         d.start_chunk(blob + BXR_WORDS_AT + 2 * (bounds & 0xFFFFu), blob + BXR_WORDS_AT + 2 * (bounds >> 16) - 2);
         uint32_t a_tile = 0;
         if (MODE == kUmma) {
-          const uint32_t hs = 2 * u + atom, so = hs % kOpN, pho = (hs / kOpN) & 1;
           if (!ctx.wait(bar_op_empty + 8 * so, pho ^ 1)) { live = false; break; }
-          a_tile = smem + L::op + so * L::kOpStage + r * 128;
+          a_tile = smem + L::op + so * L::kOpStage;
         }
-        const uint4 raw_f = lds128(blob + BXR_COUNT_BYTES + ((2 * q) * BXR_ROWS + r) * 16);
-        const uint4 raw_b = lds128(blob + BXR_COUNT_BYTES + ((2 * q + 1) * BXR_ROWS + r) * 16);
+        const uint4 raw_f = lds128(blob + raw_at);
+        const uint4 raw_b = lds128(blob + raw_at + BXR_ROWS * 16);
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           uint4 w2[2];
@@ -299,8 +305,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
             const uint32_t cin = (2 * q + dir) * BXR_STREAM_COLS + k * 8;  // column inside the chunk
             const uint32_t col = c * BXR_COLS + cin;
             if (MODE == kUmma) {
-              const uint32_t cidx = (q & 1) * 4 + dir * 2 + k;
-              sts128(a_tile + ((cidx ^ (r & 7)) << 4), w);
+              sts128(a_tile + st_at[dir * 2 + k], w);
             } else if (MODE == kDense) {
               if (row < args.rows) {
                 uint16_t* dst = args.dense + size_t(row) * args.cols + col;
@@ -338,11 +343,14 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         if (MODE == kUmma) {
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_op_full + 8 * ((2 * u + atom) % kOpN));
+          if (lane == 0) mbar_arrive(bar_op_full + 8 * so);
+          so += 2;
+          if (so >= kOpN) { so -= kOpN; pho ^= 1; }
         } else {
           __syncwarp();
         }
         if (lane == 0) mbar_arrive(bar_in_empty + 8 * s);
+        if (++s == L::kIn) { s = 0; ph ^= 1; }
       }
       if (!live) break;
       if (d.xf != BXR_STATE_LOW || d.xb != BXR_STATE_LOW) atomicOr(args.status, kStatusCheckpoint);
