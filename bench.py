@@ -397,6 +397,53 @@ def run_case(args):
                       "status_word": w.check_status()}))
 
 
+def run_sweep(args):
+    """Same-GPU comparison table: every benchmark shape (and the 4096 x 4096 parity shape) at M = 1, 8, 64, 128.
+    Each timing rotates over enough copies of the weight to exceed the L2 (>= 400 MB per rotation)."""
+    import torch
+
+    from georefine_b200.resident import ResidentWeight
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(SEED)
+
+    def timeit(fn, copies, reps):
+        for i in range(max(6, copies)):
+            fn(i % copies)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(reps):
+            fn(i % copies)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    for name, n, k in [(nm, n, k) for nm, n, k, _, _ in LINEARS] + [("config0", 4096, 4096)]:
+        words = synthetic_words(g, n, k)
+        res = ResidentWeight.from_words(words, dev, verify=False, max_m=128)
+        coded, dense = res.coded_bytes, 2 * n * k
+        images = [res] + [res.clone() for _ in range(max(2, -(-400_000_000 // coded)) - 1)]
+        wd = [torch.from_numpy(words.view(np.int16)).view(torch.bfloat16).to(dev)]
+        wd += [wd[0].clone() for _ in range(max(2, -(-400_000_000 // dense)) - 1)]
+        reps = max(20, int(2e9 // coded))
+        row = {"shape": name, "N": n, "K": k, "coded_bytes": coded, "ratio": round(dense / coded, 3)}
+        for m in (1, 8, 64, 128):
+            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+            y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+            us = timeit(lambda i: images[i].gemm(x, y), len(images), reps)
+            row[f"gemm_M{m}"] = {"us": round(us, 1), "coded_GBps": round(coded / us / 1e3), "effective_GBps": round(dense / us / 1e3)}
+            if m <= 8:
+                us = timeit(lambda i: images[i].gemv(x, y), len(images), reps)
+                row[f"gemv_M{m}"] = {"us": round(us, 1), "coded_GBps": round(coded / us / 1e3), "effective_GBps": round(dense / us / 1e3)}
+            us = timeit(lambda i: torch.matmul(x, wd[i].T, out=y), len(wd), reps)
+            row[f"torch_dense_M{m}"] = {"us": round(us, 1), "GBps": round(dense / us / 1e3)}
+        row["status_word"] = sum(im.check_status() for im in images)
+        print(json.dumps(row), flush=True)
+        del images, wd, res
+        torch.cuda.empty_cache()
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -419,11 +466,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
+    ap.add_argument("--sweep", action="store_true", help="per shape and batch size: fused gemm / gemv against torch.matmul on "
+                                                        "the dense weights, one JSON line per shape")
     ap.add_argument("--case", default=None, help="profiling aid: KIND:M:NxK (KIND = gemm, gemv or decode) runs that one "
                                                  "launch --steps times on a synthetic weight and exits")
     args = ap.parse_args()
     if args.case:
         return run_case(args)
+    if args.sweep:
+        return run_sweep(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

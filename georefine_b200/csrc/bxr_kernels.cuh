@@ -80,9 +80,9 @@ struct BxrSmem {
   static constexpr uint32_t xf32 = segoff + kIn * kSegOffBytes;
   static constexpr uint32_t bars = (xf32 + kIn * kXStage + 15) & ~15u;
   // barrier order: in_full, in_ready, in_empty [kIn each]; op_full, op_empty [kOp each]; acc_full, acc_empty [2 each]
-  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4 + 1;  // + the table's arrival barrier (last)
+  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4 + 2;  // + the table's arrival barrier, + the final verdict
   static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, reduce flag, spare
-  static constexpr uint32_t red = misc + 16;          // GEMV: FP32 [4 phases][128 rows][8]
+  static constexpr uint32_t red = misc + 48;          // GEMV: FP32 [4 phases][128 rows][8]
   static constexpr uint32_t total = red + (MODE == kGemv ? 4 * 128 * kGemvMaxM * 4 : 0);
   static constexpr uint32_t alloc = total + 1024;     // slack to align the base to 1024
   static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
@@ -194,6 +194,55 @@ __device__ __forceinline__ void decode8x2(LaneDecoder& d, uint32_t f_lo, uint32_
 __device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
 
+// Ordered reduction of the FP32 partial tiles of one row block: y[m, row] = bf16(sum over parts in K order
+// (+ bias)).  Called by the CTA that delivered the last tile.  `group` warps share the work: warp g takes the
+// batch rows g, g + group, ...; a lane takes 4 consecutive weight rows (one float4 per tile), four batch rows
+// at a time so that 4 x parts loads are in flight per thread.
+template <int NB>
+__device__ __forceinline__ void reduce_row_block(const BxrArgs& args, uint32_t row_block, uint32_t first, uint32_t parts,
+                                                 uint32_t g, uint32_t group, uint32_t lane) {
+  const uint32_t r4 = lane * 4, row4 = row_block * BXR_ROWS + r4;
+  if (row4 >= args.rows) return;
+  float bias4[4] = {0.f, 0.f, 0.f, 0.f};
+  if (args.bias)
+    for (int i = 0; i < 4; ++i)
+      if (row4 + i < args.rows) bias4[i] = __bfloat162float(args.bias[row4 + i]);
+  for (uint32_t m0 = g; m0 < args.m; m0 += 4 * group) {
+    float4 t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t m = m0 + group * j;
+      t[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first) * NB + m) * BXR_ROWS + r4))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (uint32_t p = 1; p < parts; ++p) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t m = m0 + group * j;
+        v[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4))
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        t[j].x = __fadd_rn(t[j].x, v[j].x);
+        t[j].y = __fadd_rn(t[j].y, v[j].y);
+        t[j].z = __fadd_rn(t[j].z, v[j].z);
+        t[j].w = __fadd_rn(t[j].w, v[j].w);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t m = m0 + group * j;
+      if (m >= args.m) continue;
+      const float f[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
+      __nv_bfloat16* dst = args.y + size_t(m) * args.ldy + row4;
+      for (int i = 0; i < 4; ++i)
+        if (row4 + i < args.rows) dst[i] = __float2bfloat16_rn(args.bias ? __fadd_rn(f[i], bias4[i]) : f[i]);
+    }
+  }
+}
+
 template <int MODE, int NB>
 __global__ void __launch_bounds__(MODE == kUmma ? kThreadsUmma : kThreadsSimt, 1)
 bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
@@ -210,7 +259,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   ctx.status = args.status;
   const uint32_t bar_in_full = ctx.bars, bar_in_ready = bar_in_full + 8 * L::kIn, bar_in_empty = bar_in_ready + 8 * L::kIn;
   const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
-  const uint32_t bar_acc_full = bar_op_empty + 8 * L::kOp, bar_acc_empty = bar_acc_full + 16, bar_lut = bar_acc_empty + 16;
+  const uint32_t bar_acc_full = bar_op_empty + 8 * L::kOp, bar_acc_empty = bar_acc_full + 16, bar_lut = bar_acc_empty + 16, bar_final = bar_lut + 8;
   constexpr uint32_t kTmemCols = (2 * NB < 32) ? 32 : 2 * NB;
   constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;  // ring length of the operand stages (unused outside kUmma)
 
@@ -231,7 +280,8 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       mbar_init(bar_acc_empty + 8 * i, 4);
     }
     mbar_init(bar_lut, 1);
-    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc), "r"(0u) : "memory");
+    mbar_init(bar_final, 4);  // one arrival per epilogue warp once its items are done
+    for (int i = 0; i < 3; ++i) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc + 16 * i), "r"(0u) : "memory");
     mbar_fence_init();
   }
   if (MODE == kUmma && warp == kWarpMma) {
@@ -637,51 +687,30 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         if (prev == item.parts - 1) {  // every partial tile of this row block is in memory: add them in K order
           __threadfence();
           const uint32_t first = item.slot - item.part;
-          // warp e takes batch rows e, e+4, ...; a lane takes 4 consecutive weight rows (one float4 per
-          // partial tile), eight batch rows at a time so that 8 x parts loads are in flight
-          const uint32_t r4 = lane * 4, row4 = item.row_block * BXR_ROWS + r4;
-          float bias4[4] = {0.f, 0.f, 0.f, 0.f};
-          if (args.bias)
-            for (int i = 0; i < 4; ++i)
-              if (row4 + i < args.rows) bias4[i] = __bfloat162float(args.bias[row4 + i]);
-          for (uint32_t m0 = e; m0 < args.m; m0 += 32) {
-            float4 t[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t m = m0 + 4 * j;
-              t[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first) * NB + m) * BXR_ROWS + r4))
-                                : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-            for (uint32_t p = 1; p < item.parts; ++p) {
-              float4 v[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const uint32_t m = m0 + 4 * j;
-                v[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4))
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                t[j].x = __fadd_rn(t[j].x, v[j].x);
-                t[j].y = __fadd_rn(t[j].y, v[j].y);
-                t[j].z = __fadd_rn(t[j].z, v[j].z);
-                t[j].w = __fadd_rn(t[j].w, v[j].w);
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const uint32_t m = m0 + 4 * j;
-              if (m >= args.m) continue;
-              const float f[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
-              __nv_bfloat16* dst = args.y + size_t(m) * args.ldy + row4;
-              for (int i = 0; i < 4; ++i)
-                if (row4 + i < args.rows) dst[i] = __float2bfloat16_rn(args.bias ? __fadd_rn(f[i], bias4[i]) : f[i]);
-            }
+          if (it + 1 == item_end && !args.raw) {
+            // the CTA's last item: the decoder warps have nothing left to do and share the reduction (below)
+            if (e == 0 && lane == 0)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + 16), "r"(1u), "r"(item.row_block),
+                           "r"(first), "r"(item.parts) : "memory");
+          } else {
+            reduce_row_block<NB>(args, item.row_block, first, item.parts, e, 4, lane);
           }
           if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
         }
         named_barrier(1, 128);  // the verdict word may be rewritten
       }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_final);
+  }
+
+  // A row block whose last partial tile came from this CTA's final item is reduced by the 16 decoder warps and
+  // the 4 epilogue warps together (20 warps instead of 4 on the critical tail of the kernel).
+  if (MODE == kUmma && !args.raw && (warp < kDecoderWarps || warp >= kWarpEpilogue)) {
+    if (ctx.wait(bar_final, 0)) {
+      const uint4 verdict = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
+      if (verdict.x)
+        reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
     }
   }
 
