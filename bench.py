@@ -42,8 +42,8 @@ LINEARS = [("qkv", 7168, HIDDEN, "col", [5120, 1024, 1024]), ("o", HIDDEN, HIDDE
 BATCHES = (1, 64, 128)
 SEED = 1
 # dram__bytes_read+write over algorithmic bytes of one launch, from the ncu capture summarised in
-# profiles/bxr_kernel_gemm_m1_down_5120x17408.md (121.7 MB read + 3.5 MB written for 121.9 MB algorithmic)
-DRAM_TRAFFIC_RATIO = 1.03
+# profiles/bxr_kernel_gemm_m1_down_5120x17408.md (121.7 MB read + 5.5 MB written for 121.6 MB algorithmic)
+DRAM_TRAFFIC_RATIO = 1.05
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -271,6 +271,16 @@ def kernel_times(layer, steps):
                 e["res"].gemm(x, e["y"][m])
                 b.record()
                 per.setdefault((e["name"], m), []).append((a, b))
+    # the CUDA-core GEMV at M = 1, for the record (not part of the timed step: its rows are M-invariant only
+    # among M = 1..8, while the step compares M = 1, 64 and 128 bit for bit)
+    for _ in range(steps):
+        for e in layer.entries:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x = layer.x[(1, e["k"])][:, e["k0"]:e["k1"]]
+            a.record()
+            e["res"].gemv(x, e["y"][1])
+            b.record()
+            per.setdefault((e["name"], "gemv1"), []).append((a, b))
     torch.cuda.synchronize()
     return {key: float(np.mean([a.elapsed_time(b) for a, b in evs])) for key, evs in per.items()}
 
@@ -332,6 +342,8 @@ def run_ours(args):
     dense = layer.dense_bytes_per_step()
     peak, peak_kind = measured_hbm_peak()
     algo = sum(layer.algorithmic_bytes(e, m) for m in BATCHES for e in layer.entries)
+    gemv_ms = sum(ktimes.pop((e["name"], "gemv1")) for e in layer.entries)
+    gemv_bytes = sum(layer.algorithmic_bytes(e, 1) for e in layer.entries)
     ksum = sum(ktimes.values())
     achieved = algo / (ksum * 1e-3) / 1e9
     per_m = {}
@@ -360,7 +372,10 @@ def run_ours(args):
                      "kernel": "bxr_kernel<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
                      "top_launch": {"linear": top[0], "m": top[1], "ms": round(ktimes[top], 4), "algorithmic_bytes": top_bytes,
                                     "GBps": round(top_bytes / ktimes[top] / 1e6, 1)}},
-        "per_m": per_m, "clocks": clocks.summary(),
+        "per_m": per_m,
+        "gemv_m1": {"kernel_ms": round(gemv_ms, 4), "coded_GBps": round(gemv_bytes / gemv_ms / 1e6, 1),
+                    "frac_of_hbm_peak": round(gemv_bytes / gemv_ms / 1e6 / peak, 4), "note": "CUDA-core path, outside the timed step"},
+        "clocks": clocks.summary(),
     }
     if rank == 0 and world == 1:
         value, dt, info = cpu_reference_run(sample_rows=2048, steps=1, warmup=0, threads=os.cpu_count() or 1)
