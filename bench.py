@@ -193,6 +193,7 @@ class Layer:
         self.x_host = {(m, k): torch.randn(m, k, generator=g).to(torch.bfloat16).pin_memory() for m in BATCHES for k in (HIDDEN, FFN)}
         self.x = {key: v.to(device) for key, v in self.x_host.items()}
         self.y_host = {m: torch.empty(m, HIDDEN, dtype=torch.bfloat16).pin_memory() for m in BATCHES}
+        self.xv = {(m, e["name"]): self.x[(m, e["k"])][:, e["k0"]:e["k1"]] for m in BATCHES for e in self.entries}
         self.launches_per_step = len(LINEARS) * len(BATCHES)
 
     def dense_bytes_per_step(self):
@@ -216,15 +217,20 @@ class Layer:
             for e in self.entries:
                 self.call(e, m, self.x[(m, e["k"])])
 
+    # (call() slices x per launch; the end-to-end loop below uses the views prepared once in self.xv)
+
     def step_e2e(self):
-        """Host buffers in, host buffers out, through the public linear() call."""
+        """Host buffers in, host buffers out, through the descriptor call `weight(x, y)` a serving engine makes:
+        every activation is copied from pinned host memory first, the down projection's output is copied back."""
         import torch
         import torch.distributed as dist
 
         for m in BATCHES:
-            xd = {k: self.x_host[(m, k)].to(self.device, non_blocking=True) for k in (HIDDEN, FFN)}
+            for k in (HIDDEN, FFN):
+                self.x[(m, k)].copy_(self.x_host[(m, k)], non_blocking=True)
             for e in self.entries:
-                y = e["res"].linear(xd[e["k"]][:, e["k0"]:e["k1"]])
+                y = e["y"][m]
+                e["res"](self.xv[(m, e["name"])], y)
                 if e["kind"] == "row" and self.world > 1:
                     dist.all_reduce(y)
             self.y_host[m].copy_(y, non_blocking=True)   # the down projection's output
@@ -395,6 +401,22 @@ def run_case(args):
     kind, m, shape = args.case.split(":")
     m, (n, k) = int(m), map(int, shape.lower().split("x"))
     words = synthetic_words(torch.Generator().manual_seed(SEED), n, k)
+    if kind == "bctx":   # indexed decode of the unchanged BCTX streams; the second field is the restart stride
+        from georefine_b200 import codec
+        from georefine_b200.gpu import CudaContextTensor
+
+        t = CudaContextTensor(codec.encode(words), stride=m, device="cuda:0", fused=False)
+        ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(max(args.steps, 1)):
+            if i == max(args.steps, 1) - 1:
+                ev[0].record()
+            out = t.decode(check=False)
+        ev[1].record()
+        torch.cuda.synchronize()
+        us = ev[0].elapsed_time(ev[1]) * 1e3
+        print(json.dumps({"case": args.case, "frame_bytes": t.frame_bytes, "last_decode_us": round(us, 1),
+                          "dense_GBps": round(2 * n * k / us / 1e3, 1), "status_word": int(t.error.item())}))
+        return
     w = ResidentWeight.from_words(words, torch.device("cuda:0"), verify=False, max_m=max(m, 8))
     x = torch.randn(m, k, device="cuda:0").to(torch.bfloat16)
     y = torch.empty(m, n, device="cuda:0", dtype=torch.bfloat16)

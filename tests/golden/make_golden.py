@@ -1,6 +1,6 @@
 """Regenerates tests/golden/bctx_golden.npz from the REFERENCE implementation.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where the reference checkout is available (path as argument, or $REFERENCE_ROOT):
 
     python tests/golden/make_golden.py [reference_root]
 
@@ -32,7 +32,7 @@ sys.path.insert(0, str(ROOT))
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", "/root/reference"))
     os.environ["BITEXACT_CONTEXT_CACHE_DIR"] = tempfile.mkdtemp(prefix="bctx-golden-")
     sys.path.insert(0, str(ref_root / "context-runtime"))
     from georefine_context_runtime import bitexact_context_codec as ref  # noqa: E402
