@@ -82,7 +82,7 @@ struct Source {
   // activation tile is zero there), so they carry whatever finite word is cheapest to code.
   uint16_t at(uint32_t r, uint32_t c) const { return words[size_t(std::min(r, rows - 1)) * cols + c]; }
   uint16_t padded(uint32_t r, uint32_t c, const uint8_t* base) const {
-    return c < cols ? at(r, c) : uint16_t((uint32_t(base[r]) + 10u) << 7);
+    return c < cols ? at(r, c) : uint16_t((uint32_t(base[r]) + 12u) << 7);
   }
 };
 
@@ -113,7 +113,8 @@ std::vector<uint8_t> choose_bases(const Source& src, uint32_t rows_pad, uint32_t
   for (uint32_t r = 0; r < rows_pad; ++r) {
     const uint32_t* h = &hist[size_t(r) * 256];
     const uint32_t mode = uint32_t(std::max_element(h, h + 256) - h);
-    base[r] = uint8_t(std::min<int>(241, std::max<int>(0, int(mode) - 10)));
+    // most frequent exponent at code 12: two binades of headroom above it, twelve below (the long tail)
+    base[r] = uint8_t(std::min<int>(241, std::max<int>(0, int(mode) - 12)));
   }
   for (int round = 0; round < 2; ++round) {
     double cnt[16] = {0};
@@ -129,7 +130,9 @@ std::vector<uint8_t> choose_bases(const Source& src, uint32_t rows_pad, uint32_t
     for (double c : cnt) total += c;
     double cost[16];
     for (int n = 0; n < 16; ++n) cost[n] = -std::log2((cnt[n] + 0.5) / (total + 8.0));
-    cost[15] += 8.0;
+    // 8 bits for the raw exponent, plus a penalty: an escape costs the decoding warp a divergent slow path, so
+    // the window is pushed towards the side where escapes are rarest even when the size gain is negligible
+    cost[15] += 8.0 + 24.0;
     for (uint32_t r = 0; r < rows_pad; ++r) {
       const uint32_t* h = &hist[size_t(r) * 256];
       double best = 0;
