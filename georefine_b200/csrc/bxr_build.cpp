@@ -197,22 +197,20 @@ struct StreamCoder {
     renorm(uint64_t(f) << 20);
     x = ((x / f) << BXR_PROB_BITS) + (x % f) + cum;
   }
-  void put_byte(uint32_t v) {
-    renorm(uint64_t(1) << 24);
-    x = (x << 8) | v;
-  }
 };
 
 struct ItemCode {
   std::vector<uint16_t> words[BXR_STREAMS];         // decode order, all chunks of the item
   std::vector<uint8_t> per_chunk[BXR_STREAMS];      // words consumed in each chunk
   uint32_t state[BXR_STREAMS];
+  std::vector<std::vector<uint32_t>> exceptions;    // per chunk: {segment | column in segment << 9 | exponent << 14}
 };
 
 void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, const uint32_t* freq, const uint32_t* cum,
                  ItemCode& code) {
   const uint32_t nch = it.chunk_end - it.chunk_begin;
   std::vector<uint16_t> rev;
+  code.exceptions.assign(nch, {});
   for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
     const uint32_t piece = sid / BXR_ROWS, r = sid % BXR_ROWS;  // piece = 2q + d: 16 columns of the chunk
     const uint32_t row = it.row_block * BXR_ROWS + r;
@@ -228,14 +226,15 @@ void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, con
         const uint32_t col = c * BXR_COLS + piece * BXR_STREAM_COLS + 2 * uint32_t(t);
         const uint32_t e0 = exponent_of(src.padded(row, col, base)), e1 = exponent_of(src.padded(row, col + 1, base));
         const uint32_t n0 = nibble_of(e0, b), n1 = nibble_of(e1, b);
-        if (n1 == BXR_ESCAPE) coder.put_byte(e1);
-        if (n0 == BXR_ESCAPE) coder.put_byte(e0);
+        // an exponent outside the row window is coded as nibble 15 and listed with the chunk
+        const uint32_t seg = (piece / 2) * BXR_ROWS + r, in_seg = (piece & 1) * BXR_STREAM_COLS + 2 * uint32_t(t);
+        if (n0 == BXR_ESCAPE) code.exceptions[c - it.chunk_begin].push_back(seg | in_seg << 9 | e0 << 14);
+        if (n1 == BXR_ESCAPE) code.exceptions[c - it.chunk_begin].push_back(seg | (in_seg + 1) << 9 | e1 << 14);
         const uint32_t sym = n0 | n1 << 4;
         coder.put_symbol(freq[sym], cum[sym]);
       }
       const size_t used = rev.size() - before;
-      // At most 3 words per step (one symbol, two escape bytes), so 24 per chunk; 255 flags an overflow.
-      counts[c - it.chunk_begin] = used > 120 ? uint8_t(255) : uint8_t(used);
+      counts[c - it.chunk_begin] = uint8_t(used);  // at most one word per step: 8 per chunk
     }
     code.state[sid] = coder.x;
     code.words[sid].assign(rev.rbegin(), rev.rend());
@@ -266,7 +265,6 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
 
     std::vector<uint8_t> base(rows_pad, 0);
     std::vector<uint32_t> lut(BXR_PROB_TOTAL, 0);
-    uint32_t esc_slot = BXR_PROB_TOTAL;
     std::vector<std::vector<uint8_t>> blobs(nblobs);
     std::vector<uint32_t> states(size_t(nitems) * BXR_STREAMS, BXR_STATE_LOW);
     bool raw_mode = force_raw != 0;
@@ -296,17 +294,12 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
       // A record has 12 bits for the frequency: a symbol that owns every slot cedes one to an unused symbol.
       for (uint32_t s = 0; s < 256; ++s)
         if (freq[s] == BXR_PROB_TOTAL) { freq[s] -= 1; freq[s ? 0 : 1] += 1; }
-      // Slot order: symbols without an escape first, then the ones with an escape nibble.
-      auto has_escape = [](uint32_t s) { return (s & 15) == BXR_ESCAPE || (s >> 4) == BXR_ESCAPE; };
       uint32_t run = 0;
-      for (int pass = 0; pass < 2; ++pass) {
-        if (pass == 1) esc_slot = run;
-        for (uint32_t s = 0; s < 256; ++s)
-          if (has_escape(s) == (pass == 1)) { cum[s] = run; run += freq[s]; }
+      for (uint32_t s = 0; s < 256; ++s) { cum[s] = run; run += freq[s]; }
+      for (uint32_t s = 0; s < 256; ++s) {
+        const uint32_t n0 = (s & 15) == BXR_ESCAPE ? 0 : (s & 15), n1 = (s >> 4) == BXR_ESCAPE ? 0 : (s >> 4);
+        for (uint32_t slot = cum[s]; slot < cum[s] + freq[s]; ++slot) lut[slot] = n0 | (slot - cum[s]) << 4 | n1 << 16 | freq[s] << 20;
       }
-      for (uint32_t s = 0; s < 256; ++s)
-        for (uint32_t slot = cum[s]; slot < cum[s] + freq[s]; ++slot)
-          lut[slot] = (s & 15) | (slot - cum[s]) << 4 | (s >> 4) << 16 | freq[s] << 20;
 
       std::atomic<bool> overflow{false};
       parallel_for(nitems, threads, [&](uint32_t i) {
@@ -319,15 +312,19 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
         for (uint32_t c = it.chunk_begin; c < it.chunk_end; ++c) {
           const uint32_t k = c - it.chunk_begin;
           uint32_t total = 0;
-          bool bad = false;
-          for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) {
-            if (code->per_chunk[sid][k] == 255) bad = true;
-            total += code->per_chunk[sid][k];
-          }
-          if (bad || total > BXR_WORDS_MAX) { overflow.store(true); return; }
+          for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid) total += code->per_chunk[sid][k];
+          std::vector<uint32_t>& exc = code->exceptions[k];
+          std::sort(exc.begin(), exc.end(), [](uint32_t a, uint32_t b) { return (a & 0x3FFF) < (b & 0x3FFF); });
+          const uint64_t exc_at = (BXR_WORDS_AT + 2ull * total + 3) & ~3ull;
+          const uint64_t blob_bytes = align16(exc_at + 4 + 4ull * exc.size());
+          if (total > BXR_WORDS_MAX || exc.size() > BXR_EXC_MAX || blob_bytes > BXR_BLOB_MAX) { overflow.store(true); return; }
           std::vector<uint8_t>& blob = blobs[size_t(it.row_block) * plan.chunks + c];
-          blob.assign(size_t(align16(BXR_WORDS_AT + 2ull * total)), 0);
-          uint8_t* raw = blob.data() + BXR_COUNT_BYTES;
+          blob.assign(size_t(blob_bytes), 0);
+          const uint32_t n_exc = uint32_t(exc.size());
+          std::memcpy(blob.data() + exc_at, &n_exc, 4);
+          if (n_exc) std::memcpy(blob.data() + exc_at + 4, exc.data(), 4ull * n_exc);
+          for (uint32_t v : exc) blob[BXR_EXC_BITS_AT + ((v & 511) >> 3)] |= uint8_t(1u << (v & 7));
+          uint8_t* raw = blob.data() + BXR_RAW_AT;
           for (uint32_t piece = 0; piece < 2 * BXR_PHASES; ++piece)
             for (uint32_t r = 0; r < BXR_ROWS; ++r) {
               uint8_t* dst = raw + (size_t(piece) * BXR_ROWS + r) * 16;
@@ -378,7 +375,6 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     h.workers = workers;
     h.items = nitems;
     h.partial_slots = plan.partial_slots;
-    h.esc_slot = esc_slot;
     uint64_t at = align16(sizeof(bxr_header));
     at = (at + 255) & ~uint64_t(255);
     h.lut_at = at;            at += raw_mode ? 0 : sizeof(uint32_t) * BXR_PROB_TOTAL;
@@ -449,7 +445,6 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
     const auto* lut = reinterpret_cast<const uint32_t*>(img + h.lut_at);
     const uint8_t* base = img + h.base_at;
     const auto* states = reinterpret_cast<const uint32_t*>(img + h.states_at);
-    int status = 0;
     for (uint32_t i = 0; i < h.items; ++i) {
       const bxr_item& it = items[i];
       std::vector<uint32_t> x(states + size_t(i) * BXR_STREAMS, states + size_t(i + 1) * BXR_STREAMS);
@@ -469,33 +464,39 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
           int64_t cur = backward ? int64_t(start[g + 1]) - 1 : int64_t(start[g]);
           const int step = backward ? -1 : 1;
           uint32_t s = x[sid];
-          auto refill = [&] {
+          const uint32_t row = it.row_block * BXR_ROWS + r, b = base[row];
+          const uint8_t* bytes16 = blob + BXR_RAW_AT + (size_t(piece) * BXR_ROWS + r) * 16;
+          for (uint32_t t = 0; t < BXR_STEPS; ++t) {
+            const uint32_t rec = lut[s & (BXR_PROB_TOTAL - 1)];
+            s = BXR_REC_FREQ(rec) * (s >> BXR_PROB_BITS) + BXR_REC_BIAS(rec);
             if (s < BXR_STATE_LOW) {
-              if (cur < int64_t(start[g]) || cur >= int64_t(start[g + 1])) { status = 2; return; }
+              if (cur < int64_t(start[g]) || cur >= int64_t(start[g + 1])) return 2;
               s = (s << 16) | words[cur];
               cur += step;
             }
-          };
-          const uint32_t row = it.row_block * BXR_ROWS + r, b = base[row];
-          const uint8_t* bytes16 = blob + BXR_COUNT_BYTES + (size_t(piece) * BXR_ROWS + r) * 16;
-          for (uint32_t t = 0; t < BXR_STEPS; ++t) {
-            const uint32_t slot = s & (BXR_PROB_TOTAL - 1);
-            const uint32_t rec = lut[slot];
-            s = BXR_REC_FREQ(rec) * (s >> BXR_PROB_BITS) + BXR_REC_BIAS(rec);
-            refill();
-            const uint32_t n0 = BXR_REC_N0(rec), n1 = BXR_REC_N1(rec);
-            uint32_t e0 = n0 + b, e1 = n1 + b;
-            if (slot >= h.esc_slot) {
-              if (n0 == BXR_ESCAPE) { e0 = s & 0xFF; s >>= 8; refill(); }
-              if (n1 == BXR_ESCAPE) { e1 = s & 0xFF; s >>= 8; refill(); }
-            }
+            const uint32_t e0 = BXR_REC_N0(rec) + b, e1 = BXR_REC_N1(rec) + b;
             const uint32_t b0 = bytes16[2 * t], b1 = bytes16[2 * t + 1];
             const uint32_t col = c * BXR_COLS + piece * BXR_STREAM_COLS + 2 * t;
             put(row, col, uint16_t((b0 & 0x80) << 8 | (e0 & 0xFF) << 7 | (b0 & 0x7F)));
             put(row, col + 1, uint16_t((b1 & 0x80) << 8 | (e1 & 0xFF) << 7 | (b1 & 0x7F)));
           }
           x[sid] = s;
-          if (status) return status;
+        }
+        // exceptions: the true exponent replaces the placeholder the stream produced
+        const uint64_t exc_at = (BXR_WORDS_AT + 2ull * start[BXR_SEGMENTS] + 3) & ~3ull;
+        if (exc_at + 4 > blob_bytes) return 2;
+        uint32_t n_exc;
+        std::memcpy(&n_exc, blob + exc_at, 4);
+        if (n_exc > BXR_EXC_MAX || exc_at + 4 + 4ull * n_exc > blob_bytes) return 2;
+        for (uint32_t i = 0; i < n_exc; ++i) {
+          uint32_t v;
+          std::memcpy(&v, blob + exc_at + 4 + 4ull * i, 4);
+          const uint32_t g = v & 511, in_seg = (v >> 9) & 31, e = (v >> 14) & 255;
+          if (!((blob[BXR_EXC_BITS_AT + (g >> 3)] >> (g & 7)) & 1)) return 2;
+          const uint32_t q = g / BXR_ROWS, r = g % BXR_ROWS;
+          const uint32_t row = it.row_block * BXR_ROWS + r, col = c * BXR_COLS + q * 32 + in_seg;
+          const uint32_t byte = blob[BXR_RAW_AT + (size_t(2 * q + in_seg / 16) * BXR_ROWS + r) * 16 + in_seg % 16];
+          put(row, col, uint16_t((byte & 0x80) << 8 | e << 7 | (byte & 0x7F)));
         }
       }
       for (uint32_t sid = 0; sid < BXR_STREAMS; ++sid)

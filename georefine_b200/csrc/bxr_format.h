@@ -8,12 +8,13 @@
 //
 //   word     = sign(1) exponent(8) mantissa(7)
 //   raw byte = sign << 7 | mantissa                       stored verbatim, 1 byte per weight
-//   exponent -> nibble n = exponent - base[row] when 0 <= n <= 14, else n = 15 ("escape", the 8-bit
-//               exponent follows in the same stream at probability 1/256)
+//   exponent -> nibble n = exponent - base[row] when 0 <= n <= 14, else n = 15 ("exception": the decoder
+//               emits exponent base[row] for it and the true 8-bit exponent is patched in afterwards from
+//               the chunk's exception list; about 1.5e-4 of the weights on Gaussian rows)
 //   symbol   = n(col 2t) | n(col 2t+1) << 4                one rANS step decodes two weights
 //   rANS     : 32-bit state, lower bound 2^16, 16-bit words, 12-bit probabilities, one static table
-//              per tensor stored as 4096 32-bit slot records {n0, bias, n1, freq}; symbols that contain
-//              an escape own the highest slots, so "slot >= esc_slot" is the whole escape test
+//              per tensor stored as 4096 32-bit slot records {n0, bias, n1, freq}; the decode loop has no
+//              data-dependent branch
 //
 // Geometry.  Rows are grouped in row blocks of 128 (one UMMA M tile), columns in chunks of 128.  Inside a
 // chunk every row has 8 independent streams of 16 columns (8 steps) each.  A stream runs through the
@@ -26,8 +27,11 @@
 //
 // Chunk blob (size = multiple of 16 bytes, at most BXR_BLOB_MAX):
 //   [0,512)          u8  count[512]         words in segment g = q*128 + r
-//   [512,16896)      u8  raw[8][128][16]    piece (s, r) = raw bytes of row r, chunk columns 16s..16s+15
-//   [16896, ...)     u16 words              segments in order g, then zero padding
+//   [512,576)        u8  exc_bits[64]       bit g set: segment g has at least one exception in this chunk
+//   [576,16960)      u8  raw[8][128][16]    piece (s, r) = raw bytes of row r, chunk columns 16s..16s+15
+//   [16960, ...)     u16 words              segments in order g
+//   then, 4-byte aligned: u32 exception count, u32 entries {segment[0,9) | column in segment[9,14) |
+//   exponent[14,22)} sorted by segment, then zero padding
 //
 // Work items.  The K range of every row block is cut so that `workers` CTAs get equal numbers of chunks
 // (a contiguous range of the (row block, chunk) sequence each).  An item is the part of one row block
@@ -46,10 +50,13 @@
 #define BXR_STREAMS 1024   /* per row block: (2q + d) * 128 + row, d = 0 forward / 1 backward reader */
 #define BXR_SEGMENTS 512   /* per chunk: q * 128 + row */
 #define BXR_COUNT_BYTES 512
+#define BXR_EXC_BITS_AT 512
+#define BXR_RAW_AT 576
 #define BXR_RAW_BYTES 16384
-#define BXR_WORDS_AT (BXR_COUNT_BYTES + BXR_RAW_BYTES)
+#define BXR_WORDS_AT (BXR_RAW_AT + BXR_RAW_BYTES)
+#define BXR_EXC_MAX 1024 /* exception entries a decoder will look at in one chunk */
 #define BXR_BLOB_MAX 24576 /* shared-memory slot per chunk blob */
-#define BXR_WORDS_MAX ((BXR_BLOB_MAX - BXR_WORDS_AT) / 2)
+#define BXR_WORDS_MAX ((BXR_BLOB_MAX - BXR_WORDS_AT - 16) / 2)
 #define BXR_PROB_BITS 12
 #define BXR_PROB_TOTAL 4096
 #define BXR_STATE_LOW 65536u
@@ -59,8 +66,8 @@
 #define BXR_RAW_TILE_BYTES 32768
 
 /* Slot record of the pair table, 32 bits: n0[0,4) | bias[4,16) | n1[16,20) | freq[20,32).  freq <= 4095.
- * (record & 0x000F000F) * 128 is the pair of relative exponents in packed-BF16 position, freq is the top
- * field (one shift or one multiply-high), bias = (record << 16) >> 20. */
+ * (record & 0x000F000F) * 128 is the pair of relative exponents in packed-BF16 position (an exception nibble is
+ * stored as 0), freq is the top field, bias = (record >> 4) & 0xFFF. */
 #define BXR_LUT_NIBBLES 0x000F000Fu
 #define BXR_REC_FREQ(rec) ((rec) >> 20)
 #define BXR_REC_BIAS(rec) (((rec) >> 4) & 0xFFFu)
@@ -83,7 +90,7 @@ typedef struct bxr_header {
   uint32_t row_blocks, chunks;    /* padded shape / 128 */
   uint32_t workers, items;
   uint32_t partial_slots;         /* FP32 partial tiles the workspace must hold */
-  uint32_t esc_slot;              /* slots >= esc_slot decode to a symbol with at least one escape */
+  uint32_t reserved0;
   uint64_t lut_at;                /* u32[4096] slot records (absent in raw mode) */
   uint64_t base_at;               /* u8[row_blocks*128] exponent base per row */
   uint64_t items_at;              /* bxr_item[items] */

@@ -44,7 +44,6 @@ struct BxrPowers {
 struct BxrArgs {
   // image
   const uint32_t* lut;
-  uint32_t esc_slot;
   BxrPowers k;
   const uint8_t* base;
   const bxr_item* items;
@@ -118,7 +117,6 @@ struct LaneDecoder {
   uint32_t wf, wb;   // shared addresses of the next 16-bit word of each stream
   uint32_t lut;      // shared address of the slot records
   uint32_t base2;    // row base replicated into both exponent fields
-  uint32_t esc_addr; // shared address of the first slot record whose symbol contains an escape
   BxrPowers k;
 
   __device__ __forceinline__ void start_chunk(uint32_t first_f, uint32_t first_b) {
@@ -132,24 +130,6 @@ struct LaneDecoder {
   __device__ __forceinline__ void refill_b() {
     if (xb < BXR_STATE_LOW) { xb = xb * k.p16 + lds_u16(wb); wb -= 2; }
   }
-  // rare: an exponent outside the row window follows in the stream as a raw byte
-  template <bool FWD>
-  __device__ __forceinline__ uint32_t escape(uint32_t rec) {
-    uint32_t& x = FWD ? xf : xb;
-    const uint32_t b = (base2 >> 7) & 0xFFu;
-    uint32_t e0 = BXR_REC_N0(rec) + b, e1 = BXR_REC_N1(rec) + b;
-    if (BXR_REC_N0(rec) == BXR_ESCAPE) {
-      e0 = x & 0xFFu;
-      x >>= 8;
-      if (FWD) refill_f(); else refill_b();
-    }
-    if (BXR_REC_N1(rec) == BXR_ESCAPE) {
-      e1 = x & 0xFFu;
-      x >>= 8;
-      if (FWD) refill_f(); else refill_b();
-    }
-    return (e0 << 7) | (e1 << 23);
-  }
   // One step of both streams.  The record layout keeps the integer-pipe work low: the frequency is the top
   // field (one shift), the nibble pair becomes the exponent pair with one mask and one multiply-add.
   __device__ __forceinline__ void step(uint32_t& ef, uint32_t& eb) {
@@ -161,10 +141,6 @@ struct LaneDecoder {
     refill_b();
     ef = (rf & BXR_LUT_NIBBLES) * k.p7 + base2;
     eb = (rb & BXR_LUT_NIBBLES) * k.p7 + base2;
-    if (max(af, ab) >= esc_addr) {
-      if (af >= esc_addr) ef = escape<true>(rf);
-      if (ab >= esc_addr) eb = escape<false>(rb);
-    }
   }
 };
 
@@ -311,13 +287,13 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t seg = q * BXR_ROWS + r, atom = q >> 1;
     LaneDecoder d;
     d.lut = smem + L::lut;
-    d.esc_addr = smem + L::lut + 4 * args.esc_slot;
     d.k = args.k;
     uint32_t u = 0;
     // ring positions advance by increments (no division in the chunk loop); per-lane offsets are fixed
     uint32_t s = 0, ph = 0;                          // input ring slot of chunk u and its phase parity
     uint32_t so = atom % kOpN, pho = 0;              // operand ring stage of half-stage 2u + atom
-    const uint32_t raw_at = BXR_COUNT_BYTES + ((2 * q) * BXR_ROWS + r) * 16;
+    const uint32_t raw_at = BXR_RAW_AT + ((2 * q) * BXR_ROWS + r) * 16;
+    const uint32_t exc_bit_at = BXR_EXC_BITS_AT + (seg >> 3), exc_bit = 1u << (seg & 7);
     const uint32_t seg_at = smem + L::segoff + 2 * seg;
     uint32_t st_at[4];                               // swizzled 16-byte positions of this lane's four stores
 #pragma unroll
@@ -387,6 +363,38 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
                   acc[m] = a;
                 }
               }
+            }
+          }
+        }
+        // Exceptions (exponents outside the row window, ~1.5e-4 of the weights): the stream produced the
+        // placeholder exponent base[row]; the lane that owns the segment patches its own output from the list.
+        if (lds_u8(blob + exc_bit_at) & exc_bit) {
+          const uint32_t total = lds_u16(seg_at - 2 * seg + s * kSegOffBytes + 2 * BXR_SEGMENTS);
+          const uint32_t exc_at = blob + ((BXR_WORDS_AT + 2 * total + 3) & ~3u);
+          const uint32_t n_exc = min(lds32(exc_at), uint32_t(BXR_EXC_MAX));
+          for (uint32_t i = 0; i < n_exc; ++i) {
+            const uint32_t v = lds32(exc_at + 4 + 4 * i);
+            if ((v & 511u) != seg) continue;
+            const uint32_t in_seg = (v >> 9) & 31u, e = (v >> 14) & 255u;
+            const uint32_t byte = lds_u8(blob + raw_at + (in_seg >> 4) * BXR_ROWS * 16 + (in_seg & 15u));
+            const uint32_t word = (byte & 0x80u) << 8 | e << 7 | (byte & 0x7Fu);
+            if (MODE == kUmma) {
+              sts_u16(a_tile + r * 128 + ((((q & 1) * 4 + (in_seg >> 3)) ^ (r & 7)) << 4) + 2 * (in_seg & 7u), word);
+            } else if (MODE == kDense) {
+              const uint32_t col = c * BXR_COLS + q * 32 + in_seg;
+              if (row < args.rows && col < args.cols) args.dense[size_t(row) * args.cols + col] = uint16_t(word);
+            } else {
+              // the chain already holds x * placeholder: take it out and put the true product in
+              const float good = __uint_as_float(word << 16);
+              const float wrong = __uint_as_float(((byte & 0x80u) << 8 | (d.base2 & 0x7F80u) | (byte & 0x7Fu)) << 16);
+              const uint32_t xs = smem + L::xf32 + s * L::kXStage + (q * 32 + in_seg) * 4;
+#pragma unroll
+              for (int m = 0; m < kGemvMaxM; ++m)
+                if (m < NB) {
+                  float xv;
+                  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xv) : "r"(xs + m * BXR_COLS * 4));
+                  acc[m] = __fmaf_rn(xv, good, __fmaf_rn(-xv, wrong, acc[m]));
+                }
             }
           }
         }

@@ -28,7 +28,6 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   const auto* p = static_cast<const uint8_t*>(image);
   BxrArgs a{};
   a.lut = reinterpret_cast<const uint32_t*>(p + h->lut_at);
-  a.esc_slot = h->esc_slot;
   a.k = BxrPowers{128u, 1u << 16};
   a.base = p + h->base_at;
   a.items = reinterpret_cast<const bxr_item*>(p + h->items_at);

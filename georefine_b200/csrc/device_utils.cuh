@@ -105,6 +105,14 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
 }
 // Two consecutive 16-bit values at a 2-byte aligned address, as lo | hi << 16.
 __device__ __forceinline__ uint32_t lds32_unaligned_pair(uint32_t a) { return lds_u16(a) | (lds_u16(a + 2) << 16); }
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts_u16(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"(uint16_t(v)) : "memory");
+}
 __device__ __forceinline__ void sts128(uint32_t a, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }

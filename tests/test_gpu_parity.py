@@ -104,6 +104,24 @@ def test_resident_decode_special_words(dev):
     special = np.resize(np.array([0, 0x8000, 0x7F80, 0xFF80, 0x7FC1, 0xFFE5, 1, 0x8001], dtype=np.uint16), (64, 67))
     r = ResidentWeight.from_words(special, dev)
     assert np.array_equal(_u16(r.decode()), special)
+    # ordinary weights with 2 % zeros, denormals, infinities and NaNs: the exception lists of a coded image
+    from oracle import bcx_oracle as orc_mod
+    sprinkled = orc_mod.synthetic_weight_words(200, 300, 17)
+    rng = np.random.default_rng(17)
+    at = rng.random(sprinkled.shape) < 0.02
+    sprinkled[at] = rng.choice(special.ravel()[:8], size=int(at.sum()))
+    r = ResidentWeight.from_words(sprinkled, dev)
+    assert r.mode == 0 and np.array_equal(_u16(r.decode()), sprinkled)
+    finite = sprinkled.copy()
+    finite[(finite & 0x7F80) == 0x7F80] = 0x3C00                      # keep zeros and denormals, drop inf/NaN
+    r = ResidentWeight.from_words(finite, dev)
+    x = torch.randn(8, 300, device=dev).to(torch.bfloat16)
+    ref = _reference_product(finite, x)
+    y, yv = r.linear(x), torch.empty(8, 200, device=dev, dtype=torch.bfloat16)
+    r.gemv(x.contiguous() if x.stride(0) % 8 == 0 else torch.nn.functional.pad(x, (0, 4))[:, :300], yv)
+    assert r.check_status() == 0
+    assert ((y.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
+    assert ((yv.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
     every = np.arange(65536, dtype=np.uint16).reshape(256, 256)   # every BF16 pattern once
     r = ResidentWeight.from_words(every, dev)
     if r.mode == 0:

@@ -163,8 +163,14 @@ def test_resident_image_round_trips_and_plan_is_balanced(orc, shape, seed, worke
 
 def test_resident_image_special_values_and_raw_fallback(orc):
     special = np.resize(np.array([0, 0x8000, 0x7F80, 0xFF80, 0x7FC1, 0xFFE5, 1, 0x8001], dtype=np.uint16), (64, 67))
-    image, h = resident.build_image(special, 9)
-    assert h.mode == 0 and np.array_equal(resident.decode_image_host(image), special)
+    image, h = resident.build_image(special, 9)          # half of these words lie outside any 15-binade window
+    assert h.mode == 1 and np.array_equal(resident.decode_image_host(image), special)
+    sprinkled = orc.synthetic_weight_words(200, 300, 17)    # ordinary weights with 2 % special values: exception lists
+    rng = np.random.default_rng(17)
+    at = rng.random(sprinkled.shape) < 0.02
+    sprinkled[at] = rng.choice(special.ravel()[:8], size=int(at.sum()))
+    image, h = resident.build_image(sprinkled, 9)
+    assert h.mode == 0 and np.array_equal(resident.decode_image_host(image), sprinkled)
     noise = np.random.default_rng(0).integers(0, 65536, (256, 256), dtype=np.uint16)
     image, h = resident.build_image(noise, 148)
     assert h.mode == 1 and np.array_equal(resident.decode_image_host(image), noise)
