@@ -2,7 +2,7 @@
 //
 // bxr_build re-codes decoded BF16 words (the output of the BCTX index walk) into the image the fused
 // kernels stream; bxr_decode_host walks an image exactly the way a GPU lane does (slot records, forward
-// and backward segment cursors, escape bytes) and returns the words, so a loader can bind the image to
+// and backward segment cursors, exception list) and returns the words, so a loader can bind the image to
 // the frame's source digest before it is uploaded.  This plays the role of the load-time transcode the
 // reference performs for its other resident formats (glc_serve/bctx_v21_transcode.py) and of the digest
 // check in bitexact_context_gpu.py:104-105.
@@ -130,8 +130,8 @@ std::vector<uint8_t> choose_bases(const Source& src, uint32_t rows_pad, uint32_t
     for (double c : cnt) total += c;
     double cost[16];
     for (int n = 0; n < 16; ++n) cost[n] = -std::log2((cnt[n] + 0.5) / (total + 8.0));
-    // 8 bits for the raw exponent, plus a penalty: an escape costs the decoding warp a divergent slow path, so
-    // the window is pushed towards the side where escapes are rarest even when the size gain is negligible
+    // 32 bits for the list entry, plus a penalty: an exception costs the decoding warp a divergent patch, so the
+    // window is pushed towards the side where exceptions are rarest even when the size gain is negligible
     cost[15] += 8.0 + 24.0;
     for (uint32_t r = 0; r < rows_pad; ++r) {
       const uint32_t* h = &hist[size_t(r) * 256];
