@@ -168,7 +168,7 @@ def cpu_reference_run(sample_rows, steps, warmup, threads):
 class Layer:
     """The four linears of one decoder layer on this rank, as resident images (tensor-parallel when world > 1)."""
 
-    def __init__(self, rank, world, device):
+    def __init__(self, rank, world, device, layout="window"):
         import torch
 
         from georefine_b200 import tp
@@ -185,7 +185,7 @@ class Layer:
             else:
                 k0, k1 = tp.row_range(k, rank, world, tp.CHUNK)
                 local = w[:, k0:k1]
-            res = ResidentWeight.from_words(np.ascontiguousarray(local), device, max_m=max(BATCHES), verify=False)
+            res = ResidentWeight.from_words(np.ascontiguousarray(local), device, max_m=max(BATCHES), verify=False, layout=layout)
             self.entries.append({"name": name, "kind": kind, "n": n, "k": k, "k0": k0, "k1": k1, "res": res,
                                  "y": {m: torch.empty(m, res.N, device=device, dtype=torch.bfloat16) for m in BATCHES}})
             del w, local
@@ -354,7 +354,7 @@ def run_ours(args):
         import datetime
 
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
-    layer = Layer(rank, world, device)
+    layer = Layer(rank, world, device, layout=args.layout)
 
     # The timed step is replayed from a CUDA graph (the entry points neither allocate nor synchronise), so the
     # host's launch cost is not part of `value`; the e2e figure below goes through the eager public API.
@@ -410,18 +410,19 @@ def run_ours(args):
         "config": {"workload": "hybrid-decoder linears hidden=5120 (QKV 7168x5120, O 5120x5120, gate|up 34816x5120, down 5120x17408), "
                                "seed 1, fused decode-GEMM at M=1,64,128", "parallelism": f"tp{world}",
                    "l2": "coded working set ~440 MB exceeds the 126 MB L2; no flush between iterations",
-                   "resident_format": "BXR1", "launch": launch, "status_word": status},
+                   "resident_format": "BXR1/" + args.layout, "launch": launch, "status_word": status},
         "e2e": {"value": round(dense / (ms_e2e * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms_e2e, 4),
                 "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES)},
         "gpu_launches": layer.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO), "peak_source": peak_kind,
-                     "kernel": "bxr_kernel<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
+                     "kernel": ("bxw_kernel" if args.layout == "window" else "bxr_kernel") + "<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
                      "top_launch": {"linear": top[0], "m": top[1], "ms": round(ktimes[top], 4), "algorithmic_bytes": top_bytes,
                                     "GBps": round(top_bytes / ktimes[top] / 1e6, 1)}},
         "per_m": per_m,
         "gemv_m1": {"kernel_ms": round(gemv_ms, 4), "coded_GBps": round(gemv_bytes / gemv_ms / 1e6, 1),
-                    "frac_of_hbm_peak": round(gemv_bytes / gemv_ms / 1e6 / peak, 4), "note": "CUDA-core path, outside the timed step"},
+                    "frac_of_hbm_peak": round(gemv_bytes / gemv_ms / 1e6 / peak, 4),
+                    "note": "grb_bxr_gemv outside the timed step: CUDA-core kernel for the rans layout, the tensor-core kernel at its narrowest tile for the window layout"},
         "clocks": clocks.summary(),
     }
     if rank == 0 and world == 1:
@@ -458,7 +459,7 @@ def run_case(args):
         print(json.dumps({"case": args.case, "frame_bytes": t.frame_bytes, "last_decode_us": round(us, 1),
                           "dense_GBps": round(2 * n * k / us / 1e3, 1), "status_word": int(t.error.item())}))
         return
-    w = ResidentWeight.from_words(words, torch.device("cuda:0"), verify=False, max_m=max(m, 8))
+    w = ResidentWeight.from_words(words, torch.device("cuda:0"), verify=False, max_m=max(m, 8), layout=args.layout)
     x = torch.randn(m, k, device="cuda:0").to(torch.bfloat16)
     y = torch.empty(m, n, device="cuda:0", dtype=torch.bfloat16)
     t0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -471,7 +472,7 @@ def run_case(args):
             getattr(w, kind)(x, y)
     t0[1].record()
     torch.cuda.synchronize()
-    print(json.dumps({"case": args.case, "coded_bytes": w.coded_bytes, "last_launch_us": round(t0[0].elapsed_time(t0[1]) * 1e3, 2),
+    print(json.dumps({"case": args.case, "layout": args.layout, "mode": w.mode, "coded_bytes": w.coded_bytes, "last_launch_us": round(t0[0].elapsed_time(t0[1]) * 1e3, 2),
                       "status_word": w.check_status()}))
 
 
@@ -499,13 +500,13 @@ def run_sweep(args):
 
     for name, n, k in [(nm, n, k) for nm, n, k, _, _ in LINEARS] + [("config0", 4096, 4096)]:
         words = synthetic_words(g, n, k)
-        res = ResidentWeight.from_words(words, dev, verify=False, max_m=128)
+        res = ResidentWeight.from_words(words, dev, verify=False, max_m=128, layout=args.layout)
         coded, dense = res.coded_bytes, 2 * n * k
         images = [res] + [res.clone() for _ in range(max(2, -(-400_000_000 // coded)) - 1)]
         wd = [torch.from_numpy(words.view(np.int16)).view(torch.bfloat16).to(dev)]
         wd += [wd[0].clone() for _ in range(max(2, -(-400_000_000 // dense)) - 1)]
         reps = max(20, int(2e9 // coded))
-        row = {"shape": name, "N": n, "K": k, "coded_bytes": coded, "ratio": round(dense / coded, 3)}
+        row = {"shape": name, "N": n, "K": k, "layout": args.layout, "coded_bytes": coded, "ratio": round(dense / coded, 3)}
         for m in (1, 8, 64, 128):
             x = torch.randn(m, k, device=dev).to(torch.bfloat16)
             y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
@@ -546,6 +547,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
     ap.add_argument("--sweep", action="store_true", help="per shape and batch size: fused gemm / gemv against torch.matmul on "
                                                         "the dense weights, one JSON line per shape")
+    ap.add_argument("--layout", choices=("rans", "window"), default="window",
+                    help="resident layout of the weights: entropy-coded exponent streams or fixed 3-bit window codes")
     ap.add_argument("--case", default=None, help="profiling aid: KIND:M:NxK (KIND = gemm, gemv or decode) runs that one "
                                                  "launch --steps times on a synthetic weight and exits")
     args = ap.parse_args()

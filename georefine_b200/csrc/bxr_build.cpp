@@ -243,6 +243,133 @@ void encode_item(const Source& src, const bxr_item& it, const uint8_t* base, con
 
 uint64_t align16(uint64_t v) { return (v + 15) & ~uint64_t(15); }
 
+// ---- window mode ------------------------------------------------------------------------------------------
+// Row windows: the 8 consecutive exponents [base, base + 7] that cover most of the row.
+std::vector<uint8_t> choose_window_bases(const Source& src, uint32_t rows_pad, uint32_t threads) {
+  std::vector<uint8_t> base(rows_pad);
+  parallel_for(rows_pad, threads, [&](uint32_t r) {
+    uint32_t h[256 + 8] = {0};
+    for (uint32_t c = 0; c < src.cols; ++c) ++h[exponent_of(src.at(r, c))];
+    uint32_t run = 0, best = 0, best_base = 0;
+    for (uint32_t e = 0; e < 8; ++e) run += h[e];
+    for (uint32_t b = 0;; ++b) {
+      if (run > best) { best = run; best_base = b; }
+      if (b == BXW_BASE_MAX) break;
+      run += h[b + 8];
+      run -= h[b];
+    }
+    base[r] = uint8_t(best_base);
+  });
+  return base;
+}
+
+// Where the word of (row in warp, column in the lane's 32) sits in the warp's part of the operand tile.
+inline uint32_t window_place(uint32_t q, uint32_t rl, uint32_t j) {
+  return rl * 64 + ((((q & 1) * 4 + j / 8) ^ (rl & 7)) * 8) + (j & 7);
+}
+
+// One chunk blob in window mode; false when the entry lists do not fit the slot.
+bool window_blob(const Source& src, uint32_t row_block, uint32_t chunk, const uint8_t* base, std::vector<uint8_t>& blob) {
+  std::vector<uint16_t> entries[16];
+  std::vector<uint32_t> far;
+  std::vector<uint8_t> fixed(BXW_LIST_AT, 0);
+  auto* codes = reinterpret_cast<uint32_t*>(fixed.data() + BXW_CODES_AT);
+  for (uint32_t warp = 0; warp < 16; ++warp) {
+    const uint32_t q = warp >> 2;
+    for (uint32_t rl = 0; rl < 32; ++rl) {
+      const uint32_t r = (warp & 3) * 32 + rl, row = row_block * BXR_ROWS + r, b = base[row];
+      uint32_t code[32];
+      for (uint32_t j = 0; j < 32; ++j) {
+        const uint32_t col = chunk * BXR_COLS + q * 32 + j;
+        // a padded column never reaches an output: it carries the window's first exponent and a zero raw byte
+        const uint16_t w = col < src.cols ? src.at(row, col) : uint16_t(b << 7);
+        const int delta = int(exponent_of(w)) - int(b);
+        fixed[BXW_RAW_AT + (size_t(2 * q + j / 16) * BXR_ROWS + r) * 16 + j % 16] = raw_byte_of(w);
+        if (delta >= 0 && delta <= 7) { code[j] = uint32_t(delta); continue; }
+        code[j] = 0;
+        const uint32_t place = window_place(q, rl, j);
+        int field = delta;
+        if (delta < -15 || delta > 15) {
+          field = BXW_DELTA_FAR;
+          far.push_back(warp << BXW_PLACE_BITS | place | exponent_of(w) << 16);
+        }
+        entries[warp].push_back(uint16_t(place | (uint32_t(field) & 31u) << BXW_PLACE_BITS));
+      }
+      uint32_t word[3] = {0, 0, 0};
+      for (uint32_t p = 0; p < 15; ++p) word[p / 5] |= code[2 * p] << (1 + 3 * (p % 5)) | code[2 * p + 1] << (17 + 3 * (p % 5));
+      for (uint32_t t = 0; t < 3; ++t) word[t] |= ((code[30] >> t) & 1u) | ((code[31] >> t) & 1u) << 16;
+      for (uint32_t t = 0; t < 3; ++t) codes[t * BXR_SEGMENTS + q * BXR_ROWS + r] = word[t];
+    }
+  }
+  size_t total = 0;
+  auto* warp_end = reinterpret_cast<uint16_t*>(fixed.data() + BXW_WARP_END_AT);
+  for (uint32_t w = 0; w < 16; ++w) { warp_end[w] = uint16_t(total); total += entries[w].size(); }
+  if (total > BXW_ENTRY_MAX || far.size() > BXW_FAR_MAX) return false;
+  warp_end[16] = uint16_t(total);
+  const uint16_t n_far = uint16_t(far.size());
+  std::memcpy(fixed.data() + BXW_FAR_COUNT_AT, &n_far, 2);
+  const size_t far_at = (BXW_LIST_AT + 2 * total + 3) & ~size_t(3);
+  blob.assign((far_at + 4 * far.size() + 15) & ~size_t(15), 0);
+  std::memcpy(blob.data(), fixed.data(), BXW_LIST_AT);
+  size_t at = BXW_LIST_AT;
+  for (uint32_t w = 0; w < 16; ++w) {
+    if (!entries[w].empty()) std::memcpy(blob.data() + at, entries[w].data(), 2 * entries[w].size());
+    at += 2 * entries[w].size();
+  }
+  if (!far.empty()) std::memcpy(blob.data() + far_at, far.data(), 4 * far.size());
+  return true;
+}
+
+// Inverse of window_blob, written the way a GPU warp works: fixed codes first, then the entry lists.
+bool window_unblob(const uint8_t* blob, uint64_t blob_bytes, const uint8_t* base_rows, uint16_t* tile /* [128][128] */) {
+  if (blob_bytes < BXW_LIST_AT) return false;
+  uint16_t warp_end[17], n_far;
+  std::memcpy(warp_end, blob + BXW_WARP_END_AT, sizeof warp_end);
+  std::memcpy(&n_far, blob + BXW_FAR_COUNT_AT, 2);
+  const size_t total = warp_end[16];
+  const size_t far_at = (BXW_LIST_AT + 2 * total + 3) & ~size_t(3);
+  if (total > BXW_ENTRY_MAX || n_far > BXW_FAR_MAX || far_at + 4ull * n_far > blob_bytes) return false;
+  const auto* codes = reinterpret_cast<const uint32_t*>(blob + BXW_CODES_AT);
+  for (uint32_t q = 0; q < BXR_PHASES; ++q)
+    for (uint32_t r = 0; r < BXR_ROWS; ++r) {
+      uint32_t word[3];
+      for (uint32_t t = 0; t < 3; ++t) word[t] = codes[t * BXR_SEGMENTS + q * BXR_ROWS + r];
+      const uint32_t b = base_rows[r];
+      for (uint32_t j = 0; j < 32; ++j) {
+        const uint32_t p = j / 2, odd = j & 1;
+        uint32_t code;
+        if (p < 15) code = (word[p / 5] >> (1 + 3 * (p % 5) + 16 * odd)) & 7u;
+        else code = ((word[0] >> (16 * odd)) & 1u) | ((word[1] >> (16 * odd)) & 1u) << 1 | ((word[2] >> (16 * odd)) & 1u) << 2;
+        const uint32_t e = (b + code) & 0xFFu, byte = blob[BXW_RAW_AT + (size_t(2 * q + j / 16) * BXR_ROWS + r) * 16 + j % 16];
+        tile[r * BXR_COLS + q * 32 + j] = uint16_t((byte & 0x80) << 8 | e << 7 | (byte & 0x7F));
+      }
+    }
+  for (uint32_t warp = 0; warp < 16; ++warp) {
+    if (warp_end[warp] > warp_end[warp + 1]) return false;
+    for (uint32_t i = warp_end[warp]; i < warp_end[warp + 1]; ++i) {
+      uint16_t v;
+      std::memcpy(&v, blob + BXW_LIST_AT + 2 * size_t(i), 2);
+      const uint32_t place = v & ((1u << BXW_PLACE_BITS) - 1), q = warp >> 2, rl = place >> 6;
+      const uint32_t unit = ((place >> 3) & 7u) ^ (rl & 7u), j = (unit & 3u) * 8 + (place & 7u);
+      if ((unit >> 2) != (q & 1u)) return false;
+      const int delta = int(int16_t(v)) >> BXW_PLACE_BITS;  // sign-extended 5-bit field
+      uint16_t& w = tile[((warp & 3) * 32 + rl) * BXR_COLS + q * 32 + j];
+      if (delta != BXW_DELTA_FAR) {
+        w = uint16_t(int(w) + delta * 128);
+        continue;
+      }
+      bool found = false;
+      for (uint32_t f = 0; f < n_far && !found; ++f) {
+        uint32_t x;
+        std::memcpy(&x, blob + far_at + 4 * size_t(f), 4);
+        if ((x & 0x7FFFu) == (warp << BXW_PLACE_BITS | place)) { w = uint16_t((w & 0x807Fu) | ((x >> 16) & 0xFFu) << 7); found = true; }
+      }
+      if (!found) return false;
+    }
+  }
+  return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -250,12 +377,13 @@ extern "C" {
 void bxr_free(void* p) { std::free(p); }
 
 // Builds the image.  workers = CTAs the kernels will run (one per SM); threads = host threads.
-// force_raw != 0 skips entropy coding (also chosen automatically when a chunk would not fit its slot).
+// layout = BXR_MODE_CODED (rANS exponent streams), BXR_MODE_WINDOW (fixed 3-bit codes) or BXR_MODE_RAW (no coding).
+// A chunk that does not fit its slot demotes the whole image: window -> coded -> raw.
 // Returns 0, 1 bad arguments, 2 out of memory, 3 other failure.  The image is malloc'ed; free with bxr_free.
 int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t workers, uint32_t threads,
-              uint32_t force_raw, const uint8_t* source_sha256, uint8_t** image, uint64_t* image_bytes) {
+              uint32_t layout, const uint8_t* source_sha256, uint8_t** image, uint64_t* image_bytes) {
   try {
-    if (!words || !rows || !cols || !workers || workers > 4096 || !image || !image_bytes) return 1;
+    if (!words || !rows || !cols || !workers || workers > 4096 || !image || !image_bytes || layout > BXR_MODE_WINDOW) return 1;
     if (!threads) threads = std::max(1u, std::thread::hardware_concurrency());
     const Source src{words, rows, cols};
     Plan plan = make_plan(rows, cols, workers);
@@ -267,9 +395,23 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     std::vector<uint32_t> lut(BXR_PROB_TOTAL, 0);
     std::vector<std::vector<uint8_t>> blobs(nblobs);
     std::vector<uint32_t> states(size_t(nitems) * BXR_STREAMS, BXR_STATE_LOW);
-    bool raw_mode = force_raw != 0;
+    bool raw_mode = layout == BXR_MODE_RAW;
+    bool window_mode = layout == BXR_MODE_WINDOW;
 
-    if (!raw_mode) {
+    if (window_mode) {
+      base = choose_window_bases(src, rows_pad, threads);
+      std::atomic<bool> overflow{false};
+      parallel_for(nblobs, threads, [&](uint32_t bi) {
+        if (overflow.load()) return;
+        if (!window_blob(src, bi / plan.chunks, bi % plan.chunks, base.data(), blobs[bi])) overflow.store(true);
+      });
+      if (overflow.load()) {
+        window_mode = false;
+        for (auto& b : blobs) b.clear();
+      }
+    }
+
+    if (!raw_mode && !window_mode) {
       base = choose_bases(src, rows_pad, threads);
       // pair statistics
       std::vector<std::vector<uint64_t>> local(threads, std::vector<uint64_t>(256, 0));
@@ -367,7 +509,8 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
 
     bxr_header h{};
     h.magic = BXR_MAGIC;
-    h.mode = raw_mode ? BXR_MODE_RAW : BXR_MODE_CODED;
+    h.mode = raw_mode ? BXR_MODE_RAW : window_mode ? BXR_MODE_WINDOW : BXR_MODE_CODED;
+    const bool coded = !raw_mode && !window_mode;
     h.rows = rows;
     h.cols = cols;
     h.row_blocks = plan.row_blocks;
@@ -377,11 +520,11 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     h.partial_slots = plan.partial_slots;
     uint64_t at = align16(sizeof(bxr_header));
     at = (at + 255) & ~uint64_t(255);
-    h.lut_at = at;            at += raw_mode ? 0 : sizeof(uint32_t) * BXR_PROB_TOTAL;
+    h.lut_at = at;            at += coded ? sizeof(uint32_t) * BXR_PROB_TOTAL : 0;
     h.base_at = at;           at = align16(at + rows_pad);
     h.items_at = at;          at = align16(at + sizeof(bxr_item) * nitems);
     h.worker_items_at = at;   at = align16(at + 4ull * (workers + 1));
-    h.states_at = at;         at = align16(at + (raw_mode ? 0 : 4ull * states.size()));
+    h.states_at = at;         at = align16(at + (coded ? 4ull * states.size() : 0));
     h.blob_index_at = at;     at = align16(at + 4ull * (nblobs + 1));
     at = (at + 255) & ~uint64_t(255);
     h.blobs_at = at;
@@ -391,17 +534,17 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     if ((run >> 4) > 0xFFFFFFFFull) return 3;
     index[nblobs] = uint32_t(run >> 4);
     h.total_bytes = at + run;
-    h.coded_bytes = run + (raw_mode ? 0 : 4ull * states.size()) + 4ull * (nblobs + 1);
+    h.coded_bytes = run + (coded ? 4ull * states.size() : 0) + 4ull * (nblobs + 1);
     if (source_sha256) std::memcpy(h.source_sha256, source_sha256, 32);
 
     auto* img = static_cast<uint8_t*>(std::calloc(size_t(h.total_bytes), 1));
     if (!img) return 2;
     std::memcpy(img, &h, sizeof h);
-    if (!raw_mode) std::memcpy(img + h.lut_at, lut.data(), sizeof(uint32_t) * BXR_PROB_TOTAL);
+    if (coded) std::memcpy(img + h.lut_at, lut.data(), sizeof(uint32_t) * BXR_PROB_TOTAL);
     std::memcpy(img + h.base_at, base.data(), rows_pad);
     std::memcpy(img + h.items_at, plan.items.data(), sizeof(bxr_item) * nitems);
     std::memcpy(img + h.worker_items_at, plan.worker_items.data(), 4ull * (workers + 1));
-    if (!raw_mode) std::memcpy(img + h.states_at, states.data(), 4ull * states.size());
+    if (coded) std::memcpy(img + h.states_at, states.data(), 4ull * states.size());
     std::memcpy(img + h.blob_index_at, index.data(), 4ull * (nblobs + 1));
     parallel_for(nblobs, threads, [&](uint32_t b) {
       std::memcpy(img + h.blobs_at + (uint64_t(index[b]) << 4), blobs[b].data(), blobs[b].size());
@@ -423,7 +566,7 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
     if (!img || !out || bytes < sizeof(bxr_header)) return 1;
     bxr_header h;
     std::memcpy(&h, img, sizeof h);
-    if (h.magic != BXR_MAGIC || h.total_bytes != bytes || !h.rows || !h.cols || h.mode > 1) return 1;
+    if (h.magic != BXR_MAGIC || h.total_bytes != bytes || !h.rows || !h.cols || h.mode > BXR_MODE_WINDOW) return 1;
     const auto* items = reinterpret_cast<const bxr_item*>(img + h.items_at);
     const auto* index = reinterpret_cast<const uint32_t*>(img + h.blob_index_at);
     auto put = [&](uint32_t row, uint32_t col, uint16_t w) {
@@ -442,8 +585,20 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
         }
       return 0;
     }
-    const auto* lut = reinterpret_cast<const uint32_t*>(img + h.lut_at);
     const uint8_t* base = img + h.base_at;
+    if (h.mode == BXR_MODE_WINDOW) {
+      std::vector<uint16_t> tile(size_t(BXR_ROWS) * BXR_COLS);
+      for (uint32_t rb = 0; rb < h.row_blocks; ++rb)
+        for (uint32_t c = 0; c < h.chunks; ++c) {
+          const size_t bi = size_t(rb) * h.chunks + c;
+          const uint8_t* blob = img + h.blobs_at + (uint64_t(index[bi]) << 4);
+          if (!window_unblob(blob, uint64_t(index[bi + 1] - index[bi]) << 4, base + size_t(rb) * BXR_ROWS, tile.data())) return 2;
+          for (uint32_t r = 0; r < BXR_ROWS; ++r)
+            for (uint32_t j = 0; j < BXR_COLS; ++j) put(rb * BXR_ROWS + r, c * BXR_COLS + j, tile[r * BXR_COLS + j]);
+        }
+      return 0;
+    }
+    const auto* lut = reinterpret_cast<const uint32_t*>(img + h.lut_at);
     const auto* states = reinterpret_cast<const uint32_t*>(img + h.states_at);
     for (uint32_t i = 0; i < h.items; ++i) {
       const bxr_item& it = items[i];

@@ -64,6 +64,45 @@
 #define BXR_MODE_CODED 0
 #define BXR_MODE_RAW 1 /* chunk blob = the 128x128 BF16 tile itself, already in UMMA operand order */
 #define BXR_RAW_TILE_BYTES 32768
+#define BXR_MODE_WINDOW 2 /* fixed 3-bit exponent codes inside an 8-binade row window; see below */
+
+/* Window mode.  Same geometry, work items, blob index and raw-byte order as the coded mode, but the exponent of
+ * a weight is a fixed 3-bit code: exponent = base[row] + code, base[row] in [0, 248].  A weight whose exponent
+ * lies outside its row window carries code 0 and an entry in the chunk's list that says by how much the word the
+ * decoder produced is off.  No entropy coder: no slot table, no stream states, no word segments; a decoder lane
+ * needs only masks, multiply-adds and byte permutes, and any lane of a warp can patch any of the warp's weights.
+ *
+ * A lane (phase q, row r) owns the 32 chunk columns [32q, 32q+32) of its row = 16 column pairs.  Its codes are
+ * three 32-bit words A, B, C (codes[j][q*128 + r], j = 0..2).  Word j holds pairs 5j..5j+4: pair 5j+k has the code
+ * of its even column in bits [1+3k, 4+3k) and the code of its odd column 16 bits higher, so that one mask and one
+ * multiply put both into packed-BF16 exponent position (bits 7..9 and 23..25).  Pair 15 is spread over the spare
+ * bits: bit 0 of A, B, C = bits 0, 1, 2 of the even column's code, bit 16 of A, B, C likewise for the odd column.
+ *
+ * Chunk blob in window mode (multiple of 16 bytes, at most BXR_BLOB_MAX):
+ *   [0,34)        u16 warp_end[17]     entries of decoder warp w = [warp_end[w], warp_end[w+1]); warp w covers
+ *                                      phase w/4, rows 32*(w%4) .. +31
+ *   [34,36)       u16 n_far
+ *   [64,16448)    u8  raw[8][128][16]  as in the coded mode
+ *   [16448,22592) u32 codes[3][512]
+ *   [22592, ...)  u16 entries          place[0,11) | delta[11,16).  place = where the weight's BF16 word sits in
+ *                                      the warp's 32 rows x 128 bytes of the operand tile, in 2-byte units:
+ *                                      row in warp * 64 + (16-byte unit ^ (row & 7)) * 8 + column & 7, with
+ *                                      unit = (q & 1) * 4 + (column in the lane's 32) / 8.  delta = true exponent
+ *                                      - base[row] as a 5-bit two's complement number (-15..-1 or 8..15); the
+ *                                      patch adds delta << 7 to the word.  delta = -16: see the far list
+ *   then, 4-byte aligned: u32 far[n_far] = warp << 11 | place, exponent << 16
+ */
+#define BXW_WARP_END_AT 0
+#define BXW_FAR_COUNT_AT 34
+#define BXW_RAW_AT 64
+#define BXW_CODES_AT (BXW_RAW_AT + BXR_RAW_BYTES)
+#define BXW_LIST_AT (BXW_CODES_AT + 3 * 4 * BXR_SEGMENTS)
+#define BXW_FAR_MAX 64
+#define BXW_ENTRY_MAX ((BXR_BLOB_MAX - BXW_LIST_AT - 4 * BXW_FAR_MAX - 16) / 2)
+#define BXW_PAIR_MASK 0x03800380u
+#define BXW_PLACE_BITS 11
+#define BXW_DELTA_FAR (-16)
+#define BXW_BASE_MAX 248
 
 /* Slot record of the pair table, 32 bits: n0[0,4) | bias[4,16) | n1[16,20) | freq[20,32).  freq <= 4095.
  * (record & 0x000F000F) * 128 is the pair of relative exponents in packed-BF16 position (an exception nibble is

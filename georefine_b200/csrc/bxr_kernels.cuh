@@ -41,10 +41,16 @@ struct BxrPowers {
   uint32_t p7, p16;  // 128, 65536
 };
 
+// The same device for the window-mode decoder: 1, 8, 64, 128, 256, 512.
+struct BxwPowers {
+  uint32_t p0, p3, p6, p7, p8, p9;
+};
+
 struct BxrArgs {
   // image
   const uint32_t* lut;
   BxrPowers k;
+  BxwPowers kw;
   const uint8_t* base;
   const bxr_item* items;
   const uint32_t* worker_items;
@@ -53,6 +59,7 @@ struct BxrArgs {
   const uint8_t* blobs;
   uint32_t rows, cols, row_blocks, chunks, workers;
   uint32_t raw;                // image holds plain pre-swizzled tiles (BXR_MODE_RAW): kUmma only, no decoders
+  uint32_t window;             // image holds fixed 3-bit exponent codes (BXR_MODE_WINDOW): served by bxw_kernel
   // call
   uint32_t m;                  // activation rows in this launch (<= NB, <= 8 for the GEMV)
   const __nv_bfloat16* x;      // GEMV only (the UMMA path reads x through the tensor map)

@@ -8,6 +8,7 @@
 #include "../../include/georefine_b200.h"
 #include "bctx_decode.cuh"
 #include "bxr_kernels.cuh"
+#include "bxw_kernels.cuh"
 
 namespace {
 
@@ -20,7 +21,7 @@ uint32_t batch_tile(uint32_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ?
 uint64_t counter_bytes(const bxr_header* h) { return (uint64_t(h->row_blocks) * 4 + 255) & ~uint64_t(255); }
 
 bool header_ok(const bxr_header* h) {
-  return h && h->magic == BXR_MAGIC && h->rows && h->cols && h->workers && h->mode <= 1 &&
+  return h && h->magic == BXR_MAGIC && h->rows && h->cols && h->workers && h->mode <= BXR_MODE_WINDOW &&
          h->row_blocks == (h->rows + BXR_ROWS - 1) / BXR_ROWS && h->chunks == (h->cols + BXR_COLS - 1) / BXR_COLS;
 }
 
@@ -29,6 +30,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   BxrArgs a{};
   a.lut = reinterpret_cast<const uint32_t*>(p + h->lut_at);
   a.k = BxrPowers{128u, 1u << 16};
+  a.kw = BxwPowers{1u, 8u, 64u, 128u, 256u, 512u};
   a.base = p + h->base_at;
   a.items = reinterpret_cast<const bxr_item*>(p + h->items_at);
   a.worker_items = reinterpret_cast<const uint32_t*>(p + h->worker_items_at);
@@ -41,6 +43,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   a.chunks = h->chunks;
   a.workers = h->workers;
   a.raw = h->mode == BXR_MODE_RAW;
+  a.window = h->mode == BXR_MODE_WINDOW;
   return a;
 }
 
@@ -77,6 +80,38 @@ int launch(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cuda_status(cudaLaunchKernelEx(&cfg, bxr_kernel<MODE, NB>, a, tmap));
+}
+
+// Window-mode images run bxw_kernel: same arguments, its own shared-memory plan.
+template <int MODE, int NB>
+cudaError_t prepare_window() {
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(bxw_kernel<MODE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BxwSmem<MODE, NB>::alloc));
+  if (e == cudaSuccess && dev < 64) done[dev] = true;
+  return e;
+}
+
+template <int MODE, int NB>
+int launch_window(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
+  cudaError_t e = prepare_window<MODE, NB>();
+  if (e != cudaSuccess) return cuda_status(e);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(a.workers);
+  cfg.blockDim = dim3(MODE == kUmma ? kThreadsUmma : kThreadsSimt);
+  cfg.dynamicSmemBytes = BxwSmem<MODE, NB>::alloc;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, bxw_kernel<MODE, NB>, a, tmap));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -132,7 +167,7 @@ int gemm_tile(BxrArgs a, const void* x, int64_t ldx, cudaStream_t stream) {
   CUtensorMap map;
   const int st = make_x_map(&map, x, ldx, a.m, a.cols, NB);
   if (st) return st;
-  return launch<kUmma, NB>(a, map, stream);
+  return a.window ? launch_window<kUmma, NB>(a, map, stream) : launch<kUmma, NB>(a, map, stream);
 }
 
 template <int M>
@@ -194,6 +229,7 @@ int grb_bxr_decode(const void* image, const bxr_header* h, uint16_t* out, uint32
   a.dense = out;
   a.status = status;
   CUtensorMap none{};
+  if (a.window) return launch_window<kDense, 8>(a, none, static_cast<cudaStream_t>(cuda_stream));
   return launch<kDense, 8>(a, none, static_cast<cudaStream_t>(cuda_stream));
 }
 
@@ -239,8 +275,9 @@ int grb_bxr_gemm(const void* image, const bxr_header* h, const void* x, int64_t 
 int grb_bxr_gemv(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
                  const void* bias, void* ws, uint64_t ws_bytes, uint32_t* status, void* cuda_stream) {
   if (m > uint32_t(kGemvMaxM)) return GRB_ERR_UNSUPPORTED;
-  // A raw-mode image has nothing to decode: it is served by the tensor-core path whatever the batch size.
-  if (header_ok(h) && h->mode == BXR_MODE_RAW) return grb_bxr_gemm(image, h, x, ldx, m, y, ldy, bias, ws, ws_bytes, status, cuda_stream);
+  // A raw-mode image has nothing to decode and a window-mode image decodes cheaply enough for the tensor-core
+  // pipeline to stay memory-bound at any batch size: both are served by that path.
+  if (header_ok(h) && h->mode != BXR_MODE_CODED) return grb_bxr_gemm(image, h, x, ldx, m, y, ldy, bias, ws, ws_bytes, status, cuda_stream);
   int st = check_linear(image, h, x, ldx, m, y, ldy, ws, ws_bytes, status, kGemvMaxM);
   if (st) return st;
   BxrArgs a = view_of(image, h);
@@ -297,7 +334,9 @@ static int static_scratch_address(void** out) {
 int grb_bxr_gemv_static(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
                         const void* bias, uint32_t* status, void* cuda_stream) {
   if (!header_ok(h)) return GRB_ERR_ARGUMENT;
-  const uint64_t need = counter_bytes(h) + uint64_t(h->partial_slots) * kGemvMaxM * BXR_ROWS * 4;
+  // coded images run the CUDA-core GEMV (8 batch rows of partial sums); the others the narrowest tensor-core tile
+  const uint64_t tile_rows = h->mode == BXR_MODE_CODED ? kGemvMaxM : 16;
+  const uint64_t need = counter_bytes(h) + uint64_t(h->partial_slots) * tile_rows * BXR_ROWS * 4;
   if (need > kStaticScratchBytes) return GRB_ERR_STATIC_LIMIT;
   void* scratch = nullptr;
   int st = static_scratch_address(&scratch);
@@ -318,6 +357,9 @@ int grb_kernel_attributes(int which, int out[5]) {
     case 2: e = cudaFuncGetAttributes(&fa, bxr_kernel<kGemv, 1>); break;
     case 3: e = cudaFuncGetAttributes(&fa, bxr_kernel<kUmma, 16>); break;
     case 4: e = cudaFuncGetAttributes(&fa, bxr_kernel<kUmma, 128>); break;
+    case 5: e = cudaFuncGetAttributes(&fa, bxw_kernel<kDense, 8>); break;
+    case 6: e = cudaFuncGetAttributes(&fa, bxw_kernel<kUmma, 16>); break;
+    case 7: e = cudaFuncGetAttributes(&fa, bxw_kernel<kUmma, 128>); break;
     default: return GRB_ERR_ARGUMENT;
   }
   if (e != cudaSuccess) return cuda_status(e);

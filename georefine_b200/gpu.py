@@ -99,10 +99,12 @@ class CudaContextTensor:
     ``gather_rows``) and, for rank-2 weights, the resident image the fused linear streams.
 
     ``resident_bytes`` counts every device allocation made here, the image and its scratch included.
-    ``fused=False`` skips the image (embedding tables that are only gathered).
+    ``fused=False`` skips the image (embedding tables that are only gathered); ``layout`` picks the image's layout
+    ("window": fixed 3-bit exponent codes, the default; "rans": entropy-coded exponent streams, 1-3 % smaller).
     """
 
-    def __init__(self, frame: bytes, *, stride: int = 1024, device="cuda:0", fused: bool = True, max_m: int = 128):
+    def __init__(self, frame: bytes, *, stride: int = 1024, device="cuda:0", fused: bool = True, max_m: int = 128,
+                 layout: str | None = None):
         import torch
 
         if not torch.cuda.is_available():
@@ -130,7 +132,7 @@ class CudaContextTensor:
         self.resident = None
         if fused and words is not None:
             self.resident = ResidentWeight.from_words(words, device=self.device, source_sha256=bytes.fromhex(self.source_sha256),
-                                                      max_m=max_m)
+                                                      max_m=max_m, **({} if layout is None else {"layout": layout}))
         self.resident_bytes = sum(t.numel() * t.element_size() for t in self.buffers.values()) + self.error.element_size()
         if self.resident is not None:
             self.resident_bytes += self.resident.resident_bytes

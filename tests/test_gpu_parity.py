@@ -91,7 +91,7 @@ def test_resident_decode_is_bit_exact(orc, oracle_coder, dev, shape, seed):
 
     words = orc.synthetic_weight_words(*shape, seed)
     frame = oracle_coder.encode(words)
-    t = CudaContextTensor(frame, device=dev)
+    t = CudaContextTensor(frame, device=dev, layout="rans")
     assert np.array_equal(oracle_coder.decode(frame), words)
     assert np.array_equal(_u16(t.resident.decode()), words)      # image walked by the fused kernels' decoder
     assert np.array_equal(_u16(t.decode()), words)               # unchanged streams
@@ -102,7 +102,7 @@ def test_resident_decode_special_words(dev):
     from georefine_b200.resident import ResidentWeight
 
     special = np.resize(np.array([0, 0x8000, 0x7F80, 0xFF80, 0x7FC1, 0xFFE5, 1, 0x8001], dtype=np.uint16), (64, 67))
-    r = ResidentWeight.from_words(special, dev)
+    r = ResidentWeight.from_words(special, dev, layout="rans")
     assert np.array_equal(_u16(r.decode()), special)
     # ordinary weights with 2 % zeros, denormals, infinities and NaNs: the exception lists of a coded image
     from oracle import bcx_oracle as orc_mod
@@ -110,11 +110,11 @@ def test_resident_decode_special_words(dev):
     rng = np.random.default_rng(17)
     at = rng.random(sprinkled.shape) < 0.02
     sprinkled[at] = rng.choice(special.ravel()[:8], size=int(at.sum()))
-    r = ResidentWeight.from_words(sprinkled, dev)
+    r = ResidentWeight.from_words(sprinkled, dev, layout="rans")
     assert r.mode == 0 and np.array_equal(_u16(r.decode()), sprinkled)
     finite = sprinkled.copy()
     finite[(finite & 0x7F80) == 0x7F80] = 0x3C00                      # keep zeros and denormals, drop inf/NaN
-    r = ResidentWeight.from_words(finite, dev)
+    r = ResidentWeight.from_words(finite, dev, layout="rans")
     x = torch.randn(8, 300, device=dev).to(torch.bfloat16)
     ref = _reference_product(finite, x)
     y, yv = r.linear(x), torch.empty(8, 200, device=dev, dtype=torch.bfloat16)
@@ -123,7 +123,7 @@ def test_resident_decode_special_words(dev):
     assert ((y.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
     assert ((yv.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
     every = np.arange(65536, dtype=np.uint16).reshape(256, 256)   # every BF16 pattern once
-    r = ResidentWeight.from_words(every, dev)
+    r = ResidentWeight.from_words(every, dev, layout="rans")
     if r.mode == 0:
         assert np.array_equal(_u16(r.decode()), every)
 
@@ -132,7 +132,7 @@ def test_resident_decode_flags_a_corrupt_image(orc, dev):
     from georefine_b200.resident import ResidentWeight, build_image
 
     words = orc.synthetic_weight_words(256, 512, 21)
-    image, h = build_image(words, 148)
+    image, h = build_image(words, 148, layout="rans")
     image[h.states_at + 8] ^= 0x40                                # host-injected: one stream starts from a wrong state
     r = ResidentWeight(image, dev, verify=False)
     with pytest.raises(ValueError):
@@ -151,7 +151,7 @@ def test_gemm_matches_reference_and_rows_do_not_depend_on_batch(orc, dev, shape,
     from georefine_b200.resident import ResidentWeight
 
     words = orc.synthetic_weight_words(*shape, seed)
-    r = ResidentWeight.from_words(words, dev, max_m=256)
+    r = ResidentWeight.from_words(words, dev, max_m=256, layout="rans")
     n, k = shape
     g = torch.Generator(device="cpu").manual_seed(100 + seed)
     xfull = torch.randn(200, k, generator=g).to(torch.bfloat16).to(dev)
@@ -174,7 +174,7 @@ def test_gemv_matches_reference_and_is_m_invariant(orc, dev, shape, seed):
     from georefine_b200.resident import ResidentWeight
 
     words = orc.synthetic_weight_words(*shape, seed)
-    r = ResidentWeight.from_words(words, dev)
+    r = ResidentWeight.from_words(words, dev, layout="rans")
     n, k = shape
     g = torch.Generator(device="cpu").manual_seed(200 + seed)
     xfull = torch.randn(8, k, generator=g).to(torch.bfloat16).to(dev)
@@ -201,7 +201,7 @@ def test_bias_strided_input_and_module_contract(orc, oracle_coder, dev):
     from georefine_b200.serving import BctxLinear
 
     words = orc.synthetic_weight_words(384, 256, 31)
-    t = CudaContextTensor(oracle_coder.encode(words), device=dev)
+    t = CudaContextTensor(oracle_coder.encode(words), device=dev, layout="rans")
     bias = torch.nn.Parameter(torch.randn(384, device=dev).to(torch.bfloat16), requires_grad=False)
     layer = BctxLinear(t, bias)
     assert (layer.out_features, layer.in_features) == (384, 256) and "weight" not in layer.state_dict()
@@ -226,7 +226,7 @@ def test_full_size_images_reproduce_their_source_digest(orc, dev, shape):
     from georefine_b200.resident import ResidentWeight
 
     words = orc.synthetic_weight_words(*shape, 1)
-    r = ResidentWeight.from_words(words, dev, verify=False)
+    r = ResidentWeight.from_words(words, dev, verify=False, layout="rans")
     got = _u16(r.decode())
     assert r.check_status() == 0
     assert hashlib.sha256(got.tobytes()).digest() == hashlib.sha256(words.tobytes()).digest()
@@ -239,7 +239,7 @@ def test_linearity_round_trip_at_full_size(orc, dev):
     from georefine_b200.resident import ResidentWeight
 
     words = orc.synthetic_weight_words(7168, 5120, 1)
-    r = ResidentWeight.from_words(words, dev, verify=False)
+    r = ResidentWeight.from_words(words, dev, verify=False, layout="rans")
     assert hashlib.sha256(_u16(r.decode()).tobytes()).digest() == bytes(r.header.source_sha256)
     x = torch.randn(2, 5120, device=dev).to(torch.bfloat16)
     xs = (x[0].float() + x[1].float()).to(torch.bfloat16)[None]
@@ -259,11 +259,11 @@ def test_raw_mode_images_decode_and_multiply(orc, oracle_coder, golden, dev):
 
     noise = np.random.default_rng(3).integers(0, 65536, (300, 256), dtype=np.uint16)
     noise = (noise & 0xBFFF).astype(np.uint16)                    # keep the exponents finite
-    r = ResidentWeight.from_words(noise, dev, max_m=256)
+    r = ResidentWeight.from_words(noise, dev, max_m=256, layout="rans")
     assert r.mode == 1
     assert np.array_equal(_u16(r.decode()), noise)
     forced = ResidentWeight.from_words(orc.synthetic_weight_words(256, 384, 8), dev, force_raw=True, max_m=256)
-    coded = ResidentWeight.from_words(orc.synthetic_weight_words(256, 384, 8), dev, max_m=256)
+    coded = ResidentWeight.from_words(orc.synthetic_weight_words(256, 384, 8), dev, max_m=256, layout="rans")
     assert forced.mode == 1 and coded.mode == 0
     x = torch.randn(200, 384, device=dev).to(torch.bfloat16)
     ya, yb = torch.empty(200, 256, device=dev, dtype=torch.bfloat16), torch.empty(200, 256, device=dev, dtype=torch.bfloat16)
@@ -285,7 +285,7 @@ def test_raw_mode_images_decode_and_multiply(orc, oracle_coder, golden, dev):
     t = CudaContextTensor(golden["uniform13x17.frame"].tobytes(), device=dev)
     words = (golden["uniform13x17.words"] & 0xBFFF).astype(np.uint16)
     assert t.mode == 1 and np.array_equal(_u16(t.resident.decode()), golden["uniform13x17.words"])
-    r17 = ResidentWeight.from_words(words, dev)
+    r17 = ResidentWeight.from_words(words, dev, layout="rans")
     x17 = torch.randn(5, 17, device=dev).to(torch.bfloat16)
     y17 = r17.linear(x17)
     ref = _reference_product(words, x17)

@@ -146,7 +146,7 @@ def test_lookup_tables_invert_every_slot(golden):
                                                 ((1, 1), 4, 148), ((513, 1024), 5, 37), ((256, 4096), 6, 148)])
 def test_resident_image_round_trips_and_plan_is_balanced(orc, shape, seed, workers):
     words = orc.synthetic_weight_words(*shape, seed)
-    image, h = resident.build_image(words, workers)
+    image, h = resident.build_image(words, workers, layout="rans")
     assert h.mode == 0 and h.rows == shape[0] and h.cols == shape[1] and h.total_bytes == image.size
     assert bytes(h.source_sha256) == hashlib.sha256(words.tobytes()).digest()
     assert np.array_equal(resident.decode_image_host(image), words)
@@ -163,16 +163,16 @@ def test_resident_image_round_trips_and_plan_is_balanced(orc, shape, seed, worke
 
 def test_resident_image_special_values_and_raw_fallback(orc):
     special = np.resize(np.array([0, 0x8000, 0x7F80, 0xFF80, 0x7FC1, 0xFFE5, 1, 0x8001], dtype=np.uint16), (64, 67))
-    image, h = resident.build_image(special, 9)          # half of these words lie outside any 15-binade window
+    image, h = resident.build_image(special, 9, layout="rans")          # half of these words lie outside any 15-binade window
     assert h.mode == 1 and np.array_equal(resident.decode_image_host(image), special)
     sprinkled = orc.synthetic_weight_words(200, 300, 17)    # ordinary weights with 2 % special values: exception lists
     rng = np.random.default_rng(17)
     at = rng.random(sprinkled.shape) < 0.02
     sprinkled[at] = rng.choice(special.ravel()[:8], size=int(at.sum()))
-    image, h = resident.build_image(sprinkled, 9)
+    image, h = resident.build_image(sprinkled, 9, layout="rans")
     assert h.mode == 0 and np.array_equal(resident.decode_image_host(image), sprinkled)
     noise = np.random.default_rng(0).integers(0, 65536, (256, 256), dtype=np.uint16)
-    image, h = resident.build_image(noise, 148)
+    image, h = resident.build_image(noise, 148, layout="rans")
     assert h.mode == 1 and np.array_equal(resident.decode_image_host(image), noise)
     image, h = resident.build_image(orc.synthetic_weight_words(128, 256, 1), 4, force_raw=True)
     assert h.mode == 1
@@ -180,7 +180,7 @@ def test_resident_image_special_values_and_raw_fallback(orc):
 
 def test_corrupt_resident_image_is_rejected_on_the_host(orc):
     words = orc.synthetic_weight_words(128, 256, 9)
-    image, h = resident.build_image(words, 3)
+    image, h = resident.build_image(words, 3, layout="rans")
     bad = image.copy()
     bad[h.states_at] ^= 1
     status = _native.lib().bxr_decode_host(bad.ctypes.data_as(_native.U8P), bad.size, np.empty_like(words).ctypes.data_as(_native.U16P))
@@ -189,3 +189,41 @@ def test_corrupt_resident_image_is_rejected_on_the_host(orc):
     bad[0] ^= 1
     with pytest.raises(ValueError):
         resident.decode_image_host(bad)
+
+
+@pytest.mark.parametrize("shape,seed,workers", [((128, 128), 0, 148), ((300, 200), 2, 148), ((64, 67), 3, 5),
+                                                ((1, 1), 4, 148), ((513, 1024), 5, 37), ((256, 4096), 6, 148)])
+def test_window_image_round_trips_on_the_host(orc, shape, seed, workers):
+    """Window layout (fixed 3-bit exponent codes): the host twin returns the source words; the plan is the coded one."""
+    words = orc.synthetic_weight_words(*shape, seed)
+    image, h = resident.build_image(words, workers, layout="window")
+    coded, hc = resident.build_image(words, workers, layout="rans")
+    assert h.mode == 2 and (h.rows, h.cols, h.items, h.partial_slots) == (hc.rows, hc.cols, hc.items, hc.partial_slots)
+    assert bytes(h.source_sha256) == hashlib.sha256(words.tobytes()).digest()
+    assert np.array_equal(resident.decode_image_host(image), words)
+    assert np.array_equal(image[h.items_at:h.items_at + 32 * h.items], coded[hc.items_at:hc.items_at + 32 * hc.items])
+
+
+def test_window_image_entries_far_list_and_fallbacks(orc):
+    special = np.array([0, 0x8000, 0x7F80, 0xFF80, 0x7FC1, 0xFFE5, 1, 0x8001, 0x0080, 0x7F00, 0x4F80, 0x1000], dtype=np.uint16)
+    words = orc.synthetic_weight_words(384, 640, 11)
+    rng = np.random.default_rng(11)
+    at = rng.random(words.shape) < 5e-4
+    words[at] = rng.choice(special, size=int(at.sum()))
+    words[9] = 0                                                # a row of zeros: every weight is an entry
+    words[100] = (words[100] & 0x807F) | (np.uint16(250) << 7)   # a row at the top of the exponent range
+    image, h = resident.build_image(words, 148, layout="window")
+    assert h.mode == 2 and np.array_equal(resident.decode_image_host(image), words)
+    blob0 = image[h.blobs_at:h.blobs_at + 64]
+    assert int(np.frombuffer(blob0[32:34].tobytes(), dtype=np.uint16)[0]) > 0        # entries exist in the first chunk
+    # corrupt entry bounds or a missing far record are refused by the host twin
+    bad = image.copy()
+    bad[h.blobs_at + 32:h.blobs_at + 34] = 0xFF
+    with pytest.raises(ValueError):
+        resident.decode_image_host(bad)
+    # too many exceptions for the slot: the builder demotes the image (entropy-coded, then raw)
+    noisy = words.copy()
+    at = rng.random(noisy.shape) < 0.2
+    noisy[at] = rng.choice(special, size=int(at.sum()))
+    image, h = resident.build_image(noisy, 148, layout="window")
+    assert h.mode in (0, 1) and np.array_equal(resident.decode_image_host(image), noisy)

@@ -23,7 +23,7 @@ def test_static_scratch_gemv_matches_the_workspace_gemv_twice_in_a_row(orc):
     lib = _native.lib()
     dev = torch.device("cuda:0")
     words = orc.synthetic_weight_words(1024, 4096, 41)      # 8 row blocks shared by 148 workers: many partial tiles
-    r = ResidentWeight.from_words(words, dev)
+    r = ResidentWeight.from_words(words, dev, layout="rans")   # the layout the CUDA-core GEMV decodes
     assert r.header.partial_slots > 0
     need = -(-r.header.row_blocks * 4 // 256) * 256 + r.header.partial_slots * 8 * 128 * 4
     assert need <= lib.grb_static_scratch_bytes()
@@ -55,7 +55,7 @@ def test_static_scratch_limit_is_refused_without_launching(orc):
     # built for 2048 workers, every 128x128 unit of a 4096 x 5120 weight is its own work item: 1280 shared
     # partial tiles, 5 MiB of GEMV scratch, more than the 4 MiB array holds
     words = orc.synthetic_weight_words(4096, 5120, 42)
-    image, h = build_image(words, 2048)
+    image, h = build_image(words, 2048, layout="rans")
     assert h.partial_slots * 8 * 128 * 4 > lib.grb_static_scratch_bytes()
     dev = torch.device("cuda:0")
     img = torch.from_numpy(image).to(dev)
