@@ -264,7 +264,11 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     }
     mbar_init(bar_lut, 1);
     mbar_init(bar_final, 4);  // one arrival per epilogue warp once its items are done
-    for (int i = 0; i < 3; ++i) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc + 16 * i), "r"(0u) : "memory");
+    // flags: abort at misc + 4, verdicts at misc + 8 and misc + 16 (misc + 0 receives the TMEM base address from the
+    // allocating warp and is left alone here)
+    asm volatile("st.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 4), "r"(0u) : "memory");
+    asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
+    for (int i = 1; i < 3; ++i) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc + 16 * i), "r"(0u) : "memory");
     mbar_fence_init();
   }
   if (MODE == kUmma && warp == kWarpMma) {

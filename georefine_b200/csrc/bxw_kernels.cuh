@@ -122,22 +122,33 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;
   constexpr uint32_t kXN = L::kX ? L::kX : 1;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < L::kIn; ++i) {
-      mbar_init(bar_in_full + 8 * i, 1);
-      mbar_init(bar_in_empty + 8 * i, kDecoderWarps);
+  // Work of this CTA, known from the arguments alone; the blob loader asks for its first offsets before anything
+  // else so that the first copy can leave as soon as the barriers exist.
+  const uint64_t units = uint64_t(args.row_blocks) * args.chunks;
+  const uint32_t unit_begin = uint32_t(units * worker / args.workers);
+  const uint32_t unit_count = uint32_t(units * (worker + 1) / args.workers) - unit_begin;
+  uint32_t first_i0 = 0, first_i1 = 0;
+  if (warp == kWinWarpLoader && unit_count) {
+    const uint32_t mine = unit_begin + min(uint32_t(lane), unit_count - 1);
+    first_i0 = __ldg(args.blob_index + mine);
+    first_i1 = __ldg(args.blob_index + mine + 1);
+  }
+  if (warp == 0) {  // one barrier per lane
+    static_assert(L::nbars <= 32, "one lane per barrier");
+    const uint32_t i = lane;
+    uint32_t count = 1;                                                          // in_full, op_empty, x_full
+    if (i >= uint32_t(L::kIn) && i < 2u * L::kIn) count = kDecoderWarps;          // in_empty
+    else if (i >= 2u * L::kIn && i < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
+    else if (i >= 2u * L::kIn + 2 * L::kOp + L::kX) {
+      const uint32_t j = i - (2u * L::kIn + 2 * L::kOp + L::kX);                  // acc_full x2, acc_empty x2, final
+      count = j < 2 ? 2u : 4u;                                                   // both MMA issuers / the epilogue warps
     }
-    for (int i = 0; i < L::kOp; ++i) {
-      mbar_init(bar_op_full + 8 * i, kDecoderWarps + 1);  // the decoder warps + the activation loader's go-ahead
-      mbar_init(bar_op_empty + 8 * i, 1);
-    }
-    for (int i = 0; i < L::kX; ++i) mbar_init(bar_x_full + 8 * i, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_acc_full + 8 * i, 2);  // both MMA issuers
-      mbar_init(bar_acc_empty + 8 * i, 4);
-    }
-    mbar_init(bar_final, 4);  // one arrival per epilogue warp once its items are done
-    for (int i = 0; i < 3; ++i) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc + 16 * i), "r"(0u) : "memory");
+    if (i < L::nbars) mbar_init(ctx.bars + 8 * i, count);
+    // flags: abort at misc + 4, epilogue verdict at misc + 8, final verdict at misc + 16 (misc + 0 receives the TMEM
+    // base address from the allocating warp and is left alone here)
+    if (i == 0) asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
+    if (i == 1) asm volatile("st.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 4), "r"(0u) : "memory");
+    if (i == 2 || i == 3) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc + 16 * (i - 1)), "r"(0u) : "memory");
     mbar_fence_init();
   }
   if (MODE == kUmma && warp == kWinWarpMma) {
@@ -155,9 +166,6 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   if (MODE == kUmma) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(smem + L::misc));
 
   const uint32_t item_begin = args.worker_items[worker], item_end = args.worker_items[worker + 1];
-  const uint64_t units = uint64_t(args.row_blocks) * args.chunks;
-  const uint32_t unit_begin = uint32_t(units * worker / args.workers);
-  const uint32_t unit_count = uint32_t(units * (worker + 1) / args.workers) - unit_begin;
 
   if (warp < kDecoderWarps) {
     // ------------------------------------------------------------------ decoders: 32 weights per lane and chunk
@@ -286,8 +294,12 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     // ------------------------------------------------------------------ chunk blobs, one bulk copy each
     uint32_t issued = 0;
     for (uint32_t u0 = 0; u0 < unit_count; u0 += 32) {
-      const uint32_t mine = unit_begin + min(u0 + lane, unit_count - 1);
-      const uint32_t i0 = __ldg(args.blob_index + mine), i1 = __ldg(args.blob_index + mine + 1);
+      uint32_t i0 = first_i0, i1 = first_i1;
+      if (u0) {
+        const uint32_t mine = unit_begin + min(u0 + lane, unit_count - 1);
+        i0 = __ldg(args.blob_index + mine);
+        i1 = __ldg(args.blob_index + mine + 1);
+      }
       const uint32_t n = min(32u, unit_count - u0);
       bool live = true;
       for (uint32_t i = 0; i < n && live; ++i) {
