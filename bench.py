@@ -41,9 +41,11 @@ LINEARS = [("qkv", 7168, HIDDEN, "col", [5120, 1024, 1024]), ("o", HIDDEN, HIDDE
            ("gate_up", 2 * FFN, HIDDEN, "col", [FFN, FFN]), ("down", HIDDEN, FFN, "row", None)]
 BATCHES = (1, 64, 128)
 SEED = 1
-# dram__bytes_read+write over algorithmic bytes of one launch, from the ncu capture summarised in
-# profiles/bxr_kernel_gemm_m1_down_5120x17408.md (121.7 MB read + 5.5 MB written for 121.6 MB algorithmic)
-DRAM_TRAFFIC_RATIO = 1.05
+# dram__bytes_read+write over algorithmic bytes of one launch, from the ncu captures summarised under profiles/:
+# window layout, the step's top launch (gate|up at M = 128): 261.4 MB read + 14.2 MB written for 260.8 MB algorithmic
+# (profiles/bxw_kernel_gemm_m128_gate_up_34816x5120.md); rans layout: 122.2 + 3.4 MB for 122.0 MB
+# (profiles/bxr_kernel_gemm_m1_down_5120x17408.md).  The excess is the FP32 partial tiles of split row blocks.
+DRAM_TRAFFIC_RATIO = {"window": 1.057, "rans": 1.03}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -415,7 +417,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES)},
         "gpu_launches": layer.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO), "peak_source": peak_kind,
+                     "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO[args.layout]), "peak_source": peak_kind,
                      "kernel": ("bxw_kernel" if args.layout == "window" else "bxr_kernel") + "<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
                      "top_launch": {"linear": top[0], "m": top[1], "ms": round(ktimes[top], 4), "algorithmic_bytes": top_bytes,
                                     "GBps": round(top_bytes / ktimes[top] / 1e6, 1)}},
