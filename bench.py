@@ -271,6 +271,38 @@ class Layer:
             self.y_host[m].copy_(y, non_blocking=True)   # the down projection's output
         torch.cuda.current_stream().synchronize()
 
+    def e2e_graph(self):
+        """The end-to-end step as one CUDA graph, the way the reference's serving engines replay a whole decode step
+        (glc_serve/fastdec.py capture/replay): the pinned-host -> device copies of every batch run on a side stream and
+        overlap the launches of the batches before them, the descriptor calls and the device -> host copies of the
+        results follow on the main stream.  Single rank only (no collective is ever captured).  Returns a callable that
+        replays the graph and waits until the results are in host memory."""
+        import torch
+
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream(self.device)
+        with torch.cuda.graph(graph):
+            main = torch.cuda.current_stream()
+            side.wait_stream(main)
+            ready = {}
+            with torch.cuda.stream(side):
+                for m in BATCHES:
+                    for k in (HIDDEN, FFN):
+                        self.x[(m, k)].copy_(self.x_host[(m, k)], non_blocking=True)
+                    ready[m] = torch.cuda.Event()
+                    ready[m].record(side)
+            for m in BATCHES:
+                main.wait_event(ready[m])
+                for e in self.entries:
+                    e["res"](self.xv[(m, e["name"])], e["y"][m])
+                self.y_host[m].copy_(self.entries[-1]["y"][m], non_blocking=True)   # the down projection's output
+            main.wait_stream(side)
+
+        def step():
+            graph.replay()
+            torch.cuda.current_stream().synchronize()
+
+        return step
+
     def status(self):
         return sum(e["res"].check_status() for e in self.entries)
 
@@ -384,7 +416,17 @@ def run_ours(args):
             step_fn, launch = seg, "cuda_graph segments + eager all-reduce"
     with ClockSampler(local) as clocks:
         ms = timed(step_fn, args.steps, args.warmup, world)
-    ms_e2e = timed(layer.step_e2e, args.steps, args.warmup, world)
+    e2e_fn, e2e_launch = layer.step_e2e, "eager"
+    if not args.no_graph and world == 1:
+        try:
+            layer.step_e2e()
+            e2e_fn, e2e_launch = layer.e2e_graph(), "cuda_graph, copies on a side stream"
+        except Exception as exc:  # noqa: BLE001
+            e2e_launch = f"eager (graph capture failed: {type(exc).__name__})"
+    ms_e2e = timed(e2e_fn, args.steps, args.warmup, world)
+    y_check = [layer.y_host[m].clone() for m in BATCHES]
+    layer.step_e2e()                                     # the eager public-API path must land the same outputs
+    e2e_same = all(bool((a.view(torch.int16) == layer.y_host[m].view(torch.int16)).all()) for a, m in zip(y_check, BATCHES))
     ktimes = kernel_times(layer, max(2, min(args.steps, 10)))
     status = layer.status()
 
@@ -414,7 +456,8 @@ def run_ours(args):
                    "l2": "coded working set ~440 MB exceeds the 126 MB L2; no flush between iterations",
                    "resident_format": "BXR1/" + args.layout, "launch": launch, "status_word": status},
         "e2e": {"value": round(dense / (ms_e2e * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms_e2e, 4),
-                "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES)},
+                "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES),
+                "launch": e2e_launch, "outputs_match_eager_path": e2e_same},
         "gpu_launches": layer.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO[args.layout]), "peak_source": peak_kind,
