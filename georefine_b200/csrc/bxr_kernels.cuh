@@ -99,6 +99,7 @@ struct RoleCtx {
   uint32_t bars;
   uint32_t abort_addr; // shared address of the abort flag
   uint32_t* status;
+  bool suspend = true;  // barrier probes may park the thread (see mbar_try_wait)
   __device__ __forceinline__ bool aborted() const {
     uint32_t v;
     asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(abort_addr));
@@ -110,7 +111,7 @@ struct RoleCtx {
   }
   // Bounded wait; on expiry marks the CTA aborted.
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) const {
-    if (mbar_wait(bar, parity)) return true;
+    if (mbar_wait(bar, parity, suspend)) return true;
     abort(kStatusTimeout);
     return false;
   }

@@ -114,6 +114,7 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   ctx.bars = smem + L::bars;
   ctx.abort_addr = smem + L::misc + 4;
   ctx.status = args.status;
+  ctx.suspend = false;  // this pipeline is latency-bound: plain probes wake up sooner
   const uint32_t bar_in_full = ctx.bars, bar_in_empty = bar_in_full + 8 * L::kIn;
   const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
   const uint32_t bar_x_full = bar_op_empty + 8 * L::kOp;

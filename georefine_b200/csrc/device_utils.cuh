@@ -39,29 +39,40 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// One probe of the barrier.  The hardware may suspend the thread for up to kSuspendHintNs while the phase
-// is incomplete, which keeps waiting warps out of the issue slots the decoders need.
 constexpr uint32_t kSuspendHintNs = 20000;
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One probe of the barrier.  `suspend`: let the hardware park the thread for up to kSuspendHintNs while the phase is incomplete.  That keeps
+// waiting warps out of the issue slots (it pays when the decoders are short of them: the rANS kernels) at the price
+// of a slower wake-up (it costs a few per cent where the pipeline is latency-bound: the window kernels).
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, bool suspend = true) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
-      : "memory");
+  if (suspend) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 // Waits for the phase with the given parity to complete.  False after kWaitLimitNs: the caller must
 // record kStatusTimeout and unwind.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, bool suspend = true) {
+  if (mbar_try_wait(bar, parity, suspend)) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait(bar, parity, suspend)) return true;
     if (global_ns() - t0 > kWaitLimitNs) return false;
   }
 }
