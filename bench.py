@@ -274,8 +274,8 @@ class Layer:
     def e2e_graph(self):
         """The end-to-end step as one CUDA graph, the way the reference's serving engines replay a whole decode step
         (glc_serve/fastdec.py capture/replay): the pinned-host -> device copies of every batch run on a side stream and
-        overlap the launches of the batches before them, the descriptor calls and the device -> host copies of the
-        results follow on the main stream.  Single rank only (no collective is ever captured).  Returns a callable that
+        overlap the launches of the batches before them, the descriptor calls follow on the main stream, and each
+        batch's result goes back to the host on the side stream while the next batch runs.  Single rank only (no collective is ever captured).  Returns a callable that
         replays the graph and waits until the results are in host memory."""
         import torch
 
@@ -294,7 +294,11 @@ class Layer:
                 main.wait_event(ready[m])
                 for e in self.entries:
                     e["res"](self.xv[(m, e["name"])], e["y"][m])
-                self.y_host[m].copy_(self.entries[-1]["y"][m], non_blocking=True)   # the down projection's output
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(side):   # the down projection's output goes back while the next batch runs
+                    side.wait_event(done)
+                    self.y_host[m].copy_(self.entries[-1]["y"][m], non_blocking=True)
             main.wait_stream(side)
 
         def step():
