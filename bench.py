@@ -45,7 +45,7 @@ SEED = 1
 # window layout, the step's top launch (gate|up at M = 128): 261.4 MB read + 14.2 MB written for 260.8 MB algorithmic
 # (profiles/bxw_kernel_gemm_m128_gate_up_34816x5120.md); rans layout: 122.2 + 3.4 MB for 122.0 MB
 # (profiles/bxr_kernel_gemm_m1_down_5120x17408.md).  The excess is the FP32 partial tiles of split row blocks.
-DRAM_TRAFFIC_RATIO = {"window": 1.057, "rans": 1.03}
+DRAM_TRAFFIC_RATIO = {"window4": 1.057, "window": 1.057, "rans": 1.03}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -170,7 +170,7 @@ def cpu_reference_run(sample_rows, steps, warmup, threads):
 class Layer:
     """The four linears of one decoder layer on this rank, as resident images (tensor-parallel when world > 1)."""
 
-    def __init__(self, rank, world, device, layout="window"):
+    def __init__(self, rank, world, device, layout="window4"):
         import torch
 
         from georefine_b200 import tp
@@ -465,13 +465,13 @@ def run_ours(args):
         "gpu_launches": layer.launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO[args.layout]), "peak_source": peak_kind,
-                     "kernel": ("bxw_kernel" if args.layout == "window" else "bxr_kernel") + "<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
+                     "kernel": {"window4": "bxq_kernel", "window": "bxw_kernel", "rans": "bxr_kernel"}[args.layout] + "<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
                      "top_launch": {"linear": top[0], "m": top[1], "ms": round(ktimes[top], 4), "algorithmic_bytes": top_bytes,
                                     "GBps": round(top_bytes / ktimes[top] / 1e6, 1)}},
         "per_m": per_m,
         "gemv_m1": {"kernel_ms": round(gemv_ms, 4), "coded_GBps": round(gemv_bytes / gemv_ms / 1e6, 1),
                     "frac_of_hbm_peak": round(gemv_bytes / gemv_ms / 1e6 / peak, 4),
-                    "note": "grb_bxr_gemv outside the timed step: CUDA-core kernel for the rans layout, the tensor-core kernel at its narrowest tile for the window layout"},
+                    "note": "grb_bxr_gemv outside the timed step: CUDA-core kernel for the rans layout, the tensor-core kernel at its narrowest tile for the window layouts"},
         "clocks": clocks.summary(),
     }
     if rank == 0 and world == 1:
@@ -596,8 +596,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
     ap.add_argument("--sweep", action="store_true", help="per shape and batch size: fused gemm / gemv against torch.matmul on "
                                                         "the dense weights, one JSON line per shape")
-    ap.add_argument("--layout", choices=("rans", "window"), default="window",
-                    help="resident layout of the weights: entropy-coded exponent streams or fixed 3-bit window codes")
+    ap.add_argument("--layout", choices=("rans", "window", "window4"), default="window4",
+                    help="resident layout of the weights: fixed 4-bit window codes (default), fixed 3-bit window codes, or "
+                         "entropy-coded exponent streams")
     ap.add_argument("--case", default=None, help="profiling aid: KIND:M:NxK (KIND = gemm, gemv or decode) runs that one "
                                                  "launch --steps times on a synthetic weight and exits")
     args = ap.parse_args()

@@ -1,0 +1,415 @@
+// Fused kernels over wide-window images (bxr_format.h, BXR_MODE_WINDOW4): 4-bit exponent codes inside a 16-binade
+// row window, so that a weight outside its window is a rarity (fewer than one in ten thousand on Gaussian rows) and
+// the decoded words never have to touch shared memory:
+//   * kUmma  : a lane holds the 32 weights of its row and phase in 16 registers and writes them with one tcgen05.st
+//              into tensor memory, where tcgen05.mma takes them as its A operand (M = 128 weight rows; the batch is
+//              N, read from shared memory).  Shared memory carries only what comes from outside the SM: chunk blobs
+//              and activation tiles.  (In the 3-bit window kernel the operand tile lives in shared memory, and its
+//              stores plus the tensor core's reads of it are more than 40 % of all shared-memory traffic, which sets
+//              that kernel's pace; its per-chunk exception patching is what keeps it from using tensor memory: done
+//              in registers it costs more instructions than the decode itself.)
+//   * kDense : decode twin (parity tests, ResidentWeight.decode).
+// Same persistent, warp-specialised pipeline and work partition as the other fused kernels; any batch size, the
+// batch of one padded to the narrowest tile.
+#pragma once
+#include "bxr_kernels.cuh"
+
+namespace grb {
+
+constexpr int kWideWarpLoader = 16;    // bulk copies of chunk blobs
+constexpr int kWideWarpMma = 17;       // TMEM owner and MMA issuer
+constexpr int kWideWarpXLoader = 18;   // TMA loads of activation tiles
+                                       // warp 19 idles so that the epilogue warps keep warp % 4 = TMEM lane quarter
+constexpr int kWideWarpEpilogue = 20;  // 4 warps
+
+// Tensor memory: columns [0, 2 NB) two accumulators (one item being multiplied, one being drained); columns
+// [256, 512) the decoded weights of kWideStages chunks, 64 columns each (two 128 x 64 atoms, two BF16 per column).
+constexpr uint32_t kWideTmemCols = 512;
+constexpr uint32_t kWideOperandCol = 256;
+constexpr int kWideStages = 4;
+
+// Shared-memory plan: a ring of chunk blobs and a ring of activation tiles (two NB x 64 atoms per chunk), the
+// latter requested kXLag chunks ahead of the weights they will meet (they come from L2 with a latency of about a
+// microsecond).
+template <int MODE, int NB>
+struct BxqSmem {
+  static constexpr int kOp = (MODE == kUmma) ? kWideStages : 0;
+  static constexpr int kX = (MODE == kUmma) ? (NB <= 64 ? 4 : 3) : 0;
+  static constexpr int kXLag = 2;
+  static constexpr uint32_t kXStage = 2 * NB * 128;
+  static constexpr uint32_t kReserve = 1024 /* alignment slack */ + 512 /* barriers, flags */;
+  static constexpr int kInFit = int((232448u - kReserve - kX * kXStage) / BXQ_BLOB_MAX);
+  static constexpr int kIn = kInFit > 7 ? 7 : kInFit;   // (more barriers would not fit the one-per-lane set-up)
+  static constexpr uint32_t xs = 0;
+  static constexpr uint32_t in = xs + kX * kXStage;
+  static constexpr uint32_t bars = in + kIn * BXQ_BLOB_MAX;
+  // barrier order: in_full, in_empty [kIn each]; op_full, op_empty [kOp each]; x_full [kX]; acc_full, acc_empty
+  // [2 each]; final
+  static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1;
+  static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, verdict
+  static constexpr uint32_t total = misc + 48;
+  static constexpr uint32_t alloc = total + 1024;
+  static_assert(MODE != kUmma || kIn >= 4, "ring too shallow");
+  // what keeps the activation loader at most one barrier phase behind the MMA issuer (see its role below)
+  static_assert(MODE != kUmma || (kXLag < kX && kOp + kXLag + 1 > kX), "activation ring and lag do not fit the operand ring");
+  static_assert(MODE != kUmma || 2 * NB <= int(kWideOperandCol), "accumulators overlap the operand columns");
+  static_assert(nbars <= 32, "one lane per barrier at set-up");
+  static_assert(8 * nbars + 64 <= 512, "barrier area");
+  static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
+};
+
+// A code word holds four column pairs: pair k has the code of its even column in bits [4k, 4k+4) and that of its odd
+// column 16 bits higher.  One mask and one multiply-add (whose addend is the row base in both halves) put a pair into
+// packed-BF16 exponent position; `hi` is the word shifted right by 8, which brings pairs 2 and 3 to where pairs 0
+// and 1 are.  The mask runs on the integer pipe, the multiply-add on the FMA pipe (the multipliers are kernel
+// parameters so that the compiler does not turn them back into shifts).
+template <int K>
+__device__ __forceinline__ uint32_t bxq_exponents(uint32_t lo, uint32_t hi, const BxwPowers& p, uint32_t base2) {
+  if constexpr (K == 0) return (lo & BXQ_PAIR_MASK) * p.p7 + base2;
+  else if constexpr (K == 1) return (lo & (BXQ_PAIR_MASK << 4)) * p.p3 + base2;
+  else if constexpr (K == 2) return (hi & BXQ_PAIR_MASK) * p.p7 + base2;
+  else return (hi & (BXQ_PAIR_MASK << 4)) * p.p3 + base2;
+}
+// raw bytes (sign << 7 | mantissa) of two columns merged with their exponents
+__device__ __forceinline__ uint32_t bxq_join(uint32_t raw4, uint32_t selector, uint32_t exponents) {
+  return (__byte_perm(raw4, 0, selector) & 0x807F807Fu) | exponents;
+}
+// The 32 weights of a lane, two per register in column order: four code words and the raw bytes of its two
+// 16-column pieces.
+__device__ __forceinline__ void bxq_decode32(const uint32_t (&w)[4], const uint4& rf, const uint4& rb, const BxwPowers& p,
+                                             uint32_t base2, uint32_t (&out)[16]) {
+  const uint32_t raw[8] = {rf.x, rf.y, rf.z, rf.w, rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t lo = w[j], hi = w[j] >> 8;
+    out[4 * j + 0] = bxq_join(raw[2 * j], 0x1100, bxq_exponents<0>(lo, hi, p, base2));
+    out[4 * j + 1] = bxq_join(raw[2 * j], 0x3322, bxq_exponents<1>(lo, hi, p, base2));
+    out[4 * j + 2] = bxq_join(raw[2 * j + 1], 0x1100, bxq_exponents<2>(lo, hi, p, base2));
+    out[4 * j + 3] = bxq_join(raw[2 * j + 1], 0x3322, bxq_exponents<3>(lo, hi, p, base2));
+  }
+}
+// An exception entry applied to the registers of the lane that owns it: the exponent field of one half of one
+// register is replaced.  The register index is data, so the choice is sixteen predicated operations; this runs only
+// for the rare warp that has entries at all.
+__device__ __forceinline__ void bxq_patch(uint32_t (&out)[16], uint32_t column, uint32_t exponent) {
+  const uint32_t reg = column >> 1, sh = (column & 1u) ? 16u : 0u;
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    if (reg == uint32_t(i)) out[i] = (out[i] & ~(0x7F80u << sh)) | (exponent & 0xFFu) << (7 + sh);
+}
+
+template <int MODE, int NB>
+__global__ void __launch_bounds__(MODE == kUmma ? kThreadsUmma : kThreadsSimt, 1)
+bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
+  using L = BxqSmem<MODE, NB>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t worker = blockIdx.x;
+
+  RoleCtx ctx;
+  ctx.smem = smem;
+  ctx.bars = smem + L::bars;
+  ctx.abort_addr = smem + L::misc + 4;
+  ctx.status = args.status;
+  ctx.suspend = false;  // this pipeline is latency-bound: plain probes wake up sooner
+  const uint32_t bar_in_full = ctx.bars, bar_in_empty = bar_in_full + 8 * L::kIn;
+  const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
+  const uint32_t bar_x_full = bar_op_empty + 8 * L::kOp;
+  const uint32_t bar_acc_full = bar_x_full + 8 * L::kX, bar_acc_empty = bar_acc_full + 16, bar_final = bar_acc_empty + 16;
+  constexpr uint32_t kTmemCols = kWideTmemCols;
+  constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;
+  constexpr uint32_t kXN = L::kX ? L::kX : 1;
+
+  // Work of this CTA, known from the arguments alone; the blob loader asks for its first offsets before anything
+  // else so that the first copy can leave as soon as the barriers exist.
+  const uint64_t units = uint64_t(args.row_blocks) * args.chunks;
+  const uint32_t unit_begin = uint32_t(units * worker / args.workers);
+  const uint32_t unit_count = uint32_t(units * (worker + 1) / args.workers) - unit_begin;
+  uint32_t first_i0 = 0, first_i1 = 0;
+  if (warp == kWideWarpLoader && unit_count) {
+    const uint32_t mine = unit_begin + min(uint32_t(lane), unit_count - 1);
+    first_i0 = __ldg(args.blob_index + mine);
+    first_i1 = __ldg(args.blob_index + mine + 1);
+  }
+  if (warp == 0) {  // one barrier per lane
+    static_assert(L::nbars <= 32, "one lane per barrier");
+    const uint32_t i = lane;
+    uint32_t count = 1;                                                          // in_full, op_empty, x_full
+    if (i >= uint32_t(L::kIn) && i < 2u * L::kIn) count = kDecoderWarps;          // in_empty
+    else if (i >= 2u * L::kIn && i < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
+    else if (i >= 2u * L::kIn + 2 * L::kOp + L::kX) {
+      const uint32_t j = i - (2u * L::kIn + 2 * L::kOp + L::kX);                  // acc_full x2, acc_empty x2, final
+      count = j < 2 ? 1u : 4u;                                                   // the MMA issuer's commit / the epilogue warps
+    }
+    if (i < L::nbars) mbar_init(ctx.bars + 8 * i, count);
+    // flags: abort at misc + 4, epilogue verdict at misc + 8, final verdict at misc + 16 (misc + 0 receives the TMEM
+    // base address from the allocating warp and is left alone here)
+    if (i == 0) asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
+    if (i == 1) asm volatile("st.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 4), "r"(0u) : "memory");
+    if (i == 2 || i == 3) asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(smem + L::misc + 16 * (i - 1)), "r"(0u) : "memory");
+    mbar_fence_init();
+  }
+  if (MODE == kUmma && warp == kWideWarpMma) {
+    tmem_alloc(smem + L::misc, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // The image is never written by a kernel: everything up to the first access to x, bias, y or the workspace may
+  // overlap the tail of the previous kernel in the stream.
+  grid_dependents_may_launch();
+  if (MODE == kDense) grid_dependency_wait();
+  uint32_t tmem_base = 0;
+  if (MODE == kUmma) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(smem + L::misc));
+
+  const uint32_t item_begin = args.worker_items[worker], item_end = args.worker_items[worker + 1];
+
+  if (warp < kDecoderWarps) {
+    // ------------------------------------------------------------------ decoders: 32 weights per lane and chunk
+    const uint32_t q = warp >> 2, rg = warp & 3, r = rg * 32 + lane;
+    uint32_t s = 0, ph = 0;    // input ring slot of the current chunk and its phase parity
+    uint32_t so = 0, pho = 0;  // operand stage (tensor memory) of the current chunk
+    const uint32_t raw_at = BXQ_RAW_AT + ((2 * q) * BXR_ROWS + r) * 16;
+    const uint32_t code_at = BXQ_CODES_AT + 4 * (q * BXR_ROWS + r);
+    // this lane's 16 operand columns: lane = row, columns = its 32 weights inside the chunk's atom
+    const uint32_t operand_at = ((rg * 32u) << 16) + kWideOperandCol + (q >> 1) * 32 + (q & 1) * 16;
+    bool live = true;
+    for (uint32_t it = item_begin; it < item_end && live; ++it) {
+      const bxr_item item = args.items[it];
+      const uint32_t row = item.row_block * BXR_ROWS + r;
+      const uint32_t base2 = uint32_t(args.base[row]) * 0x00800080u;
+      for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c) {
+        if (!ctx.wait(bar_in_full + 8 * s, ph)) { live = false; break; }
+        const uint32_t blob = smem + L::in + s * BXQ_BLOB_MAX;
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = lds32(blob + code_at + 4 * BXR_SEGMENTS * j);
+        const uint4 raw_f = lds128(blob + raw_at);
+        const uint4 raw_b = lds128(blob + raw_at + BXR_ROWS * 16);
+        const uint32_t e_lo = lds_u16(blob + BXQ_WARP_END_AT + 2 * warp);
+        const uint32_t e_hi = min(lds_u16(blob + BXQ_WARP_END_AT + 2 * warp + 2), uint32_t(BXQ_ENTRY_MAX));
+        uint32_t out[16];
+        bxq_decode32(w, raw_f, raw_b, args.kw, base2, out);
+        // Exceptions (weights outside their row window): rare.  Every lane reads the same entry; its owner acts.
+        // Corrupt bounds are clamped so that every read stays inside the slot.
+        for (uint32_t i = e_lo; i < e_hi; ++i) {
+          const uint32_t v = lds32(blob + BXQ_LIST_AT + 4 * i);
+          if (((v >> 5) & 31u) == uint32_t(lane)) bxq_patch(out, v & 31u, v >> 16);
+        }
+        __syncwarp();   // every lane has what it needs from the blob: hand the slot back
+        if (lane == 0) mbar_arrive(bar_in_empty + 8 * s);
+        if (MODE == kUmma) {
+          if (!ctx.wait(bar_op_empty + 8 * so, pho ^ 1)) { live = false; break; }
+          tc_fence_after();
+          tmem_st16(tmem_base + operand_at + so * 64, out);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_op_full + 8 * so);
+          if (++so == kOpN) { so = 0; pho ^= 1; }
+        } else if (row < args.rows) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t col = c * BXR_COLS + q * 32 + i * 8;
+            uint16_t* dst = args.dense + size_t(row) * args.cols + col;
+            if (col + 8 <= args.cols && (args.cols & 7) == 0) {
+              *reinterpret_cast<uint4*>(dst) = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+            } else {
+              for (int e = 0; e < 8; ++e)
+                if (col + e < args.cols) dst[e] = uint16_t(out[4 * i + (e >> 1)] >> (16 * (e & 1)));
+            }
+          }
+        }
+        if (++s == L::kIn) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == kWideWarpLoader) {
+    // ------------------------------------------------------------------ chunk blobs, one bulk copy each
+    uint32_t issued = 0;
+    for (uint32_t u0 = 0; u0 < unit_count; u0 += 32) {
+      uint32_t i0 = first_i0, i1 = first_i1;
+      if (u0) {
+        const uint32_t mine = unit_begin + min(u0 + lane, unit_count - 1);
+        i0 = __ldg(args.blob_index + mine);
+        i1 = __ldg(args.blob_index + mine + 1);
+      }
+      const uint32_t n = min(32u, unit_count - u0);
+      bool live = true;
+      for (uint32_t i = 0; i < n && live; ++i) {
+        const uint32_t u = u0 + i, s = u % L::kIn, ph = (u / L::kIn) & 1;
+        const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, i0, i), b1 = __shfl_sync(0xFFFFFFFFu, i1, i);
+        const uint32_t bytes = (b1 - b0) << 4;
+        if (ctx.aborted() || !ctx.wait(bar_in_empty + 8 * s, ph ^ 1)) { live = false; break; }
+        if (b1 < b0 || bytes > BXQ_BLOB_MAX || bytes < BXQ_LIST_AT) {
+          ctx.abort(kStatusBadArgument);
+          live = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar_in_full + 8 * s, bytes);
+          bulk_g2s(smem + L::in + s * BXQ_BLOB_MAX, args.blobs + (size_t(b0) << 4), bytes, bar_in_full + 8 * s);
+        }
+        issued = u + 1;
+      }
+      if (!live) break;
+    }
+    // after an abort: give copies still in flight a bounded time to land before the CTA exits
+    if (ctx.aborted() && lane == 0)
+      for (uint32_t u = (issued > uint32_t(L::kIn) ? issued - L::kIn : 0); u < issued; ++u) mbar_wait(bar_in_full + 8 * (u % L::kIn), (u / L::kIn) & 1);
+  } else if (MODE == kUmma && warp == kWideWarpXLoader) {
+    // ------------------------------------------------------------------ activation tiles by TMA, and the go-ahead
+    // One thread.  Chunk v of this CTA (in the order the items list them) uses activation stage v % kX and operand
+    // stage v % kOp (tensor memory).  The tiles of chunk v are requested once chunk v - kX has been multiplied (its stage is free);
+    // kXLag chunks later the thread waits for them and gives the MMA warp the go-ahead by arriving on the operand
+    // stage's `full` barrier, which the decoder warps complete.  "Chunk c has been multiplied" is the phase of
+    // op_empty[c % kOp] that the MMA warp's commit completes; this thread is never more than one phase behind it,
+    // because the multiply of chunk c + kOp needs its own go-ahead.
+    if (lane == 0) {
+      grid_dependency_wait();
+      bool live = true;
+      uint32_t it_v = item_begin, c_v = 0;  // cursor of the chunk to request: item and chunk inside it
+      bxr_item item_v = args.items[item_begin < item_end ? item_begin : 0];
+      c_v = item_v.chunk_begin;
+      auto multiplied = [&](uint32_t c) { return ctx.wait(bar_op_empty + 8 * (c % kOpN), (c / kOpN) & 1); };
+      for (uint32_t v = 0; v < unit_count + L::kXLag && live; ++v) {
+        if (ctx.aborted()) break;
+        if (v < unit_count) {
+          if (v >= kXN && !multiplied(v - kXN)) { live = false; break; }
+          const uint32_t sx = v % kXN, stage = smem + L::xs + sx * L::kXStage;
+          mbar_arrive_expect_tx(bar_x_full + 8 * sx, L::kXStage);
+          tma_load_2d(stage, &tmap_x, int(c_v * BXR_COLS), 0, bar_x_full + 8 * sx);
+          tma_load_2d(stage + NB * 128, &tmap_x, int(c_v * BXR_COLS + 64), 0, bar_x_full + 8 * sx);
+          if (++c_v == item_v.chunk_end && it_v + 1 < item_end) {
+            item_v = args.items[++it_v];
+            c_v = item_v.chunk_begin;
+          }
+        }
+        if (v >= uint32_t(L::kXLag)) {
+          const uint32_t w = v - L::kXLag;
+          if (!ctx.wait(bar_x_full + 8 * (w % kXN), (w / kXN) & 1)) { live = false; break; }
+          if (w >= kOpN && !multiplied(w - kOpN)) { live = false; break; }
+          mbar_arrive(bar_op_full + 8 * (w % kOpN));
+        }
+      }
+    }
+  } else if (MODE == kUmma && warp == kWideWarpMma) {
+    // ------------------------------------------------------------------ MMA issue: one wait, eight MMAs, one commit
+    constexpr uint32_t idesc = umma_idesc_bf16(NB);
+    uint32_t n_item = 0, so = 0, pho = 0, sx = 0;
+    bool live = true;
+    for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
+      const bxr_item item = args.items[it];
+      const uint32_t buf = n_item & 1;
+      if (ctx.aborted() || !ctx.wait(bar_acc_empty + 8 * buf, ((n_item >> 1) & 1) ^ 1)) { live = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * NB;
+      uint32_t accumulate = 0;
+      for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c) {
+        if (!ctx.wait(bar_op_full + 8 * so, pho)) { live = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_tmem = tmem_base + kWideOperandCol + so * 64;
+          const uint64_t bdesc = umma_desc_sw128(smem + L::xs + sx * L::kXStage);
+#pragma unroll
+          for (uint32_t a = 0; a < 2; ++a)
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+              umma_bf16_ts(d_tmem, a_tmem + a * 32 + k * 8, bdesc + a * (NB * 128 >> 4) + 2 * k, idesc, accumulate);
+              accumulate = 1;
+            }
+          umma_commit(bar_op_empty + 8 * so);
+        }
+        __syncwarp();
+        if (++so == kOpN) { so = 0; pho ^= 1; }
+        if (++sx == kXN) sx = 0;
+      }
+      if (live && lane == 0) umma_commit(bar_acc_full + 8 * buf);
+      __syncwarp();
+    }
+  } else if (MODE == kUmma && warp >= kWideWarpEpilogue) {
+    // ------------------------------------------------------------------ TMEM -> y, or -> FP32 partial tile
+    const uint32_t e = warp - kWideWarpEpilogue;  // == warp % 4: the TMEM lane quarter this warp may read
+    const uint32_t r = e * 32 + lane;
+    const uint32_t mcols = (args.m + 7) & ~7u;
+    uint32_t n_item = 0;
+    bool live = true;
+    grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
+    for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
+      const bxr_item item = args.items[it];
+      const uint32_t buf = n_item & 1;
+      if (ctx.aborted() || !ctx.wait(bar_acc_full + 8 * buf, (n_item >> 1) & 1)) { live = false; break; }
+      tc_fence_after();
+      const uint32_t row = item.row_block * BXR_ROWS + r;
+      const uint32_t taddr = tmem_base + ((e * 32) << 16) + buf * NB;
+      const float b = (args.bias && row < args.rows) ? __bfloat162float(args.bias[row]) : 0.f;
+      for (uint32_t m0 = 0; m0 < mcols; m0 += 8) {
+        uint32_t v[8];
+        tmem_ld8(taddr + m0, v);
+        tmem_ld_wait();
+        if (item.parts == 1) {
+          if (row < args.rows)
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              if (m0 + i < args.m) {
+                const float f = __uint_as_float(v[i]);
+                args.y[size_t(m0 + i) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(f, b) : f);
+              }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) args.partials[(size_t(item.slot) * NB + m0 + i) * BXR_ROWS + r] = __uint_as_float(v[i]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+      if (item.parts > 1) {
+        __threadfence();
+        named_barrier(1, 128);
+        if (e == 0 && lane == 0) {
+          const uint32_t prev = atomicAdd(args.counters + item.row_block, 1u);
+          asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(prev) : "memory");
+        }
+        named_barrier(1, 128);
+        uint32_t prev;
+        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
+        if (prev == item.parts - 1) {  // every partial tile of this row block is in memory: add them in K order
+          __threadfence();
+          const uint32_t first = item.slot - item.part;
+          if (it + 1 == item_end) {
+            // the CTA's last item: the decoder warps have nothing left to do and share the reduction (below)
+            if (e == 0 && lane == 0)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + 16), "r"(1u), "r"(item.row_block),
+                           "r"(first), "r"(item.parts) : "memory");
+          } else {
+            reduce_row_block<NB>(args, item.row_block, first, item.parts, e, 4, lane);
+          }
+          if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
+        }
+        named_barrier(1, 128);  // the verdict word may be rewritten
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_final);
+  }
+
+  // A row block whose last partial tile came from this CTA's final item is reduced by the 16 decoder warps and
+  // the 4 epilogue warps together.
+  if (MODE == kUmma && (warp < kDecoderWarps || warp >= kWideWarpEpilogue)) {
+    if (ctx.wait(bar_final, 0)) {
+      const uint4 verdict = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
+      if (verdict.x)
+        reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (MODE == kUmma && warp == kWideWarpMma) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace grb

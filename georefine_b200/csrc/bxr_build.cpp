@@ -370,6 +370,96 @@ bool window_unblob(const uint8_t* blob, uint64_t blob_bytes, const uint8_t* base
   return true;
 }
 
+// ---- wide-window mode -------------------------------------------------------------------------------------
+// Row windows: the 16 consecutive exponents [base, base + 15] that cover most of the row.
+std::vector<uint8_t> choose_window4_bases(const Source& src, uint32_t rows_pad, uint32_t threads) {
+  std::vector<uint8_t> base(rows_pad);
+  parallel_for(rows_pad, threads, [&](uint32_t r) {
+    uint32_t h[256 + 16] = {0};
+    for (uint32_t c = 0; c < src.cols; ++c) ++h[exponent_of(src.at(r, c))];
+    uint32_t run = 0, best = 0, best_base = 0;
+    for (uint32_t e = 0; e < 16; ++e) run += h[e];
+    for (uint32_t b = 0;; ++b) {
+      if (run >= best) { best = run; best_base = b; }   // ties go to the higher window: the tail below is the long one
+      if (b == BXQ_BASE_MAX) break;
+      run += h[b + 16];
+      run -= h[b];
+    }
+    base[r] = uint8_t(best_base);
+  });
+  return base;
+}
+
+bool window4_blob(const Source& src, uint32_t row_block, uint32_t chunk, const uint8_t* base, std::vector<uint8_t>& blob) {
+  std::vector<uint32_t> entries[16];
+  std::vector<uint8_t> fixed(BXQ_LIST_AT, 0);
+  auto* codes = reinterpret_cast<uint32_t*>(fixed.data() + BXQ_CODES_AT);
+  for (uint32_t warp = 0; warp < 16; ++warp) {
+    const uint32_t q = warp >> 2;
+    for (uint32_t rl = 0; rl < 32; ++rl) {
+      const uint32_t r = (warp & 3) * 32 + rl, row = row_block * BXR_ROWS + r, b = base[row];
+      uint32_t word[4] = {0, 0, 0, 0};
+      for (uint32_t j = 0; j < 32; ++j) {
+        const uint32_t col = chunk * BXR_COLS + q * 32 + j;
+        // a padded column never reaches an output: it carries the window's first exponent and a zero raw byte
+        const uint16_t w = col < src.cols ? src.at(row, col) : uint16_t(b << 7);
+        const uint32_t e = exponent_of(w);
+        fixed[BXQ_RAW_AT + (size_t(2 * q + j / 16) * BXR_ROWS + r) * 16 + j % 16] = raw_byte_of(w);
+        uint32_t code = e - b;  // wraps below the window
+        if (code > 15) {
+          code = 0;
+          entries[warp].push_back(j | rl << 5 | e << 16);
+        }
+        const uint32_t p = j / 2;
+        word[p / 4] |= code << (4 * (p % 4) + 16 * (j & 1));
+      }
+      for (uint32_t t = 0; t < 4; ++t) codes[t * BXR_SEGMENTS + q * BXR_ROWS + r] = word[t];
+    }
+  }
+  size_t total = 0;
+  auto* warp_end = reinterpret_cast<uint16_t*>(fixed.data() + BXQ_WARP_END_AT);
+  for (uint32_t w = 0; w < 16; ++w) { warp_end[w] = uint16_t(total); total += entries[w].size(); }
+  if (total > BXQ_ENTRY_MAX) return false;
+  warp_end[16] = uint16_t(total);
+  blob.assign((BXQ_LIST_AT + 4 * total + 15) & ~size_t(15), 0);
+  std::memcpy(blob.data(), fixed.data(), BXQ_LIST_AT);
+  size_t at = BXQ_LIST_AT;
+  for (uint32_t w = 0; w < 16; ++w) {
+    if (!entries[w].empty()) std::memcpy(blob.data() + at, entries[w].data(), 4 * entries[w].size());
+    at += 4 * entries[w].size();
+  }
+  return true;
+}
+
+bool window4_unblob(const uint8_t* blob, uint64_t blob_bytes, const uint8_t* base_rows, uint16_t* tile /* [128][128] */) {
+  if (blob_bytes < BXQ_LIST_AT) return false;
+  uint16_t warp_end[17];
+  std::memcpy(warp_end, blob + BXQ_WARP_END_AT, sizeof warp_end);
+  const size_t total = warp_end[16];
+  if (total > BXQ_ENTRY_MAX || BXQ_LIST_AT + 4ull * total > blob_bytes) return false;
+  const auto* codes = reinterpret_cast<const uint32_t*>(blob + BXQ_CODES_AT);
+  for (uint32_t q = 0; q < BXR_PHASES; ++q)
+    for (uint32_t r = 0; r < BXR_ROWS; ++r)
+      for (uint32_t j = 0; j < 32; ++j) {
+        const uint32_t p = j / 2, word = codes[(p / 4) * BXR_SEGMENTS + q * BXR_ROWS + r];
+        const uint32_t code = (word >> (4 * (p % 4) + 16 * (j & 1))) & 15u;
+        const uint32_t e = (base_rows[r] + code) & 0xFFu, byte = blob[BXQ_RAW_AT + (size_t(2 * q + j / 16) * BXR_ROWS + r) * 16 + j % 16];
+        tile[r * BXR_COLS + q * 32 + j] = uint16_t((byte & 0x80) << 8 | e << 7 | (byte & 0x7F));
+      }
+  for (uint32_t warp = 0; warp < 16; ++warp) {
+    if (warp_end[warp] > warp_end[warp + 1]) return false;
+    for (uint32_t i = warp_end[warp]; i < warp_end[warp + 1]; ++i) {
+      uint32_t v;
+      std::memcpy(&v, blob + BXQ_LIST_AT + 4 * size_t(i), 4);
+      if ((v & 0xFC00u) || (v >> 24)) return false;
+      const uint32_t j = v & 31u, rl = (v >> 5) & 31u, e = (v >> 16) & 0xFFu;
+      uint16_t& w = tile[((warp & 3) * 32 + rl) * BXR_COLS + (warp >> 2) * 32 + j];
+      w = uint16_t((w & 0x807Fu) | e << 7);
+    }
+  }
+  return true;
+}
+
 }  // namespace
 
 extern "C" {
@@ -377,13 +467,14 @@ extern "C" {
 void bxr_free(void* p) { std::free(p); }
 
 // Builds the image.  workers = CTAs the kernels will run (one per SM); threads = host threads.
-// layout = BXR_MODE_CODED (rANS exponent streams), BXR_MODE_WINDOW (fixed 3-bit codes) or BXR_MODE_RAW (no coding).
-// A chunk that does not fit its slot demotes the whole image: window -> coded -> raw.
+// layout = BXR_MODE_CODED (rANS exponent streams), BXR_MODE_WINDOW (fixed 3-bit codes), BXR_MODE_WINDOW4 (fixed 4-bit
+// codes) or BXR_MODE_RAW (no coding).  A chunk that does not fit its slot demotes the whole image: window4 or window
+// -> coded -> raw.
 // Returns 0, 1 bad arguments, 2 out of memory, 3 other failure.  The image is malloc'ed; free with bxr_free.
 int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t workers, uint32_t threads,
               uint32_t layout, const uint8_t* source_sha256, uint8_t** image, uint64_t* image_bytes) {
   try {
-    if (!words || !rows || !cols || !workers || workers > 4096 || !image || !image_bytes || layout > BXR_MODE_WINDOW) return 1;
+    if (!words || !rows || !cols || !workers || workers > 4096 || !image || !image_bytes || layout > BXR_MODE_WINDOW4) return 1;
     if (!threads) threads = std::max(1u, std::thread::hardware_concurrency());
     const Source src{words, rows, cols};
     Plan plan = make_plan(rows, cols, workers);
@@ -397,6 +488,20 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     std::vector<uint32_t> states(size_t(nitems) * BXR_STREAMS, BXR_STATE_LOW);
     bool raw_mode = layout == BXR_MODE_RAW;
     bool window_mode = layout == BXR_MODE_WINDOW;
+    bool window4_mode = layout == BXR_MODE_WINDOW4;
+
+    if (window4_mode) {
+      base = choose_window4_bases(src, rows_pad, threads);
+      std::atomic<bool> overflow{false};
+      parallel_for(nblobs, threads, [&](uint32_t bi) {
+        if (overflow.load()) return;
+        if (!window4_blob(src, bi / plan.chunks, bi % plan.chunks, base.data(), blobs[bi])) overflow.store(true);
+      });
+      if (overflow.load()) {
+        window4_mode = false;
+        for (auto& b : blobs) b.clear();
+      }
+    }
 
     if (window_mode) {
       base = choose_window_bases(src, rows_pad, threads);
@@ -411,7 +516,7 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
       }
     }
 
-    if (!raw_mode && !window_mode) {
+    if (!raw_mode && !window_mode && !window4_mode) {
       base = choose_bases(src, rows_pad, threads);
       // pair statistics
       std::vector<std::vector<uint64_t>> local(threads, std::vector<uint64_t>(256, 0));
@@ -509,8 +614,8 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
 
     bxr_header h{};
     h.magic = BXR_MAGIC;
-    h.mode = raw_mode ? BXR_MODE_RAW : window_mode ? BXR_MODE_WINDOW : BXR_MODE_CODED;
-    const bool coded = !raw_mode && !window_mode;
+    h.mode = raw_mode ? BXR_MODE_RAW : window4_mode ? BXR_MODE_WINDOW4 : window_mode ? BXR_MODE_WINDOW : BXR_MODE_CODED;
+    const bool coded = !raw_mode && !window_mode && !window4_mode;
     h.rows = rows;
     h.cols = cols;
     h.row_blocks = plan.row_blocks;
@@ -566,7 +671,7 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
     if (!img || !out || bytes < sizeof(bxr_header)) return 1;
     bxr_header h;
     std::memcpy(&h, img, sizeof h);
-    if (h.magic != BXR_MAGIC || h.total_bytes != bytes || !h.rows || !h.cols || h.mode > BXR_MODE_WINDOW) return 1;
+    if (h.magic != BXR_MAGIC || h.total_bytes != bytes || !h.rows || !h.cols || h.mode > BXR_MODE_WINDOW4) return 1;
     const auto* items = reinterpret_cast<const bxr_item*>(img + h.items_at);
     const auto* index = reinterpret_cast<const uint32_t*>(img + h.blob_index_at);
     auto put = [&](uint32_t row, uint32_t col, uint16_t w) {
@@ -586,13 +691,16 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
       return 0;
     }
     const uint8_t* base = img + h.base_at;
-    if (h.mode == BXR_MODE_WINDOW) {
+    if (h.mode == BXR_MODE_WINDOW || h.mode == BXR_MODE_WINDOW4) {
       std::vector<uint16_t> tile(size_t(BXR_ROWS) * BXR_COLS);
       for (uint32_t rb = 0; rb < h.row_blocks; ++rb)
         for (uint32_t c = 0; c < h.chunks; ++c) {
           const size_t bi = size_t(rb) * h.chunks + c;
           const uint8_t* blob = img + h.blobs_at + (uint64_t(index[bi]) << 4);
-          if (!window_unblob(blob, uint64_t(index[bi + 1] - index[bi]) << 4, base + size_t(rb) * BXR_ROWS, tile.data())) return 2;
+          const uint64_t blob_bytes = uint64_t(index[bi + 1] - index[bi]) << 4;
+          const bool ok = h.mode == BXR_MODE_WINDOW ? window_unblob(blob, blob_bytes, base + size_t(rb) * BXR_ROWS, tile.data())
+                                                    : window4_unblob(blob, blob_bytes, base + size_t(rb) * BXR_ROWS, tile.data());
+          if (!ok) return 2;
           for (uint32_t r = 0; r < BXR_ROWS; ++r)
             for (uint32_t j = 0; j < BXR_COLS; ++j) put(rb * BXR_ROWS + r, c * BXR_COLS + j, tile[r * BXR_COLS + j]);
         }

@@ -104,6 +104,33 @@
 #define BXW_DELTA_FAR (-16)
 #define BXW_BASE_MAX 248
 
+/* Wide-window mode.  As the window mode, with 4-bit codes: exponent = base[row] + code over a 16-binade window
+ * (base in [0, 240]).  On Gaussian rows fewer than one weight in ten thousand falls outside, so exceptions are a rare
+ * slow path, the decoder has no per-chunk patching to do, and the decoded words can stay in registers until they are
+ * written to tensor memory.  12 bits per weight.
+ *
+ * A lane (phase q, row r) owns the 32 chunk columns [32q, 32q+32) of its row = 16 column pairs; its codes are four
+ * 32-bit words (codes[j][q*128 + r], j = 0..3).  Word j holds pairs 4j..4j+3: pair 4j+k has the code of its even
+ * column in bits [4k, 4k+4) and the code of its odd column 16 bits higher.
+ *
+ * Chunk blob in wide-window mode (multiple of 16 bytes, at most BXQ_BLOB_MAX):
+ *   [0,34)        u16 warp_end[17]     entries of decoder warp w = [warp_end[w], warp_end[w+1]); warp w covers phase
+ *                                      w/4, rows 32*(w%4) .. +31, one lane per row
+ *   [64,16448)    u8  raw[8][128][16]  as in the coded mode
+ *   [16448,24640) u32 codes[4][512]
+ *   [24640, ...)  u32 entries          column in the lane's 32 [0,5) | lane [5,10) | true exponent [16,24); the
+ *                                      weight carries code 0
+ */
+#define BXR_MODE_WINDOW4 3
+#define BXQ_WARP_END_AT 0
+#define BXQ_RAW_AT 64
+#define BXQ_CODES_AT (BXQ_RAW_AT + BXR_RAW_BYTES)
+#define BXQ_LIST_AT (BXQ_CODES_AT + 4 * 4 * BXR_SEGMENTS)
+#define BXQ_BLOB_MAX 25600 /* shared-memory slot per chunk blob in this mode */
+#define BXQ_ENTRY_MAX ((BXQ_BLOB_MAX - BXQ_LIST_AT - 16) / 4)
+#define BXQ_PAIR_MASK 0x000F000Fu
+#define BXQ_BASE_MAX 240
+
 /* Slot record of the pair table, 32 bits: n0[0,4) | bias[4,16) | n1[16,20) | freq[20,32).  freq <= 4095.
  * (record & 0x000F000F) * 128 is the pair of relative exponents in packed-BF16 position (an exception nibble is
  * stored as 0), freq is the top field, bias = (record >> 4) & 0xFFF. */

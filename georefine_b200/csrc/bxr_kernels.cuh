@@ -60,6 +60,7 @@ struct BxrArgs {
   uint32_t rows, cols, row_blocks, chunks, workers;
   uint32_t raw;                // image holds plain pre-swizzled tiles (BXR_MODE_RAW): kUmma only, no decoders
   uint32_t window;             // image holds fixed 3-bit exponent codes (BXR_MODE_WINDOW): served by bxw_kernel
+  uint32_t window4;            // image holds fixed 4-bit exponent codes (BXR_MODE_WINDOW4): served by bxq_kernel
   // call
   uint32_t m;                  // activation rows in this launch (<= NB, <= 8 for the GEMV)
   const __nv_bfloat16* x;      // GEMV only (the UMMA path reads x through the tensor map)

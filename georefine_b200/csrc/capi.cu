@@ -9,6 +9,7 @@
 #include "bctx_decode.cuh"
 #include "bxr_kernels.cuh"
 #include "bxw_kernels.cuh"
+#include "bxq_kernels.cuh"
 
 namespace {
 
@@ -21,7 +22,7 @@ uint32_t batch_tile(uint32_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ?
 uint64_t counter_bytes(const bxr_header* h) { return (uint64_t(h->row_blocks) * 4 + 255) & ~uint64_t(255); }
 
 bool header_ok(const bxr_header* h) {
-  return h && h->magic == BXR_MAGIC && h->rows && h->cols && h->workers && h->mode <= BXR_MODE_WINDOW &&
+  return h && h->magic == BXR_MAGIC && h->rows && h->cols && h->workers && h->mode <= BXR_MODE_WINDOW4 &&
          h->row_blocks == (h->rows + BXR_ROWS - 1) / BXR_ROWS && h->chunks == (h->cols + BXR_COLS - 1) / BXR_COLS;
 }
 
@@ -44,6 +45,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   a.workers = h->workers;
   a.raw = h->mode == BXR_MODE_RAW;
   a.window = h->mode == BXR_MODE_WINDOW;
+  a.window4 = h->mode == BXR_MODE_WINDOW4;
   return a;
 }
 
@@ -114,6 +116,38 @@ int launch_window(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream
   return cuda_status(cudaLaunchKernelEx(&cfg, bxw_kernel<MODE, NB>, a, tmap));
 }
 
+// Wide-window images run bxq_kernel.
+template <int MODE, int NB>
+cudaError_t prepare_wide() {
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 64 && done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(bxq_kernel<MODE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BxqSmem<MODE, NB>::alloc));
+  if (e == cudaSuccess && dev < 64) done[dev] = true;
+  return e;
+}
+
+template <int MODE, int NB>
+int launch_wide(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
+  cudaError_t e = prepare_wide<MODE, NB>();
+  if (e != cudaSuccess) return cuda_status(e);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(a.workers);
+  cfg.blockDim = dim3(MODE == kUmma ? kThreadsUmma : kThreadsSimt);
+  cfg.dynamicSmemBytes = BxqSmem<MODE, NB>::alloc;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, bxq_kernel<MODE, NB>, a, tmap));
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -167,6 +201,7 @@ int gemm_tile(BxrArgs a, const void* x, int64_t ldx, cudaStream_t stream) {
   CUtensorMap map;
   const int st = make_x_map(&map, x, ldx, a.m, a.cols, NB);
   if (st) return st;
+  if (a.window4) return launch_wide<kUmma, NB>(a, map, stream);
   return a.window ? launch_window<kUmma, NB>(a, map, stream) : launch<kUmma, NB>(a, map, stream);
 }
 
@@ -229,6 +264,7 @@ int grb_bxr_decode(const void* image, const bxr_header* h, uint16_t* out, uint32
   a.dense = out;
   a.status = status;
   CUtensorMap none{};
+  if (a.window4) return launch_wide<kDense, 8>(a, none, static_cast<cudaStream_t>(cuda_stream));
   if (a.window) return launch_window<kDense, 8>(a, none, static_cast<cudaStream_t>(cuda_stream));
   return launch<kDense, 8>(a, none, static_cast<cudaStream_t>(cuda_stream));
 }
@@ -360,6 +396,9 @@ int grb_kernel_attributes(int which, int out[5]) {
     case 5: e = cudaFuncGetAttributes(&fa, bxw_kernel<kDense, 8>); break;
     case 6: e = cudaFuncGetAttributes(&fa, bxw_kernel<kUmma, 16>); break;
     case 7: e = cudaFuncGetAttributes(&fa, bxw_kernel<kUmma, 128>); break;
+    case 8: e = cudaFuncGetAttributes(&fa, bxq_kernel<kDense, 8>); break;
+    case 9: e = cudaFuncGetAttributes(&fa, bxq_kernel<kUmma, 16>); break;
+    case 10: e = cudaFuncGetAttributes(&fa, bxq_kernel<kUmma, 128>); break;
     default: return GRB_ERR_ARGUMENT;
   }
   if (e != cudaSuccess) return cuda_status(e);

@@ -100,7 +100,8 @@ class CudaContextTensor:
 
     ``resident_bytes`` counts every device allocation made here, the image and its scratch included.
     ``fused=False`` skips the image (embedding tables that are only gathered); ``layout`` picks the image's layout
-    ("window": fixed 3-bit exponent codes, the default; "rans": entropy-coded exponent streams, 1-3 % smaller).
+    ("window4": fixed 4-bit exponent codes, the default and the fastest; "window": 3-bit codes; "rans": entropy-coded
+    exponent streams, the smallest).
     """
 
     def __init__(self, frame: bytes, *, stride: int = 1024, device="cuda:0", fused: bool = True, max_m: int = 128,

@@ -1,4 +1,5 @@
-"""GPU parity of the window-mode resident layout (fixed 3-bit exponent codes, csrc/bxw_kernels.cuh).
+"""GPU parity of the window resident layouts: fixed 3-bit exponent codes (csrc/bxw_kernels.cuh, operand tile in shared
+memory) and fixed 4-bit codes (csrc/bxq_kernels.cuh, operand in tensor memory).
 
 The decode twin must return the source words bit for bit; the fused product must agree with the FP32 reference
 within the stated tolerance and give rows that do not depend on the batch size.
@@ -12,6 +13,7 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 REL_TOL = 1e-2  # BF16 output, FP32 accumulation: relative to the largest reference magnitude of the call
+LAYOUTS = [("window", 2), ("window4", 3)]   # layout name, header mode
 
 
 @pytest.fixture(scope="module")
@@ -45,35 +47,37 @@ def _sprinkle(words, rate, seed):
 
 @pytest.mark.parametrize("shape,seed", [((128, 128), 0), ((256, 512), 1), ((300, 200), 2), ((64, 67), 3), ((1000, 1536), 4),
                                         ((777, 1032), 5), ((64, 17408), 6), ((4096, 4096), 0)])
-def test_window_decode_is_bit_exact(orc, dev, shape, seed):
+@pytest.mark.parametrize("layout,mode", LAYOUTS)
+def test_window_decode_is_bit_exact(orc, dev, shape, seed, layout, mode):
     from georefine_b200.resident import ResidentWeight, build_image, decode_image_host
 
     words = orc.synthetic_weight_words(*shape, seed)
-    image, h = build_image(words, 148, layout="window")
-    assert h.mode == 2
+    image, h = build_image(words, 148, layout=layout)
+    assert h.mode == mode
     assert np.array_equal(decode_image_host(image), words)
     r = ResidentWeight(image, dev)
     assert np.array_equal(_u16(r.decode()), words)
     assert r.check_status() == 0
 
 
-def test_window_decode_special_words_and_far_exponents(orc, dev):
+@pytest.mark.parametrize("layout,mode", LAYOUTS)
+def test_window_decode_special_words_and_far_exponents(orc, dev, layout, mode):
     from georefine_b200.resident import ResidentWeight
 
     words = _sprinkle(orc.synthetic_weight_words(384, 640, 11), 5e-4, 11)
-    r = ResidentWeight.from_words(words, dev, layout="window")
-    assert r.mode == 2 and np.array_equal(_u16(r.decode()), words)
+    r = ResidentWeight.from_words(words, dev, layout=layout)
+    assert r.mode == mode and np.array_equal(_u16(r.decode()), words)
     # rows of very different scale, one constant row, one row of zeros
     words = orc.synthetic_weight_words(256, 384, 12)
     words[7] = 0x3F80
     words[9] = 0
     words[100] = (words[100] & 0x807F) | (np.uint16(3) << 7)
     words[101] = (words[101] & 0x807F) | (np.uint16(250) << 7)
-    r = ResidentWeight.from_words(words, dev, layout="window")
+    r = ResidentWeight.from_words(words, dev, layout=layout)
     assert np.array_equal(_u16(r.decode()), words)
     # a tensor whose exceptions do not fit falls back to another layout and still decodes exactly
     noisy = _sprinkle(orc.synthetic_weight_words(200, 300, 17), 0.2, 17)
-    r = ResidentWeight.from_words(noisy, dev, layout="window")
+    r = ResidentWeight.from_words(noisy, dev, layout=layout)
     assert r.mode in (0, 1) and np.array_equal(_u16(r.decode()), noisy)
 
 
@@ -81,14 +85,15 @@ SHAPES = [((128, 128), 0), ((256, 512), 1), ((300, 200), 2), ((1024, 4096), 3), 
           ((777, 1032), 5), ((64, 17408), 6)]
 
 
+@pytest.mark.parametrize("layout,mode", LAYOUTS)
 @pytest.mark.parametrize("shape,seed", SHAPES)
-def test_window_gemm_matches_reference_and_rows_do_not_depend_on_batch(orc, dev, shape, seed):
+def test_window_gemm_matches_reference_and_rows_do_not_depend_on_batch(orc, dev, shape, seed, layout, mode):
     from georefine_b200.resident import ResidentWeight
 
     words = orc.synthetic_weight_words(*shape, seed)
-    r = ResidentWeight.from_words(words, dev, max_m=256, layout="window")
+    r = ResidentWeight.from_words(words, dev, max_m=256, layout=layout)
     coded = ResidentWeight.from_words(words, dev, max_m=256, layout="rans")
-    assert r.mode == 2 and coded.mode == 0
+    assert r.mode == mode and coded.mode == 0
     n, k = shape
     g = torch.Generator(device="cpu").manual_seed(300 + seed)
     xfull = torch.randn(200, k, generator=g).to(torch.bfloat16).to(dev)
@@ -117,13 +122,14 @@ def test_window_gemm_matches_reference_and_rows_do_not_depend_on_batch(orc, dev,
     assert r.check_status() == 0 and np.array_equal(_u16(y3), rows[200][:3])
 
 
-def test_window_linear_with_bias_exceptions_and_module(orc, oracle_coder, dev):
+@pytest.mark.parametrize("layout,mode", LAYOUTS)
+def test_window_linear_with_bias_exceptions_and_module(orc, oracle_coder, dev, layout, mode):
     from georefine_b200.resident import ResidentWeight
 
     words = _sprinkle(orc.synthetic_weight_words(384, 520, 31), 5e-4, 31)
     words[(words & 0x7F80) >= 0x6000] = 0x3C00                      # keep zeros, denormals and far small exponents; drop huge, inf, NaN
-    r = ResidentWeight.from_words(words, dev, layout="window")
-    assert r.mode == 2
+    r = ResidentWeight.from_words(words, dev, layout=layout)
+    assert r.mode == mode
     bias = torch.randn(384, device=dev).to(torch.bfloat16)
     x = torch.randn(4, 9, 1040, device=dev).to(torch.bfloat16)[..., ::2]      # strided batched input
     y = r.linear(x, bias=bias)
@@ -132,17 +138,18 @@ def test_window_linear_with_bias_exceptions_and_module(orc, oracle_coder, dev):
     assert ((y.reshape(-1, 384).float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
 
 
+@pytest.mark.parametrize("layout,mode", LAYOUTS)
 @pytest.mark.parametrize("shape", [(34816, 5120), (5120, 17408)])
-def test_window_full_size_images_reproduce_their_source_digest(orc, dev, shape):
+def test_window_full_size_images_reproduce_their_source_digest(orc, dev, shape, layout, mode):
     from georefine_b200.resident import ResidentWeight
 
     words = orc.synthetic_weight_words(*shape, 1)
-    r = ResidentWeight.from_words(words, dev, verify=False, layout="window")
-    assert r.mode == 2
+    r = ResidentWeight.from_words(words, dev, verify=False, layout=layout)
+    assert r.mode == mode
     got = _u16(r.decode())
     assert r.check_status() == 0
     assert hashlib.sha256(got.tobytes()).digest() == hashlib.sha256(words.tobytes()).digest()
-    assert 1.35 < 2 * words.size / r.coded_bytes < 1.50
+    assert (1.35 if layout == "window" else 1.30) < 2 * words.size / r.coded_bytes < 1.50
     x = torch.randn(2, shape[1], device=dev).to(torch.bfloat16)
     y = torch.empty(2, shape[0], device=dev, dtype=torch.bfloat16)
     r.gemm(x, y)

@@ -193,12 +193,13 @@ def test_corrupt_resident_image_is_rejected_on_the_host(orc):
 
 @pytest.mark.parametrize("shape,seed,workers", [((128, 128), 0, 148), ((300, 200), 2, 148), ((64, 67), 3, 5),
                                                 ((1, 1), 4, 148), ((513, 1024), 5, 37), ((256, 4096), 6, 148)])
-def test_window_image_round_trips_on_the_host(orc, shape, seed, workers):
-    """Window layout (fixed 3-bit exponent codes): the host twin returns the source words; the plan is the coded one."""
+@pytest.mark.parametrize("layout,mode", [("window", 2), ("window4", 3)])
+def test_window_image_round_trips_on_the_host(orc, shape, seed, workers, layout, mode):
+    """Window layouts (fixed 3-bit / 4-bit exponent codes): the host twin returns the source words; the plan is the coded one."""
     words = orc.synthetic_weight_words(*shape, seed)
-    image, h = resident.build_image(words, workers, layout="window")
+    image, h = resident.build_image(words, workers, layout=layout)
     coded, hc = resident.build_image(words, workers, layout="rans")
-    assert h.mode == 2 and (h.rows, h.cols, h.items, h.partial_slots) == (hc.rows, hc.cols, hc.items, hc.partial_slots)
+    assert h.mode == mode and (h.rows, h.cols, h.items, h.partial_slots) == (hc.rows, hc.cols, hc.items, hc.partial_slots)
     assert bytes(h.source_sha256) == hashlib.sha256(words.tobytes()).digest()
     assert np.array_equal(resident.decode_image_host(image), words)
     assert np.array_equal(image[h.items_at:h.items_at + 32 * h.items], coded[hc.items_at:hc.items_at + 32 * hc.items])
@@ -226,4 +227,13 @@ def test_window_image_entries_far_list_and_fallbacks(orc):
     at = rng.random(noisy.shape) < 0.2
     noisy[at] = rng.choice(special, size=int(at.sum()))
     image, h = resident.build_image(noisy, 148, layout="window")
+    assert h.mode in (0, 1) and np.array_equal(resident.decode_image_host(image), noisy)
+    # the 4-bit layout keeps exceptions in its own list (full exponents, no far list)
+    image, h = resident.build_image(words, 148, layout="window4")
+    assert h.mode == 3 and np.array_equal(resident.decode_image_host(image), words)
+    bad = image.copy()
+    bad[h.blobs_at + 32:h.blobs_at + 34] = 0xFF
+    with pytest.raises(ValueError):
+        resident.decode_image_host(bad)
+    image, h = resident.build_image(noisy, 148, layout="window4")
     assert h.mode in (0, 1) and np.array_equal(resident.decode_image_host(image), noisy)
