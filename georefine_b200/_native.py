@@ -38,7 +38,7 @@ class BxrHeader(ctypes.Structure):
     _fields_ = [("magic", ctypes.c_uint32), ("mode", ctypes.c_uint32), ("rows", ctypes.c_uint32),
                 ("cols", ctypes.c_uint32), ("row_blocks", ctypes.c_uint32), ("chunks", ctypes.c_uint32),
                 ("workers", ctypes.c_uint32), ("items", ctypes.c_uint32), ("partial_slots", ctypes.c_uint32),
-                ("reserved0", ctypes.c_uint32), ("lut_at", ctypes.c_uint64), ("base_at", ctypes.c_uint64),
+                ("blob_stride16", ctypes.c_uint32), ("lut_at", ctypes.c_uint64), ("base_at", ctypes.c_uint64),
                 ("items_at", ctypes.c_uint64), ("worker_items_at", ctypes.c_uint64), ("states_at", ctypes.c_uint64),
                 ("blob_index_at", ctypes.c_uint64), ("blobs_at", ctypes.c_uint64), ("total_bytes", ctypes.c_uint64),
                 ("coded_bytes", ctypes.c_uint64), ("source_sha256", ctypes.c_uint8 * 32)]

@@ -127,7 +127,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   const uint32_t unit_begin = uint32_t(units * worker / args.workers);
   const uint32_t unit_count = uint32_t(units * (worker + 1) / args.workers) - unit_begin;
   uint32_t first_i0 = 0, first_i1 = 0;
-  if (warp == kWideWarpLoader && unit_count) {
+  if (warp == kWideWarpLoader && unit_count && !args.blob_stride16) {
     const uint32_t mine = unit_begin + min(uint32_t(lane), unit_count - 1);
     first_i0 = __ldg(args.blob_index + mine);
     first_i1 = __ldg(args.blob_index + mine + 1);
@@ -230,7 +230,10 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     uint32_t issued = 0;
     for (uint32_t u0 = 0; u0 < unit_count; u0 += 32) {
       uint32_t i0 = first_i0, i1 = first_i1;
-      if (u0) {
+      if (args.blob_stride16) {  // blobs of one size: no offsets to look up
+        i0 = (unit_begin + min(u0 + lane, unit_count - 1)) * args.blob_stride16;
+        i1 = i0 + args.blob_stride16;
+      } else if (u0) {
         const uint32_t mine = unit_begin + min(u0 + lane, unit_count - 1);
         i0 = __ldg(args.blob_index + mine);
         i1 = __ldg(args.blob_index + mine + 1);

@@ -633,6 +633,18 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
     h.blob_index_at = at;     at = align16(at + 4ull * (nblobs + 1));
     at = (at + 255) & ~uint64_t(255);
     h.blobs_at = at;
+    // Wide-window blobs differ only by their (rare) exception entries: pad them to one size, so that a kernel can
+    // address blob b without looking its offset up (the index is written all the same).
+    uint32_t blob_stride16 = 0;
+    if (window4_mode) {
+      size_t lo = SIZE_MAX, hi = 0;
+      for (const auto& b : blobs) { lo = std::min(lo, b.size()); hi = std::max(hi, b.size()); }
+      if (hi - lo <= 512) {
+        for (auto& b : blobs) b.resize(hi, 0);
+        blob_stride16 = uint32_t(hi >> 4);
+      }
+    }
+    h.blob_stride16 = blob_stride16;
     std::vector<uint32_t> index(nblobs + 1);
     uint64_t run = 0;
     for (uint32_t b = 0; b < nblobs; ++b) { index[b] = uint32_t(run >> 4); run += blobs[b].size(); }

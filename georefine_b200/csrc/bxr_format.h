@@ -156,7 +156,7 @@ typedef struct bxr_header {
   uint32_t row_blocks, chunks;    /* padded shape / 128 */
   uint32_t workers, items;
   uint32_t partial_slots;         /* FP32 partial tiles the workspace must hold */
-  uint32_t reserved0;
+  uint32_t blob_stride16;         /* nonzero: every blob has this size (16-byte units) and blob b starts at b * size */
   uint64_t lut_at;                /* u32[4096] slot records (absent in raw mode) */
   uint64_t base_at;               /* u8[row_blocks*128] exponent base per row */
   uint64_t items_at;              /* bxr_item[items] */

@@ -57,6 +57,7 @@ struct BxrArgs {
   const uint32_t* states;
   const uint32_t* blob_index;
   const uint8_t* blobs;
+  uint32_t blob_stride16;      // nonzero: blobs of one size (16-byte units), blob b at b * size; else see blob_index
   uint32_t rows, cols, row_blocks, chunks, workers;
   uint32_t raw;                // image holds plain pre-swizzled tiles (BXR_MODE_RAW): kUmma only, no decoders
   uint32_t window;             // image holds fixed 3-bit exponent codes (BXR_MODE_WINDOW): served by bxw_kernel

@@ -38,6 +38,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   a.states = reinterpret_cast<const uint32_t*>(p + h->states_at);
   a.blob_index = reinterpret_cast<const uint32_t*>(p + h->blob_index_at);
   a.blobs = p + h->blobs_at;
+  a.blob_stride16 = h->blob_stride16;
   a.rows = h->rows;
   a.cols = h->cols;
   a.row_blocks = h->row_blocks;
