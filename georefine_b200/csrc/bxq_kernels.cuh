@@ -278,6 +278,13 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       auto multiplied = [&](uint32_t c) { return ctx.wait(bar_op_empty + 8 * (c % kOpN), (c / kOpN) & 1); };
       for (uint32_t v = 0; v < unit_count + L::kXLag && live; ++v) {
         if (ctx.aborted()) break;
+        // the go-ahead first: the request below waits for a multiply that may need it
+        if (v >= uint32_t(L::kXLag)) {
+          const uint32_t w = v - L::kXLag;
+          if (!ctx.wait(bar_x_full + 8 * (w % kXN), (w / kXN) & 1)) { live = false; break; }
+          if (w >= kOpN && !multiplied(w - kOpN)) { live = false; break; }
+          mbar_arrive(bar_op_full + 8 * (w % kOpN));
+        }
         if (v < unit_count) {
           if (v >= kXN && !multiplied(v - kXN)) { live = false; break; }
           const uint32_t sx = v % kXN, stage = smem + L::xs + sx * L::kXStage;
@@ -288,12 +295,6 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
             item_v = args.items[++it_v];
             c_v = item_v.chunk_begin;
           }
-        }
-        if (v >= uint32_t(L::kXLag)) {
-          const uint32_t w = v - L::kXLag;
-          if (!ctx.wait(bar_x_full + 8 * (w % kXN), (w / kXN) & 1)) { live = false; break; }
-          if (w >= kOpN && !multiplied(w - kOpN)) { live = false; break; }
-          mbar_arrive(bar_op_full + 8 * (w % kOpN));
         }
       }
     }
@@ -337,7 +338,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t r = e * 32 + lane;
     const uint32_t mcols = (args.m + 7) & ~7u;
     uint32_t n_item = 0;
-    bool live = true;
+    bool live = true, early_taken = false;
     grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
       const bxr_item item = args.items[it];
@@ -347,21 +348,24 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       const uint32_t row = item.row_block * BXR_ROWS + r;
       const uint32_t taddr = tmem_base + ((e * 32) << 16) + buf * NB;
       const float b = (args.bias && row < args.rows) ? __bfloat162float(args.bias[row]) : 0.f;
-      for (uint32_t m0 = 0; m0 < mcols; m0 += 8) {
-        uint32_t v[8];
-        tmem_ld8(taddr + m0, v);
+      constexpr int kStep = NB >= 32 ? 32 : 16;  // accumulator columns per tensor-memory load
+      for (uint32_t m0 = 0; m0 < mcols; m0 += kStep) {
+        uint32_t v[kStep];
+        if constexpr (kStep == 32) tmem_ld32(taddr + m0, v);
+        else tmem_ld16(taddr + m0, v);
         tmem_ld_wait();
         if (item.parts == 1) {
           if (row < args.rows)
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < kStep; ++i)
               if (m0 + i < args.m) {
                 const float f = __uint_as_float(v[i]);
                 args.y[size_t(m0 + i) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(f, b) : f);
               }
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) args.partials[(size_t(item.slot) * NB + m0 + i) * BXR_ROWS + r] = __uint_as_float(v[i]);
+          for (int i = 0; i < kStep; ++i)
+            if (m0 + i < mcols) args.partials[(size_t(item.slot) * NB + m0 + i) * BXR_ROWS + r] = __uint_as_float(v[i]);
         }
       }
       tc_fence_before();
@@ -380,11 +384,14 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         if (prev == item.parts - 1) {  // every partial tile of this row block is in memory: add them in K order
           __threadfence();
           const uint32_t first = item.slot - item.part;
-          if (it + 1 == item_end) {
-            // the CTA's last item: the decoder warps have nothing left to do and share the reduction (below)
+          // Reduced at the end of the CTA by the decoder and epilogue warps together (below).  Only the first and the
+          // last item of a CTA can be part of a split row block, hence two verdict slots; anything else is reduced here.
+          const bool final_item = it + 1 == item_end;
+          if (final_item || !early_taken) {
             if (e == 0 && lane == 0)
-              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + 16), "r"(1u), "r"(item.row_block),
-                           "r"(first), "r"(item.parts) : "memory");
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + (final_item ? 16 : 32)), "r"(1u),
+                           "r"(item.row_block), "r"(first), "r"(item.parts) : "memory");
+            early_taken = early_taken || !final_item;
           } else {
             reduce_row_block<NB>(args, item.row_block, first, item.parts, e, 4, lane);
           }
@@ -397,13 +404,16 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     if (lane == 0) mbar_arrive(bar_final);
   }
 
-  // A row block whose last partial tile came from this CTA's final item is reduced by the 16 decoder warps and
-  // the 4 epilogue warps together.
+  // Row blocks whose last partial tile came from this CTA are reduced by the 16 decoder warps and the 4 epilogue
+  // warps together, once the epilogue has drained the CTA's last item.
   if (MODE == kUmma && (warp < kDecoderWarps || warp >= kWideWarpEpilogue)) {
     if (ctx.wait(bar_final, 0)) {
-      const uint4 verdict = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
-      if (verdict.x)
-        reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
+#pragma unroll 1
+      for (uint32_t at = 32; at >= 16; at -= 16) {
+        const uint4 verdict = lds128(smem + L::misc + at);  // {reduce?, row block, first slot, parts}
+        if (verdict.x)
+          reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
+      }
     }
   }
 

@@ -182,51 +182,77 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 
 // Ordered reduction of the FP32 partial tiles of one row block: y[m, row] = bf16(sum over parts in K order
 // (+ bias)).  Called by the CTA that delivered the last tile.  `group` warps share the work: warp g takes the
-// batch rows g, g + group, ...; a lane takes 4 consecutive weight rows (one float4 per tile), four batch rows
-// at a time so that 4 x parts loads are in flight per thread.
-template <int NB>
-__device__ __forceinline__ void reduce_row_block(const BxrArgs& args, uint32_t row_block, uint32_t first, uint32_t parts,
-                                                 uint32_t g, uint32_t group, uint32_t lane) {
+// batch rows g, g + group, ...; a lane takes 4 consecutive weight rows (one float4 per tile).  The tiles come from
+// other SMs through the L2, a round trip of half a microsecond: a thread asks for MS batch rows x PS tiles at once
+// and adds them, in tile order, when they are there.
+template <int NB, int MS, int PS>
+__device__ __forceinline__ void reduce_row_block_by(const BxrArgs& args, uint32_t row_block, uint32_t first, uint32_t parts,
+                                                    uint32_t g, uint32_t group, uint32_t lane) {
   const uint32_t r4 = lane * 4, row4 = row_block * BXR_ROWS + r4;
   if (row4 >= args.rows) return;
   float bias4[4] = {0.f, 0.f, 0.f, 0.f};
   if (args.bias)
     for (int i = 0; i < 4; ++i)
       if (row4 + i < args.rows) bias4[i] = __bfloat162float(args.bias[row4 + i]);
-  for (uint32_t m0 = g; m0 < args.m; m0 += 4 * group) {
-    float4 t[4];
+  const bool whole = row4 + 3 < args.rows;
+  for (uint32_t m0 = g; m0 < args.m; m0 += MS * group) {
+    float4 t[MS];
+    for (uint32_t p0 = 0; p0 < parts; p0 += PS) {
+      float4 v[MS][PS];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t m = m0 + group * j;
-      t[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first) * NB + m) * BXR_ROWS + r4))
+      for (int j = 0; j < MS; ++j)
+#pragma unroll
+        for (int q = 0; q < PS; ++q) {
+          const uint32_t m = m0 + group * j, p = p0 + q;
+          v[j][q] = (m < args.m && p < parts)
+                        ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4))
                         : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    for (uint32_t p = 1; p < parts; ++p) {
-      float4 v[4];
+        }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t m = m0 + group * j;
-        v[j] = m < args.m ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4))
-                          : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = 0; q < PS; ++q) {
+        if (p0 + q >= parts) break;
+#pragma unroll
+        for (int j = 0; j < MS; ++j) {
+          if (p0 + q == 0) {
+            t[j] = v[j][q];  // the first tile is taken as it is (adding it to zero would lose the sign of a -0)
+          } else {
+            t[j].x = __fadd_rn(t[j].x, v[j][q].x);
+            t[j].y = __fadd_rn(t[j].y, v[j][q].y);
+            t[j].z = __fadd_rn(t[j].z, v[j][q].z);
+            t[j].w = __fadd_rn(t[j].w, v[j][q].w);
+          }
+        }
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        t[j].x = __fadd_rn(t[j].x, v[j].x);
-        t[j].y = __fadd_rn(t[j].y, v[j].y);
-        t[j].z = __fadd_rn(t[j].z, v[j].z);
-        t[j].w = __fadd_rn(t[j].w, v[j].w);
-      }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < MS; ++j) {
       const uint32_t m = m0 + group * j;
       if (m >= args.m) continue;
       const float f[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
       __nv_bfloat16* dst = args.y + size_t(m) * args.ldy + row4;
-      for (int i = 0; i < 4; ++i)
-        if (row4 + i < args.rows) dst[i] = __float2bfloat16_rn(args.bias ? __fadd_rn(f[i], bias4[i]) : f[i]);
+      if (whole && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+        __nv_bfloat162 lo, hi;
+        lo.x = __float2bfloat16_rn(args.bias ? __fadd_rn(f[0], bias4[0]) : f[0]);
+        lo.y = __float2bfloat16_rn(args.bias ? __fadd_rn(f[1], bias4[1]) : f[1]);
+        hi.x = __float2bfloat16_rn(args.bias ? __fadd_rn(f[2], bias4[2]) : f[2]);
+        hi.y = __float2bfloat16_rn(args.bias ? __fadd_rn(f[3], bias4[3]) : f[3]);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst) = packed;
+      } else {
+        for (int i = 0; i < 4; ++i)
+          if (row4 + i < args.rows) dst[i] = __float2bfloat16_rn(args.bias ? __fadd_rn(f[i], bias4[i]) : f[i]);
+      }
     }
   }
+}
+template <int NB>
+__device__ __forceinline__ void reduce_row_block(const BxrArgs& args, uint32_t row_block, uint32_t first, uint32_t parts,
+                                                 uint32_t g, uint32_t group, uint32_t lane) {
+  // eight loads in flight per thread either way
+  if (parts <= 2) reduce_row_block_by<NB, 4, 2>(args, row_block, first, parts, g, group, lane);
+  else reduce_row_block_by<NB, 2, 4>(args, row_block, first, parts, g, group, lane);
 }
 
 template <int MODE, int NB>
