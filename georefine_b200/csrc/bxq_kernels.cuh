@@ -38,14 +38,18 @@ struct BxqSmem {
   static constexpr int kXLag = 2;
   static constexpr uint32_t kXStage = 2 * NB * 128;
   static constexpr uint32_t kReserve = 1024 /* alignment slack */ + 512 /* barriers, flags */;
-  static constexpr int kInFit = int((232448u - kReserve - kX * kXStage) / BXQ_BLOB_MAX);
+  // the epilogue warps turn their accumulator columns around in shared memory (a lane holds one weight row, memory
+  // wants consecutive rows together): 32 columns x 32 rows x 4 bytes per warp
+  static constexpr uint32_t kTurn = (MODE == kUmma) ? 4096u : 0u;
+  static constexpr int kInFit = int((232448u - kReserve - kX * kXStage - 4 * kTurn) / BXQ_BLOB_MAX);
   static constexpr int kIn = kInFit > 7 ? 7 : kInFit;   // (more barriers would not fit the one-per-lane set-up)
   static constexpr uint32_t xs = 0;
-  static constexpr uint32_t in = xs + kX * kXStage;
+  static constexpr uint32_t turn = xs + kX * kXStage;
+  static constexpr uint32_t in = turn + 4 * kTurn;
   static constexpr uint32_t bars = in + kIn * BXQ_BLOB_MAX;
   // barrier order: in_full, in_empty [kIn each]; op_full, op_empty [kOp each]; x_full [kX]; acc_full, acc_empty
-  // [2 each]; final
-  static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1;
+  // [2 each]; final; tile_full, tile_used [2 each] (the closing reduction)
+  static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1 + 4;
   static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, verdict
   static constexpr uint32_t total = misc + 48;
   static constexpr uint32_t alloc = total + 1024;
@@ -53,7 +57,6 @@ struct BxqSmem {
   // what keeps the activation loader at most one barrier phase behind the MMA issuer (see its role below)
   static_assert(MODE != kUmma || (kXLag < kX && kOp + kXLag + 1 > kX), "activation ring and lag do not fit the operand ring");
   static_assert(MODE != kUmma || 2 * NB <= int(kWideOperandCol), "accumulators overlap the operand columns");
-  static_assert(nbars <= 32, "one lane per barrier at set-up");
   static_assert(8 * nbars + 64 <= 512, "barrier area");
   static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
 };
@@ -98,6 +101,95 @@ __device__ __forceinline__ void bxq_patch(uint32_t (&out)[16], uint32_t column, 
     if (reg == uint32_t(i)) out[i] = (out[i] & ~(0x7F80u << sh)) | (exponent & 0xFFu) << (7 + sh);
 }
 
+// The closing reduction of a split row block, by the (kDecoderWarps + 4) x 32 threads that have nothing else left
+// to do: y[m, row] = bf16(sum of the row block's FP32 tiles in K order (+ bias)).  A reducing SM has to pull
+// (parts - 1) x NB x 512 bytes through its one L2 port, so the tiles come by bulk copy, two in flight, into the
+// shared memory the pipeline no longer needs (bytes [T, 3T) for T = NB x 512; the CTA's own last tile, if it takes
+// part, lies at [0, T) and was never in memory).  A thread owns the same few float4 positions of every tile and
+// keeps their running sums in registers.  `fetched` counts the tiles brought in so far by this CTA (barrier phases).
+template <int NB>
+__device__ __forceinline__ void bxq_reduce_row_block(const BxrArgs& args, const RoleCtx& ctx, uint32_t row_block, uint32_t first,
+                                                     uint32_t parts, uint32_t own, uint32_t smem, uint32_t bar_full, uint32_t bar_used,
+                                                     uint32_t t, uint32_t& fetched) {
+  constexpr uint32_t kThreads = (kDecoderWarps + 4) * 32;
+  constexpr int kMine = (NB * 32 + kThreads - 1) / kThreads;  // float4 positions per thread
+  constexpr uint32_t kTile = NB * BXR_ROWS * 4;
+  const uint32_t mcols = (args.m + 7) & ~7u, total = mcols * 32, bytes = mcols * BXR_ROWS * 4;
+  const uint32_t remote = parts - (own < parts ? 1u : 0u);
+  const uint32_t lane = t & 31;
+  uint32_t asked = 0;  // remote tiles requested in this call
+  bool live = true;
+  auto ask = [&](uint32_t j) {  // thread 0: the j-th remote tile into buffer (fetched + j) & 1, once its last readers are done
+    const uint32_t n = fetched + j, b = n & 1, p = j + ((own < parts && own <= j) ? 1u : 0u);
+    if (!ctx.wait(bar_used + 8 * b, ((n >> 1) & 1) ^ 1)) { live = false; return; }
+    mbar_arrive_expect_tx(bar_full + 8 * b, bytes);
+    bulk_g2s(smem + kTile * (1 + b), args.partials + size_t(first + p) * NB * BXR_ROWS, bytes, bar_full + 8 * b, l2_policy_evict_first());
+    asked = j + 1;
+  };
+  if (t == 0)
+    for (uint32_t j = 0; j < 2 && j < remote && live; ++j) ask(j);
+  float4 sum[kMine];
+  uint32_t j = 0;  // remote tiles consumed
+  for (uint32_t p = 0; p < parts && live; ++p) {
+    uint32_t src = smem, b = 0;
+    if (p != own) {
+      const uint32_t n = fetched + j;
+      b = n & 1;
+      if (!ctx.wait(bar_full + 8 * b, (n >> 1) & 1)) { live = false; break; }
+      src = smem + kTile * (1 + b);
+    }
+#pragma unroll
+    for (int k = 0; k < kMine; ++k) {
+      const uint32_t at = t + k * kThreads;
+      if (at < total) {
+        const uint4 u = lds128(src + at * 16);
+        if (p == 0) {  // taken as it is: adding it to zero would lose the sign of a -0
+          sum[k] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+        } else {
+          sum[k].x = __fadd_rn(sum[k].x, __uint_as_float(u.x));
+          sum[k].y = __fadd_rn(sum[k].y, __uint_as_float(u.y));
+          sum[k].z = __fadd_rn(sum[k].z, __uint_as_float(u.z));
+          sum[k].w = __fadd_rn(sum[k].w, __uint_as_float(u.w));
+        }
+      }
+    }
+    if (p != own) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_used + 8 * b);
+      if (t == 0 && j + 2 < remote) ask(j + 2);
+      ++j;
+    }
+  }
+  if (t == 0 && !live)  // unwinding: copies still in flight must land before the CTA may exit
+    for (uint32_t k = j; k < asked; ++k) mbar_wait(bar_full + 8 * ((fetched + k) & 1), ((fetched + k) >> 1) & 1);
+  fetched += remote;
+  if (!live) return;
+#pragma unroll
+  for (int k = 0; k < kMine; ++k) {
+    const uint32_t at = t + k * kThreads, m = at >> 5, row4 = row_block * BXR_ROWS + (at & 31) * 4;
+    if (at >= total || m >= args.m || row4 >= args.rows) continue;
+    float f[4] = {sum[k].x, sum[k].y, sum[k].z, sum[k].w};
+    if (args.bias)
+      for (int i = 0; i < 4; ++i)
+        if (row4 + i < args.rows) f[i] = __fadd_rn(f[i], __bfloat162float(args.bias[row4 + i]));
+    __nv_bfloat16* dst = args.y + size_t(m) * args.ldy + row4;
+    if (row4 + 3 < args.rows && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+      __nv_bfloat162 lo, hi;
+      lo.x = __float2bfloat16_rn(f[0]);
+      lo.y = __float2bfloat16_rn(f[1]);
+      hi.x = __float2bfloat16_rn(f[2]);
+      hi.y = __float2bfloat16_rn(f[3]);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = packed;
+    } else {
+      for (int i = 0; i < 4; ++i)
+        if (row4 + i < args.rows) dst[i] = __float2bfloat16_rn(f[i]);
+    }
+  }
+}
+
 template <int MODE, int NB>
 __global__ void __launch_bounds__(MODE == kUmma ? kThreadsUmma : kThreadsSimt, 1)
 bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
@@ -117,6 +209,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
   const uint32_t bar_x_full = bar_op_empty + 8 * L::kOp;
   const uint32_t bar_acc_full = bar_x_full + 8 * L::kX, bar_acc_empty = bar_acc_full + 16, bar_final = bar_acc_empty + 16;
+  const uint32_t bar_tile_full = bar_final + 8, bar_tile_used = bar_tile_full + 16;
   constexpr uint32_t kTmemCols = kWideTmemCols;
   constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;
   constexpr uint32_t kXN = L::kX ? L::kX : 1;
@@ -132,17 +225,20 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     first_i0 = __ldg(args.blob_index + mine);
     first_i1 = __ldg(args.blob_index + mine + 1);
   }
-  if (warp == 0) {  // one barrier per lane
-    static_assert(L::nbars <= 32, "one lane per barrier");
+  if (warp == 0) {  // one or two barriers per lane
+    static_assert(L::nbars <= 64, "two barriers per lane at most");
     const uint32_t i = lane;
-    uint32_t count = 1;                                                          // in_full, op_empty, x_full
-    if (i >= uint32_t(L::kIn) && i < 2u * L::kIn) count = kDecoderWarps;          // in_empty
-    else if (i >= 2u * L::kIn && i < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
-    else if (i >= 2u * L::kIn + 2 * L::kOp + L::kX) {
-      const uint32_t j = i - (2u * L::kIn + 2 * L::kOp + L::kX);                  // acc_full x2, acc_empty x2, final
-      count = j < 2 ? 1u : 4u;                                                   // the MMA issuer's commit / the epilogue warps
+#pragma unroll
+    for (uint32_t n = i; n < L::nbars; n += 32) {
+      uint32_t count = 1;                                                          // in_full, op_empty, x_full
+      if (n >= uint32_t(L::kIn) && n < 2u * L::kIn) count = kDecoderWarps;          // in_empty
+      else if (n >= 2u * L::kIn && n < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
+      else if (n >= 2u * L::kIn + 2 * L::kOp + L::kX) {
+        const uint32_t j = n - (2u * L::kIn + 2 * L::kOp + L::kX);  // acc_full x2, acc_empty x2, final, tile_full x2, tile_used x2
+        count = j < 2 ? 1u : j < 5 ? 4u : j < 7 ? 1u : uint32_t(kDecoderWarps + 4);
+      }
+      mbar_init(ctx.bars + 8 * n, count);
     }
-    if (i < L::nbars) mbar_init(ctx.bars + 8 * i, count);
     // flags: abort at misc + 4, epilogue verdict at misc + 8, final verdict at misc + 16 (misc + 0 receives the TMEM
     // base address from the allocating warp and is left alone here)
     if (i == 0) asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
@@ -228,6 +324,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   } else if (warp == kWideWarpLoader) {
     // ------------------------------------------------------------------ chunk blobs, one bulk copy each
     uint32_t issued = 0;
+    const uint64_t once = l2_policy_evict_first();  // a blob is read once per launch
     for (uint32_t u0 = 0; u0 < unit_count; u0 += 32) {
       uint32_t i0 = first_i0, i1 = first_i1;
       if (args.blob_stride16) {  // blobs of one size: no offsets to look up
@@ -252,7 +349,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         }
         if (lane == 0) {
           mbar_arrive_expect_tx(bar_in_full + 8 * s, bytes);
-          bulk_g2s(smem + L::in + s * BXQ_BLOB_MAX, args.blobs + (size_t(b0) << 4), bytes, bar_in_full + 8 * s);
+          bulk_g2s(smem + L::in + s * BXQ_BLOB_MAX, args.blobs + (size_t(b0) << 4), bytes, bar_in_full + 8 * s, once);
         }
         issued = u + 1;
       }
@@ -271,6 +368,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     // because the multiply of chunk c + kOp needs its own go-ahead.
     if (lane == 0) {
       grid_dependency_wait();
+      const uint64_t stay = l2_policy_evict_last();  // every CTA reads the same activation tiles
       bool live = true;
       uint32_t it_v = item_begin, c_v = 0;  // cursor of the chunk to request: item and chunk inside it
       bxr_item item_v = args.items[item_begin < item_end ? item_begin : 0];
@@ -289,8 +387,8 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           if (v >= kXN && !multiplied(v - kXN)) { live = false; break; }
           const uint32_t sx = v % kXN, stage = smem + L::xs + sx * L::kXStage;
           mbar_arrive_expect_tx(bar_x_full + 8 * sx, L::kXStage);
-          tma_load_2d(stage, &tmap_x, int(c_v * BXR_COLS), 0, bar_x_full + 8 * sx);
-          tma_load_2d(stage + NB * 128, &tmap_x, int(c_v * BXR_COLS + 64), 0, bar_x_full + 8 * sx);
+          tma_load_2d(stage, &tmap_x, int(c_v * BXR_COLS), 0, bar_x_full + 8 * sx, stay);
+          tma_load_2d(stage + NB * 128, &tmap_x, int(c_v * BXR_COLS + 64), 0, bar_x_full + 8 * sx, stay);
           if (++c_v == item_v.chunk_end && it_v + 1 < item_end) {
             item_v = args.items[++it_v];
             c_v = item_v.chunk_begin;
@@ -339,6 +437,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t mcols = (args.m + 7) & ~7u;
     uint32_t n_item = 0;
     bool live = true, early_taken = false;
+    const uint64_t stay = l2_policy_evict_last();  // partial tiles are read back within the launch
     grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
       const bxr_item item = args.items[it];
@@ -349,55 +448,119 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       const uint32_t taddr = tmem_base + ((e * 32) << 16) + buf * NB;
       const float b = (args.bias && row < args.rows) ? __bfloat162float(args.bias[row]) : 0.f;
       constexpr int kStep = NB >= 32 ? 32 : 16;  // accumulator columns per tensor-memory load
+      // The CTA's last item, if it is part of a split row block, keeps its tile in shared memory (all of it is free
+      // by now: every blob and every activation tile has been multiplied).  If the other tiles of the row block are already in memory -
+      // the usual case, they were finished long ago as some CTA's first item - this tile never goes to memory at
+      // all: no store, no fence, no counter update on the tail of the kernel.
+      const bool final_item = it + 1 == item_end;
+      const bool keep = item.parts > 1 && final_item;
+      const uint32_t tile = smem;           // [batch row][128 weight rows] FP32, like a partial tile in memory
+      uint32_t arrived = 0;
+      if (keep && e == 0 && lane == 0) arrived = ld_acquire_gpu(args.counters + item.row_block);  // answer used after the drain
+      // A lane holds one weight row and kStep batch columns; y and the partial tiles keep the rows of one batch
+      // column together.  Stored from the registers that is one narrow store instruction per column, and the
+      // store queue, not the memory, sets the pace (a 128-column drain took 4 400 to 10 000 cycles).  So the
+      // columns are turned around in shared memory and leave as 16-byte stores: 8 (y) or 4 (tiles) columns each.
+      const uint32_t turn = smem + L::turn + e * L::kTurn;
+      const bool y_wide = (reinterpret_cast<uintptr_t>(args.y) & 15u) == 0 && (args.ldy & 7u) == 0 &&
+                          item.row_block * BXR_ROWS + e * 32 + 32 <= args.rows;
       for (uint32_t m0 = 0; m0 < mcols; m0 += kStep) {
         uint32_t v[kStep];
         if constexpr (kStep == 32) tmem_ld32(taddr + m0, v);
         else tmem_ld16(taddr + m0, v);
         tmem_ld_wait();
-        if (item.parts == 1) {
-          if (row < args.rows)
+        if (keep) {
+#pragma unroll
+          for (int i = 0; i < kStep; ++i)
+            if (m0 + i < mcols) sts32(tile + ((m0 + i) * BXR_ROWS + r) * 4, v[i]);
+        } else if (item.parts == 1) {
+          if (y_wide) {
+#pragma unroll
+            for (int i = 0; i < kStep; ++i) {
+              const float f = __uint_as_float(v[i]);
+              const __nv_bfloat16 h = __float2bfloat16_rn(args.bias ? __fadd_rn(f, b) : f);
+              sts_u16(turn + (i * 32 + lane) * 2, uint32_t(*reinterpret_cast<const uint16_t*>(&h)));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < kStep / 8; ++j) {  // a store: 8 columns x 64 bytes (32 rows)
+              const uint32_t ml = j * 8 + (lane >> 2), m = m0 + ml;
+              const uint4 piece = lds128(turn + ml * 64 + (lane & 3) * 16);
+              if (m < args.m)
+                *reinterpret_cast<uint4*>(args.y + size_t(m) * args.ldy + item.row_block * BXR_ROWS + e * 32 + (lane & 3) * 8) = piece;
+            }
+            __syncwarp();
+          } else if (row < args.rows) {
 #pragma unroll
             for (int i = 0; i < kStep; ++i)
               if (m0 + i < args.m) {
                 const float f = __uint_as_float(v[i]);
                 args.y[size_t(m0 + i) * args.ldy + row] = __float2bfloat16_rn(args.bias ? __fadd_rn(f, b) : f);
               }
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < kStep; ++i)
-            if (m0 + i < mcols) args.partials[(size_t(item.slot) * NB + m0 + i) * BXR_ROWS + r] = __uint_as_float(v[i]);
+          for (int i = 0; i < kStep; ++i) sts32(turn + (i * 32 + lane) * 4, v[i]);
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < kStep / 4; ++j) {  // a store: 4 columns x 128 bytes (32 rows)
+            const uint32_t ml = j * 4 + (lane >> 3), m = m0 + ml;
+            const uint4 piece = lds128(turn + ml * 128 + (lane & 7) * 16);
+            if (m < mcols) stg128(args.partials + (size_t(item.slot) * NB + m) * BXR_ROWS + e * 32 + (lane & 7) * 4, piece, stay);
+          }
+          __syncwarp();
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
       if (item.parts > 1) {
-        __threadfence();
-        named_barrier(1, 128);
-        if (e == 0 && lane == 0) {
-          const uint32_t prev = atomicAdd(args.counters + item.row_block, 1u);
-          asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(prev) : "memory");
-        }
-        named_barrier(1, 128);
+        // `prev` = how many tiles of the row block were in memory before this one; the CTA that completes the set
+        // reduces it.  Flag words: misc + 8 and misc + 12.
         uint32_t prev;
-        asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
-        if (prev == item.parts - 1) {  // every partial tile of this row block is in memory: add them in K order
+        if (keep) {
+          fence_proxy_async_smem();  // the tile may leave through a bulk copy
+          if (e == 0 && lane == 0) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(arrived) : "memory");
+          named_barrier(1, 128);
+          asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
+          if (prev != item.parts - 1) {  // someone else is still missing: publish the tile like any other
+            if (e == 0 && lane == 0) {
+              bulk_s2g(args.partials + size_t(item.slot) * NB * BXR_ROWS, tile, mcols * BXR_ROWS * 4);
+              bulk_commit_and_wait();
+              fence_proxy_async_all();
+              __threadfence();
+              const uint32_t before = atomicAdd(args.counters + item.row_block, 1u);
+              asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 12), "r"(before) : "memory");
+            }
+            named_barrier(1, 128);
+            asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 12));
+          }
+        } else {
+          __threadfence();
+          named_barrier(1, 128);
+          if (e == 0 && lane == 0) {
+            const uint32_t before = atomicAdd(args.counters + item.row_block, 1u);
+            asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(before) : "memory");
+          }
+          named_barrier(1, 128);
+          asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
+        }
+        if (prev == item.parts - 1) {  // every other tile of this row block is in memory: add them in K order
           __threadfence();
           const uint32_t first = item.slot - item.part;
           // Reduced at the end of the CTA by the decoder and epilogue warps together (below).  Only the first and the
           // last item of a CTA can be part of a split row block, hence two verdict slots; anything else is reduced here.
-          const bool final_item = it + 1 == item_end;
           if (final_item || !early_taken) {
-            if (e == 0 && lane == 0)
-              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + (final_item ? 16 : 32)), "r"(1u),
-                           "r"(item.row_block), "r"(first), "r"(item.parts) : "memory");
+            if (e == 0 && lane == 0)  // {1 | (index + 1 of the tile kept in shared memory) << 8, row block, first slot, parts}
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + (final_item ? 16 : 32)),
+                           "r"(1u | (keep ? (item.part + 1u) << 8 : 0u)), "r"(item.row_block), "r"(first), "r"(item.parts) : "memory");
             early_taken = early_taken || !final_item;
           } else {
             reduce_row_block<NB>(args, item.row_block, first, item.parts, e, 4, lane);
           }
           if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
         }
-        named_barrier(1, 128);  // the verdict word may be rewritten
+        named_barrier(1, 128);  // the flag words may be rewritten
       }
     }
     __syncwarp();
@@ -408,11 +571,13 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   // warps together, once the epilogue has drained the CTA's last item.
   if (MODE == kUmma && (warp < kDecoderWarps || warp >= kWideWarpEpilogue)) {
     if (ctx.wait(bar_final, 0)) {
+      uint32_t fetched = 0;  // tiles brought in so far: position in the two-buffer ring
 #pragma unroll 1
       for (uint32_t at = 32; at >= 16; at -= 16) {
-        const uint4 verdict = lds128(smem + L::misc + at);  // {reduce?, row block, first slot, parts}
+        const uint4 verdict = lds128(smem + L::misc + at);  // {reduce? | own tile << 8, row block, first slot, parts}
         if (verdict.x)
-          reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
+          bxq_reduce_row_block<NB>(args, ctx, verdict.y, verdict.z, verdict.w, (verdict.x >> 8) - 1u, smem, bar_tile_full, bar_tile_used,
+                                   (warp < kDecoderWarps ? warp : warp - 4) * 32 + lane, fetched);
       }
     }
   }

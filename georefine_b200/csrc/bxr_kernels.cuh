@@ -184,10 +184,11 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 // (+ bias)).  Called by the CTA that delivered the last tile.  `group` warps share the work: warp g takes the
 // batch rows g, g + group, ...; a lane takes 4 consecutive weight rows (one float4 per tile).  The tiles come from
 // other SMs through the L2, a round trip of half a microsecond: a thread asks for MS batch rows x PS tiles at once
-// and adds them, in tile order, when they are there.
+// and adds them, in tile order, when they are there.  Tile `own` (an index among the parts; none if >= parts) is
+// read from shared memory at `own_tile` instead, in the same [batch row][128 weight rows] order.
 template <int NB, int MS, int PS>
 __device__ __forceinline__ void reduce_row_block_by(const BxrArgs& args, uint32_t row_block, uint32_t first, uint32_t parts,
-                                                    uint32_t g, uint32_t group, uint32_t lane) {
+                                                    uint32_t g, uint32_t group, uint32_t lane, uint32_t own, uint32_t own_tile) {
   const uint32_t r4 = lane * 4, row4 = row_block * BXR_ROWS + r4;
   if (row4 >= args.rows) return;
   float bias4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -204,9 +205,16 @@ __device__ __forceinline__ void reduce_row_block_by(const BxrArgs& args, uint32_
 #pragma unroll
         for (int q = 0; q < PS; ++q) {
           const uint32_t m = m0 + group * j, p = p0 + q;
-          v[j][q] = (m < args.m && p < parts)
-                        ? __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4))
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
+          if (m < args.m && p < parts) {
+            if (p == own) {
+              const uint4 u = lds128(own_tile + (m * BXR_ROWS + r4) * 4);
+              v[j][q] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+            } else {
+              v[j][q] = __ldcg(reinterpret_cast<const float4*>(args.partials + (size_t(first + p) * NB + m) * BXR_ROWS + r4));
+            }
+          } else {
+            v[j][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
 #pragma unroll
       for (int q = 0; q < PS; ++q) {
@@ -249,10 +257,11 @@ __device__ __forceinline__ void reduce_row_block_by(const BxrArgs& args, uint32_
 }
 template <int NB>
 __device__ __forceinline__ void reduce_row_block(const BxrArgs& args, uint32_t row_block, uint32_t first, uint32_t parts,
-                                                 uint32_t g, uint32_t group, uint32_t lane) {
+                                                 uint32_t g, uint32_t group, uint32_t lane, uint32_t own = 0xFFFFFFFFu,
+                                                 uint32_t own_tile = 0) {
   // eight loads in flight per thread either way
-  if (parts <= 2) reduce_row_block_by<NB, 4, 2>(args, row_block, first, parts, g, group, lane);
-  else reduce_row_block_by<NB, 2, 4>(args, row_block, first, parts, g, group, lane);
+  if (parts <= 2) reduce_row_block_by<NB, 4, 2>(args, row_block, first, parts, g, group, lane, own, own_tile);
+  else reduce_row_block_by<NB, 2, 4>(args, row_block, first, parts, g, group, lane, own, own_tile);
 }
 
 template <int MODE, int NB>
