@@ -4,7 +4,7 @@
 //   * kUmma  : a lane holds the 32 weights of its row and phase in 16 registers and writes them with one tcgen05.st
 //              into tensor memory, where tcgen05.mma takes them as its A operand (M = 128 weight rows; the batch is
 //              N, read from shared memory).  Shared memory carries only what comes from outside the SM: chunk blobs
-//              and activation tiles.  (In the 3-bit window kernel the operand tile lives in shared memory, and its
+//              and activation tiles.  Two threads issue the MMAs, chunk about, each into an accumulator of its own.  (In the 3-bit window kernel the operand tile lives in shared memory, and its
 //              stores plus the tensor core's reads of it are more than 40 % of all shared-memory traffic, which sets
 //              that kernel's pace; its per-chunk exception patching is what keeps it from using tensor memory: done
 //              in registers it costs more instructions than the decode itself.)
@@ -17,13 +17,16 @@
 namespace grb {
 
 constexpr int kWideWarpLoader = 16;    // bulk copies of chunk blobs
-constexpr int kWideWarpMma = 17;       // TMEM owner and MMA issuer
+constexpr int kWideWarpMma = 17;       // TMEM owner and MMA issuer of the even chunks of an item
+constexpr int kWideWarpMma2 = 19;      // MMA issuer of the odd chunks
 constexpr int kWideWarpXLoader = 18;   // TMA loads of activation tiles
-                                       // warp 19 idles so that the epilogue warps keep warp % 4 = TMEM lane quarter
-constexpr int kWideWarpEpilogue = 20;  // 4 warps
+constexpr int kWideWarpEpilogue = 20;  // 4 warps: warp % 4 = the tensor-memory lane quarter a warp may read
 
-// Tensor memory: columns [0, 2 NB) two accumulators (one item being multiplied, one being drained); columns
-// [256, 512) the decoded weights of kWideStages chunks, 64 columns each (two 128 x 64 atoms, two BF16 per column).
+// Tensor memory: columns [0, 256) accumulators, FP32: an item has two, one per MMA issuer (even chunks, odd chunks;
+// the epilogue adds them), NB columns each.  Up to NB = 64 two items fit (one being multiplied, one being drained);
+// at NB = 128 there is room for one, and the issuers wait for the drain at an item boundary while the decoders fill
+// the operand stages.  Columns [256, 512): the decoded weights of kWideStages chunks, 64 columns each (two 128 x 64
+// atoms, two BF16 per column).
 constexpr uint32_t kWideTmemCols = 512;
 constexpr uint32_t kWideOperandCol = 256;
 constexpr int kWideStages = 4;
@@ -39,8 +42,8 @@ struct BxqSmem {
   static constexpr uint32_t kXStage = 2 * NB * 128;
   static constexpr uint32_t kReserve = 1024 /* alignment slack */ + 512 /* barriers, flags */;
   // the epilogue warps turn their accumulator columns around in shared memory (a lane holds one weight row, memory
-  // wants consecutive rows together): 32 columns x 32 rows x 4 bytes per warp
-  static constexpr uint32_t kTurn = (MODE == kUmma) ? 4096u : 0u;
+  // wants consecutive rows together): 16 columns x 32 rows x 4 bytes per warp
+  static constexpr uint32_t kTurn = (MODE == kUmma) ? 2048u : 0u;
   static constexpr int kInFit = int((232448u - kReserve - kX * kXStage - 4 * kTurn) / BXQ_BLOB_MAX);
   static constexpr int kIn = kInFit > 7 ? 7 : kInFit;   // (more barriers would not fit the one-per-lane set-up)
   static constexpr uint32_t xs = 0;
@@ -56,7 +59,7 @@ struct BxqSmem {
   static_assert(MODE != kUmma || kIn >= 4, "ring too shallow");
   // what keeps the activation loader at most one barrier phase behind the MMA issuer (see its role below)
   static_assert(MODE != kUmma || (kXLag < kX && kOp + kXLag + 1 > kX), "activation ring and lag do not fit the operand ring");
-  static_assert(MODE != kUmma || 2 * NB <= int(kWideOperandCol), "accumulators overlap the operand columns");
+  static_assert(MODE != kUmma || 2 * NB * (NB <= 64 ? 2 : 1) <= int(kWideOperandCol), "accumulators overlap the operand columns");
   static_assert(8 * nbars + 64 <= 512, "barrier area");
   static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
 };
@@ -213,6 +216,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   constexpr uint32_t kTmemCols = kWideTmemCols;
   constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;
   constexpr uint32_t kXN = L::kX ? L::kX : 1;
+  constexpr uint32_t kAccBufs = NB <= 64 ? 2 : 1;  // items whose accumulators fit tensor memory at once
 
   // Work of this CTA, known from the arguments alone; the blob loader asks for its first offsets before anything
   // else so that the first copy can leave as soon as the barriers exist.
@@ -235,7 +239,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       else if (n >= 2u * L::kIn && n < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
       else if (n >= 2u * L::kIn + 2 * L::kOp + L::kX) {
         const uint32_t j = n - (2u * L::kIn + 2 * L::kOp + L::kX);  // acc_full x2, acc_empty x2, final, tile_full x2, tile_used x2
-        count = j < 2 ? 1u : j < 5 ? 4u : j < 7 ? 1u : uint32_t(kDecoderWarps + 4);
+        count = j < 2 ? 2u : j < 5 ? 4u : j < 7 ? 1u : uint32_t(kDecoderWarps + 4);  // acc_full: both MMA issuers commit
       }
       mbar_init(ctx.bars + 8 * n, count);
     }
@@ -396,34 +400,41 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
         }
       }
     }
-  } else if (MODE == kUmma && warp == kWideWarpMma) {
+  } else if (MODE == kUmma && (warp == kWideWarpMma || warp == kWideWarpMma2)) {
     // ------------------------------------------------------------------ MMA issue: one wait, eight MMAs, one commit
+    // Issuing takes a thread about a hundred cycles per MMA, more than the tensor core needs for it: two threads
+    // take turns chunk by chunk.  The order of additions has to be a fixed one, so each has an accumulator of its own:
+    // chunk i of an item (counted from the item's first) goes to accumulator i mod 2, whatever the batch size.
     constexpr uint32_t idesc = umma_idesc_bf16(NB);
+    const uint32_t which = warp == kWideWarpMma2 ? 1u : 0u;
     uint32_t n_item = 0, so = 0, pho = 0, sx = 0;
     bool live = true;
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
       const bxr_item item = args.items[it];
-      const uint32_t buf = n_item & 1;
-      if (ctx.aborted() || !ctx.wait(bar_acc_empty + 8 * buf, ((n_item >> 1) & 1) ^ 1)) { live = false; break; }
+      const uint32_t buf = n_item % kAccBufs, use = n_item / kAccBufs;
+      if (ctx.aborted() || !ctx.wait(bar_acc_empty + 8 * buf, (use & 1) ^ 1)) { live = false; break; }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * NB;
-      uint32_t accumulate = 0;
+      const uint32_t d_tmem = tmem_base + (buf * 2 + which) * NB;
       for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c) {
-        if (!ctx.wait(bar_op_full + 8 * so, pho)) { live = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_tmem = tmem_base + kWideOperandCol + so * 64;
-          const uint64_t bdesc = umma_desc_sw128(smem + L::xs + sx * L::kXStage);
+        const uint32_t i = c - item.chunk_begin;
+        if ((i & 1) == which) {
+          if (!ctx.wait(bar_op_full + 8 * so, pho)) { live = false; break; }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t a_tmem = tmem_base + kWideOperandCol + so * 64;
+            const uint64_t bdesc = umma_desc_sw128(smem + L::xs + sx * L::kXStage);
+            uint32_t accumulate = i >= 2 ? 1u : 0u;
 #pragma unroll
-          for (uint32_t a = 0; a < 2; ++a)
+            for (uint32_t a = 0; a < 2; ++a)
 #pragma unroll
-            for (uint32_t k = 0; k < 4; ++k) {
-              umma_bf16_ts(d_tmem, a_tmem + a * 32 + k * 8, bdesc + a * (NB * 128 >> 4) + 2 * k, idesc, accumulate);
-              accumulate = 1;
-            }
-          umma_commit(bar_op_empty + 8 * so);
+              for (uint32_t k = 0; k < 4; ++k) {
+                umma_bf16_ts(d_tmem, a_tmem + a * 32 + k * 8, bdesc + a * (NB * 128 >> 4) + 2 * k, idesc, accumulate);
+                accumulate = 1;
+              }
+            umma_commit(bar_op_empty + 8 * so);
+          }
+          __syncwarp();
         }
-        __syncwarp();
         if (++so == kOpN) { so = 0; pho ^= 1; }
         if (++sx == kXN) sx = 0;
       }
@@ -441,13 +452,14 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
       const bxr_item item = args.items[it];
-      const uint32_t buf = n_item & 1;
-      if (ctx.aborted() || !ctx.wait(bar_acc_full + 8 * buf, (n_item >> 1) & 1)) { live = false; break; }
+      const uint32_t buf = n_item % kAccBufs, use = n_item / kAccBufs;
+      if (ctx.aborted() || !ctx.wait(bar_acc_full + 8 * buf, use & 1)) { live = false; break; }
       tc_fence_after();
       const uint32_t row = item.row_block * BXR_ROWS + r;
-      const uint32_t taddr = tmem_base + ((e * 32) << 16) + buf * NB;
+      const uint32_t taddr = tmem_base + ((e * 32) << 16) + buf * 2 * NB;   // even-chunk accumulator; the odd one NB columns on
+      const bool two = item.chunk_end - item.chunk_begin > 1;                // a one-chunk item has no odd chunk
       const float b = (args.bias && row < args.rows) ? __bfloat162float(args.bias[row]) : 0.f;
-      constexpr int kStep = NB >= 32 ? 32 : 16;  // accumulator columns per tensor-memory load
+      constexpr int kStep = 16;  // accumulator columns per tensor-memory load
       // The CTA's last item, if it is part of a split row block, keeps its tile in shared memory (all of it is free
       // by now: every blob and every activation tile has been multiplied).  If the other tiles of the row block are already in memory -
       // the usual case, they were finished long ago as some CTA's first item - this tile never goes to memory at
@@ -466,9 +478,16 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
                           item.row_block * BXR_ROWS + e * 32 + 32 <= args.rows;
       for (uint32_t m0 = 0; m0 < mcols; m0 += kStep) {
         uint32_t v[kStep];
-        if constexpr (kStep == 32) tmem_ld32(taddr + m0, v);
-        else tmem_ld16(taddr + m0, v);
-        tmem_ld_wait();
+        tmem_ld16(taddr + m0, v);
+        if (two) {
+          uint32_t odd[kStep];
+          tmem_ld16(taddr + NB + m0, odd);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < kStep; ++i) v[i] = __float_as_uint(__fadd_rn(__uint_as_float(v[i]), __uint_as_float(odd[i])));
+        } else {
+          tmem_ld_wait();
+        }
         if (keep) {
 #pragma unroll
           for (int i = 0; i < kStep; ++i)
