@@ -229,11 +229,37 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     first_i0 = __ldg(args.blob_index + mine);
     first_i1 = __ldg(args.blob_index + mine + 1);
   }
+  // The CTA's item list and its first item: asked for now, needed after the set-up.
+  const uint32_t item_begin = __ldg(args.worker_items + worker), item_end = __ldg(args.worker_items + worker + 1);
+  bxr_item first_item = {};
+  if (item_begin < item_end) first_item = args.items[item_begin];
+  uint32_t first_base = 0;  // decoders: the window base of this thread's row in the first item
+  if (warp < kDecoderWarps && item_begin < item_end) first_base = args.base[first_item.row_block * BXR_ROWS + (warp & 3) * 32 + lane];
+  // An SM runs the launches of a stream back to back, so whatever a CTA does before its first multiply is not hidden
+  // behind the previous launch on the SM that finished last.  The longest wait in it is the first blob's trip from
+  // HBM: with blobs of one size the loader needs nothing but its own barriers to start it, and sets those up itself.
+  uint32_t early = 0;
+  if (warp == kWideWarpLoader && args.blob_stride16) {
+    const uint32_t bytes = args.blob_stride16 << 4;
+    if (bytes <= BXQ_BLOB_MAX && bytes >= BXQ_LIST_AT) early = min(unit_count, uint32_t(L::kIn));
+    if (lane == 0) {
+      for (uint32_t n = 0; n < uint32_t(L::kIn); ++n) mbar_init(bar_in_full + 8 * n, 1);
+      mbar_fence_init();
+      fence_proxy_async_smem();
+      const uint64_t once = l2_policy_evict_first();
+      for (uint32_t u = 0; u < early; ++u) {
+        mbar_arrive_expect_tx(bar_in_full + 8 * u, bytes);
+        bulk_g2s(smem + L::in + u * BXQ_BLOB_MAX, args.blobs + size_t(unit_begin + u) * bytes, bytes, bar_in_full + 8 * u, once);
+      }
+    }
+    __syncwarp();
+  }
   if (warp == 0) {  // one or two barriers per lane
     static_assert(L::nbars <= 64, "two barriers per lane at most");
     const uint32_t i = lane;
 #pragma unroll
     for (uint32_t n = i; n < L::nbars; n += 32) {
+      if (n < uint32_t(L::kIn) && args.blob_stride16) continue;                    // in_full: the loader's own (above)
       uint32_t count = 1;                                                          // in_full, op_empty, x_full
       if (n >= uint32_t(L::kIn) && n < 2u * L::kIn) count = kDecoderWarps;          // in_empty
       else if (n >= 2u * L::kIn && n < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
@@ -264,7 +290,6 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   uint32_t tmem_base = 0;
   if (MODE == kUmma) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(smem + L::misc));
 
-  const uint32_t item_begin = args.worker_items[worker], item_end = args.worker_items[worker + 1];
 
   if (warp < kDecoderWarps) {
     // ------------------------------------------------------------------ decoders: 32 weights per lane and chunk
@@ -277,9 +302,9 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t operand_at = ((rg * 32u) << 16) + kWideOperandCol + (q >> 1) * 32 + (q & 1) * 16;
     bool live = true;
     for (uint32_t it = item_begin; it < item_end && live; ++it) {
-      const bxr_item item = args.items[it];
+      const bxr_item item = it == item_begin ? first_item : args.items[it];
       const uint32_t row = item.row_block * BXR_ROWS + r;
-      const uint32_t base2 = uint32_t(args.base[row]) * 0x00800080u;
+      const uint32_t base2 = uint32_t(it == item_begin ? first_base : args.base[row]) * 0x00800080u;
       for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c) {
         if (!ctx.wait(bar_in_full + 8 * s, ph)) { live = false; break; }
         const uint32_t blob = smem + L::in + s * BXQ_BLOB_MAX;
@@ -344,6 +369,10 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       for (uint32_t i = 0; i < n && live; ++i) {
         const uint32_t u = u0 + i, s = u % L::kIn, ph = (u / L::kIn) & 1;
         const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, i0, i), b1 = __shfl_sync(0xFFFFFFFFu, i1, i);
+        if (u < early) {  // requested before the set-up
+          issued = u + 1;
+          continue;
+        }
         const uint32_t bytes = (b1 - b0) << 4;
         if (ctx.aborted() || !ctx.wait(bar_in_empty + 8 * s, ph ^ 1)) { live = false; break; }
         if (b1 < b0 || bytes > BXQ_BLOB_MAX || bytes < BXQ_LIST_AT) {
@@ -375,7 +404,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       const uint64_t stay = l2_policy_evict_last();  // every CTA reads the same activation tiles
       bool live = true;
       uint32_t it_v = item_begin, c_v = 0;  // cursor of the chunk to request: item and chunk inside it
-      bxr_item item_v = args.items[item_begin < item_end ? item_begin : 0];
+      bxr_item item_v = first_item;
       c_v = item_v.chunk_begin;
       auto multiplied = [&](uint32_t c) { return ctx.wait(bar_op_empty + 8 * (c % kOpN), (c / kOpN) & 1); };
       for (uint32_t v = 0; v < unit_count + L::kXLag && live; ++v) {
@@ -410,7 +439,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     uint32_t n_item = 0, so = 0, pho = 0, sx = 0;
     bool live = true;
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
-      const bxr_item item = args.items[it];
+      const bxr_item item = it == item_begin ? first_item : args.items[it];
       const uint32_t buf = n_item % kAccBufs, use = n_item / kAccBufs;
       if (ctx.aborted() || !ctx.wait(bar_acc_empty + 8 * buf, (use & 1) ^ 1)) { live = false; break; }
       tc_fence_after();
@@ -451,7 +480,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint64_t stay = l2_policy_evict_last();  // partial tiles are read back within the launch
     grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
-      const bxr_item item = args.items[it];
+      const bxr_item item = it == item_begin ? first_item : args.items[it];
       const uint32_t buf = n_item % kAccBufs, use = n_item / kAccBufs;
       if (ctx.aborted() || !ctx.wait(bar_acc_full + 8 * buf, use & 1)) { live = false; break; }
       tc_fence_after();
