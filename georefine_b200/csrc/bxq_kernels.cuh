@@ -51,8 +51,9 @@ struct BxqSmem {
   static constexpr uint32_t in = turn + 4 * kTurn;
   static constexpr uint32_t bars = in + kIn * BXQ_BLOB_MAX;
   // barrier order: in_full, in_empty [kIn each]; op_full, op_empty [kOp each]; x_full [kX]; acc_full, acc_empty
-  // [2 each]; final; tile_full, tile_used [2 each] (the closing reduction)
-  static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1 + 4;
+  // [2 each]; final; tile_full, tile_used [kRing each] (the closing reduction)
+  static constexpr uint32_t kRing = (NB <= 64) ? 4 : 2;  // tiles in flight in the closing reduction (kWideTileRing)
+  static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1 + 2 * kRing;
   static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, verdict
   static constexpr uint32_t total = misc + 48;
   static constexpr uint32_t alloc = total + 1024;
@@ -61,6 +62,7 @@ struct BxqSmem {
   static_assert(MODE != kUmma || (kXLag < kX && kOp + kXLag + 1 > kX), "activation ring and lag do not fit the operand ring");
   static_assert(MODE != kUmma || 2 * NB * (NB <= 64 ? 2 : 1) <= int(kWideOperandCol), "accumulators overlap the operand columns");
   static_assert(8 * nbars + 64 <= 512, "barrier area");
+  static_assert(MODE != kUmma || (1 + kRing) * NB * 512u <= bars, "the closing reduction's tiles would overwrite the barriers");
   static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
 };
 
@@ -106,10 +108,13 @@ __device__ __forceinline__ void bxq_patch(uint32_t (&out)[16], uint32_t column, 
 
 // The closing reduction of a split row block, by the (kDecoderWarps + 4) x 32 threads that have nothing else left
 // to do: y[m, row] = bf16(sum of the row block's FP32 tiles in K order (+ bias)).  A reducing SM has to pull
-// (parts - 1) x NB x 512 bytes through its one L2 port, so the tiles come by bulk copy, two in flight, into the
-// shared memory the pipeline no longer needs (bytes [T, 3T) for T = NB x 512; the CTA's own last tile, if it takes
-// part, lies at [0, T) and was never in memory).  A thread owns the same few float4 positions of every tile and
+// (parts - 1) x NB x 512 bytes through its one L2 port, so the tiles come by bulk copy, kWideTileRing<NB> in flight,
+// into the shared memory the pipeline no longer needs (from byte T on, T = NB x 512; the CTA's own last tile, if it
+// takes part, lies at [0, T) and was never in memory).  A thread owns the same few float4 positions of every tile and
 // keeps their running sums in registers.  `fetched` counts the tiles brought in so far by this CTA (barrier phases).
+template <int NB>
+constexpr uint32_t kWideTileRing = NB <= 64 ? 4 : 2;  // (1 + ring) x NB x 512 bytes of shared memory
+
 template <int NB>
 __device__ __forceinline__ void bxq_reduce_row_block(const BxrArgs& args, const RoleCtx& ctx, uint32_t row_block, uint32_t first,
                                                      uint32_t parts, uint32_t own, uint32_t smem, uint32_t bar_full, uint32_t bar_used,
@@ -122,23 +127,24 @@ __device__ __forceinline__ void bxq_reduce_row_block(const BxrArgs& args, const 
   const uint32_t lane = t & 31;
   uint32_t asked = 0;  // remote tiles requested in this call
   bool live = true;
-  auto ask = [&](uint32_t j) {  // thread 0: the j-th remote tile into buffer (fetched + j) & 1, once its last readers are done
-    const uint32_t n = fetched + j, b = n & 1, p = j + ((own < parts && own <= j) ? 1u : 0u);
-    if (!ctx.wait(bar_used + 8 * b, ((n >> 1) & 1) ^ 1)) { live = false; return; }
+  constexpr uint32_t kRing = kWideTileRing<NB>;
+  auto ask = [&](uint32_t j) {  // thread 0: the j-th remote tile into buffer (fetched + j) % kRing, once its last readers are done
+    const uint32_t n = fetched + j, b = n % kRing, p = j + ((own < parts && own <= j) ? 1u : 0u);
+    if (!ctx.wait(bar_used + 8 * b, ((n / kRing) & 1) ^ 1)) { live = false; return; }
     mbar_arrive_expect_tx(bar_full + 8 * b, bytes);
     bulk_g2s(smem + kTile * (1 + b), args.partials + size_t(first + p) * NB * BXR_ROWS, bytes, bar_full + 8 * b, l2_policy_evict_first());
     asked = j + 1;
   };
   if (t == 0)
-    for (uint32_t j = 0; j < 2 && j < remote && live; ++j) ask(j);
+    for (uint32_t j = 0; j < kRing && j < remote && live; ++j) ask(j);
   float4 sum[kMine];
   uint32_t j = 0;  // remote tiles consumed
   for (uint32_t p = 0; p < parts && live; ++p) {
     uint32_t src = smem, b = 0;
     if (p != own) {
       const uint32_t n = fetched + j;
-      b = n & 1;
-      if (!ctx.wait(bar_full + 8 * b, (n >> 1) & 1)) { live = false; break; }
+      b = n % kRing;
+      if (!ctx.wait(bar_full + 8 * b, (n / kRing) & 1)) { live = false; break; }
       src = smem + kTile * (1 + b);
     }
 #pragma unroll
@@ -159,12 +165,12 @@ __device__ __forceinline__ void bxq_reduce_row_block(const BxrArgs& args, const 
     if (p != own) {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_used + 8 * b);
-      if (t == 0 && j + 2 < remote) ask(j + 2);
+      if (t == 0 && j + kRing < remote) ask(j + kRing);
       ++j;
     }
   }
   if (t == 0 && !live)  // unwinding: copies still in flight must land before the CTA may exit
-    for (uint32_t k = j; k < asked; ++k) mbar_wait(bar_full + 8 * ((fetched + k) & 1), ((fetched + k) >> 1) & 1);
+    for (uint32_t k = j; k < asked; ++k) mbar_wait(bar_full + 8 * ((fetched + k) % kRing), ((fetched + k) / kRing) & 1);
   fetched += remote;
   if (!live) return;
 #pragma unroll
@@ -212,7 +218,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   const uint32_t bar_op_full = bar_in_empty + 8 * L::kIn, bar_op_empty = bar_op_full + 8 * L::kOp;
   const uint32_t bar_x_full = bar_op_empty + 8 * L::kOp;
   const uint32_t bar_acc_full = bar_x_full + 8 * L::kX, bar_acc_empty = bar_acc_full + 16, bar_final = bar_acc_empty + 16;
-  const uint32_t bar_tile_full = bar_final + 8, bar_tile_used = bar_tile_full + 16;
+  const uint32_t bar_tile_full = bar_final + 8, bar_tile_used = bar_tile_full + 8 * L::kRing;
   constexpr uint32_t kTmemCols = kWideTmemCols;
   constexpr uint32_t kOpN = L::kOp ? L::kOp : 1;
   constexpr uint32_t kXN = L::kX ? L::kX : 1;
@@ -265,7 +271,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       else if (n >= 2u * L::kIn && n < 2u * L::kIn + L::kOp) count = kDecoderWarps + 1;  // op_full: + the loader's go-ahead
       else if (n >= 2u * L::kIn + 2 * L::kOp + L::kX) {
         const uint32_t j = n - (2u * L::kIn + 2 * L::kOp + L::kX);  // acc_full x2, acc_empty x2, final, tile_full x2, tile_used x2
-        count = j < 2 ? 2u : j < 5 ? 4u : j < 7 ? 1u : uint32_t(kDecoderWarps + 4);  // acc_full: both MMA issuers commit
+        count = j < 2 ? 2u : j < 5 ? 4u : j < 5 + L::kRing ? 1u : uint32_t(kDecoderWarps + 4);  // acc_full: both MMA issuers commit
       }
       mbar_init(ctx.bars + 8 * n, count);
     }
@@ -497,7 +503,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       const bool keep = item.parts > 1 && final_item;
       const uint32_t tile = smem;           // [batch row][128 weight rows] FP32, like a partial tile in memory
       uint32_t arrived = 0;
-      if (keep && e == 0 && lane == 0) arrived = ld_acquire_gpu(args.counters + item.row_block);  // answer used after the drain
+      if (keep && e == 0 && lane == 0) arrived = ld_relaxed_gpu(args.counters + item.row_block);  // answer used after the drain; fenced there
       // A lane holds one weight row and kStep batch columns; y and the partial tiles keep the rows of one batch
       // column together.  Stored from the registers that is one narrow store instruction per column, and the
       // store queue, not the memory, sets the pace (a 128-column drain took 4 400 to 10 000 cycles).  So the
