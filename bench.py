@@ -41,11 +41,13 @@ LINEARS = [("qkv", 7168, HIDDEN, "col", [5120, 1024, 1024]), ("o", HIDDEN, HIDDE
            ("gate_up", 2 * FFN, HIDDEN, "col", [FFN, FFN]), ("down", HIDDEN, FFN, "row", None)]
 BATCHES = (1, 64, 128)
 SEED = 1
-# dram__bytes_read+write over algorithmic bytes of one launch, from the ncu captures summarised under profiles/:
-# window layout, the step's top launch (gate|up at M = 128): 261.4 MB read + 14.2 MB written for 260.8 MB algorithmic
-# (profiles/bxw_kernel_gemm_m128_gate_up_34816x5120.md); rans layout: 122.2 + 3.4 MB for 122.0 MB
-# (profiles/bxr_kernel_gemm_m1_down_5120x17408.md).  The excess is the FP32 partial tiles of split row blocks.
-DRAM_TRAFFIC_RATIO = {"window4": 1.057, "window": 1.057, "rans": 1.03}
+# dram__bytes_read+write over algorithmic bytes of one launch, from the ncu captures summarised under profiles/, each
+# on the step's top launch (gate|up at M = 128) unless noted: window4 layout 270.1 MB read + 4.5 MB written for
+# 278.9 MB algorithmic (profiles/bxq_kernel_gemm_m128_gate_up_34816x5120.md; part of y is still in L2 when the launch
+# ends, the FP32 partial tiles of split row blocks stay in L2 or in shared memory); window layout 261.4 + 14.2 MB for
+# 260.8 MB (profiles/bxw_kernel_gemm_m128_gate_up_34816x5120.md); rans layout, down projection at M = 1: 122.2 + 3.4 MB
+# for 122.0 MB (profiles/bxr_kernel_gemm_m1_down_5120x17408.md).
+DRAM_TRAFFIC_RATIO = {"window4": 0.984, "window": 1.057, "rans": 1.03}
 FALLBACK_HBM_GBS = 6650.0
 
 
