@@ -127,10 +127,12 @@ int grb_bctx_decode_words(const grb_bctx_tensor* tensor, const int64_t* block_id
 
 /* Host: re-codes decoded BF16 words into a resident image for `workers` persistent CTAs (the SM count of the
  * target GPU).  Stands where the reference transcodes a frame into its runtime formats at load
- * (gs/bctx_v21_transcode.py:59-560; gs/tbe_desc.py:42-51).  layout: 0 = entropy-coded exponent streams (rANS),
- * 2 = fixed 3-bit exponent codes in an 8-binade row window with an exception list (the role of the reference's TBE
- * container, gl/tbe_container.py:259-404; cheaper to decode, 1-3 % larger), 1 = plain tiles.  An image whose chunks
- * do not fit is demoted 2 -> 0 -> 1; the header's `mode` says what was built.
+ * (gs/bctx_v21_transcode.py:59-560; gs/tbe_desc.py:42-51).  layout: 3 = fixed 4-bit exponent codes in a 16-binade
+ * row window with a (nearly empty) exception list and chunk blobs of one size (the role of the reference's TBE
+ * container, gl/tbe_container.py:259-404; 1.506 bytes per weight, the fastest kernel), 2 = 3-bit codes in an 8-binade
+ * window (1.406 bytes per weight), 0 = entropy-coded exponent streams (rANS; 1.365-1.39 bytes per weight, the slowest
+ * kernel), 1 = plain tiles.  An image whose chunks do not fit is demoted 3 or 2 -> 0 -> 1; the header's `mode` says
+ * what was built.
  * source_sha256 (optional, 32 bytes) is copied into the header.  *image is malloc'ed: release with bxr_free.
  * 0 ok, 1 arguments, 2 out of memory, 3 other. */
 int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t workers, uint32_t host_threads,
