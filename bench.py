@@ -199,6 +199,49 @@ class Layer:
         self.y_host = {m: torch.empty(m, HIDDEN, dtype=torch.bfloat16).pin_memory() for m in BATCHES}
         self.xv = {(m, e["name"]): self.x[(m, e["k"])][:, e["k0"]:e["k1"]] for m in BATCHES for e in self.entries}
         self.launches_per_step = len(LINEARS) * len(BATCHES)
+        # More than one rank: the partial outputs of the column-split linears (O, down) are summed over peer memory by
+        # the library's own kernel, which - unlike a NCCL collective on this pool - can be captured in a CUDA graph.
+        # The linear writes its partial into the reducer's slot (e["y"]), the sum lands in e["sum"].  NCCL is the
+        # fallback if the buffers cannot be mapped on every rank.
+        self.peer, self.reduce_kind = None, "none"
+        if world > 1:
+            self.peer, self.reduce_kind = self._peer_reducer(), "nccl"
+            if self.peer is not None:
+                self.reduce_kind = "peer"
+                for e in self.entries:
+                    if e["kind"] == "row":
+                        e["sum"] = {m: torch.empty(m, e["res"].N, device=device, dtype=torch.bfloat16) for m in BATCHES}
+                        e["y"] = {m: self.peer.slot(f'{e["name"]}:{m}', m, e["res"].N) for m in BATCHES}
+                self.launches_per_step += sum(len(BATCHES) for e in self.entries if e["kind"] == "row")
+
+    def _peer_reducer(self):
+        import torch
+        import torch.distributed as dist
+
+        from georefine_b200.peer import PeerReducer
+
+        slots = {f'{e["name"]}:{m}': (m * e["res"].N + 7) // 8 * 8 for e in self.entries if e["kind"] == "row" for m in BATCHES}
+        peer, ok = None, 1
+        try:
+            peer = PeerReducer(slots, device=self.device)
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] rank {self.rank}: peer-memory all-reduce unavailable ({type(exc).__name__}: {exc}); using NCCL", file=sys.stderr)
+            ok = 0
+        flag = torch.tensor([ok], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return peer if int(flag.item()) else None
+
+    def result(self, e, m):
+        """Where the finished output of a linear is."""
+        return e["sum"][m] if (self.peer is not None and e["kind"] == "row") else e["y"][m]
+
+    def all_reduce(self, e, m):
+        import torch.distributed as dist
+
+        if self.peer is not None:
+            self.peer.reduce(f'{e["name"]}:{m}', e["sum"][m])
+        else:
+            dist.all_reduce(e["y"][m])
 
     def dense_bytes_per_step(self):
         return sum(2 * n * k for _, n, k, _, _ in LINEARS) * len(BATCHES)
@@ -213,8 +256,8 @@ class Layer:
         y = e["y"][m]
         e["res"].gemm(x[:, e["k0"]:e["k1"]], y)
         if e["kind"] == "row" and self.world > 1:
-            dist.all_reduce(y)
-        return y
+            self.all_reduce(e, m)
+        return self.result(e, m)
 
     def step(self):
         for m in BATCHES:
@@ -266,18 +309,18 @@ class Layer:
             for k in (HIDDEN, FFN):
                 self.x[(m, k)].copy_(self.x_host[(m, k)], non_blocking=True)
             for e in self.entries:
-                y = e["y"][m]
-                e["res"](self.xv[(m, e["name"])], y)
+                e["res"](self.xv[(m, e["name"])], e["y"][m])
                 if e["kind"] == "row" and self.world > 1:
-                    dist.all_reduce(y)
-            self.y_host[m].copy_(y, non_blocking=True)   # the down projection's output
+                    self.all_reduce(e, m)
+            self.y_host[m].copy_(self.result(self.entries[-1], m), non_blocking=True)   # the down projection's output
         torch.cuda.current_stream().synchronize()
 
     def e2e_graph(self):
         """The end-to-end step as one CUDA graph, the way the reference's serving engines replay a whole decode step
         (glc_serve/fastdec.py capture/replay): the pinned-host -> device copies of every batch run on a side stream and
         overlap the launches of the batches before them, the descriptor calls follow on the main stream, and each
-        batch's result goes back to the host on the side stream while the next batch runs.  Single rank only (no collective is ever captured).  Returns a callable that
+        batch's result goes back to the host on the side stream while the next batch runs.  With more than one rank only
+        when the sums go over peer memory (no NCCL collective is ever captured).  Returns a callable that
         replays the graph and waits until the results are in host memory."""
         import torch
 
@@ -296,11 +339,13 @@ class Layer:
                 main.wait_event(ready[m])
                 for e in self.entries:
                     e["res"](self.xv[(m, e["name"])], e["y"][m])
+                    if e["kind"] == "row" and self.peer is not None:
+                        self.all_reduce(e, m)
                 done = torch.cuda.Event()
                 done.record(main)
                 with torch.cuda.stream(side):   # the down projection's output goes back while the next batch runs
                     side.wait_event(done)
-                    self.y_host[m].copy_(self.entries[-1]["y"][m], non_blocking=True)
+                    self.y_host[m].copy_(self.result(self.entries[-1], m), non_blocking=True)
             main.wait_stream(side)
 
         def step():
@@ -310,7 +355,7 @@ class Layer:
         return step
 
     def status(self):
-        return sum(e["res"].check_status() for e in self.entries)
+        return sum(e["res"].check_status() for e in self.entries) + (self.peer.check_status() if self.peer is not None else 0)
 
 
 def timed(fn, steps, warmup, world):
@@ -402,7 +447,8 @@ def run_ours(args):
     # With more than one rank the step contains NCCL all-reduces; capturing those in a graph hung on this pool
     # (twice, at two ranks), so multi-rank runs replay graphs of the fused launches only and issue the
     # collectives eagerly between them (segmented_step).
-    if not args.no_graph and world == 1:
+    whole_graph = world == 1 or layer.peer is not None   # nothing of NCCL inside the step
+    if not args.no_graph and whole_graph:
         try:
             for _ in range(2):
                 layer.step()
@@ -410,10 +456,15 @@ def run_ours(args):
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 layer.step()
-            step_fn, launch = graph.replay, "cuda_graph"
+            step_fn, launch = graph.replay, "cuda_graph" + (" (peer-memory all-reduce inside)" if world > 1 else "")
         except Exception as exc:  # noqa: BLE001
             launch = f"eager (graph capture failed: {type(exc).__name__})"
-    if not args.no_graph and world > 1:
+        if world > 1:   # every rank must replay the same thing: one failed capture sends all of them to eager launches
+            agreed = torch.tensor([1 if step_fn is not layer.step else 0], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if not int(agreed.item()):
+                step_fn, launch = layer.step, "eager (graph capture failed on some rank)"
+    if not args.no_graph and world > 1 and not whole_graph:
         for _ in range(2):
             layer.step()
         torch.cuda.synchronize()
@@ -423,12 +474,17 @@ def run_ours(args):
     with ClockSampler(local) as clocks:
         ms = timed(step_fn, args.steps, args.warmup, world)
     e2e_fn, e2e_launch = layer.step_e2e, "eager"
-    if not args.no_graph and world == 1:
+    if not args.no_graph and whole_graph:
         try:
             layer.step_e2e()
             e2e_fn, e2e_launch = layer.e2e_graph(), "cuda_graph, copies on a side stream"
         except Exception as exc:  # noqa: BLE001
             e2e_launch = f"eager (graph capture failed: {type(exc).__name__})"
+        if world > 1:
+            agreed = torch.tensor([1 if e2e_fn is not layer.step_e2e else 0], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if not int(agreed.item()):
+                e2e_fn, e2e_launch = layer.step_e2e, "eager (graph capture failed on some rank)"
     ms_e2e = timed(e2e_fn, args.steps, args.warmup, world)
     y_check = [layer.y_host[m].clone() for m in BATCHES]
     layer.step_e2e()                                     # the eager public-API path must land the same outputs
@@ -460,7 +516,7 @@ def run_ours(args):
         "config": {"workload": "hybrid-decoder linears hidden=5120 (QKV 7168x5120, O 5120x5120, gate|up 34816x5120, down 5120x17408), "
                                "seed 1, fused decode-GEMM at M=1,64,128", "parallelism": f"tp{world}",
                    "l2": "coded working set ~440 MB exceeds the 126 MB L2; no flush between iterations",
-                   "resident_format": "BXR1/" + args.layout, "launch": launch, "status_word": status},
+                   "resident_format": "BXR1/" + args.layout, "launch": launch, "all_reduce": layer.reduce_kind, "status_word": status},
         "e2e": {"value": round(dense / (ms_e2e * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms_e2e, 4),
                 "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES),
                 "launch": e2e_launch, "outputs_match_eager_path": e2e_same},

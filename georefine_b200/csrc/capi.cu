@@ -3,6 +3,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cstring>
 #include <mutex>
 
 #include "../../include/georefine_b200.h"
@@ -10,6 +12,7 @@
 #include "bxr_kernels.cuh"
 #include "bxw_kernels.cuh"
 #include "bxq_kernels.cuh"
+#include "peer_reduce.cuh"
 
 namespace {
 
@@ -409,6 +412,89 @@ int grb_kernel_attributes(int which, int out[5]) {
   out[3] = fa.maxDynamicSharedSizeBytes;
   out[4] = fa.maxThreadsPerBlock;
   return GRB_OK;
+}
+
+uint64_t grb_peer_control_bytes(void) { return uint64_t(kPeerControlWords) * 4; }
+
+// A buffer other processes of the node can map: its own cudaMalloc allocation (an IPC handle names a whole
+// allocation), zeroed; `handle` receives the 64 bytes a peer passes to grb_peer_open.
+int grb_peer_alloc(uint64_t bytes, void** ptr, uint8_t handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  if (!ptr || !handle || bytes == 0) return GRB_ERR_ARGUMENT;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cuda_status(e);
+  e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_status(e);
+  }
+  memcpy(handle, &h, 64);
+  *ptr = p;
+  return GRB_OK;
+}
+int grb_peer_free(void* ptr) { return cuda_status(cudaFree(ptr)); }
+// Maps a peer's buffer into this process for the CURRENT device (peer access is enabled by the runtime as needed).
+int grb_peer_open(const uint8_t handle[64], void** ptr) {
+  if (!ptr || !handle) return GRB_ERR_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  return cuda_status(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+int grb_peer_close(void* ptr) { return cuda_status(cudaIpcCloseMemHandle(ptr)); }
+
+int grb_peer_enable(int peer_device) {
+  int current = 0;
+  cudaError_t e = cudaGetDevice(&current);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (peer_device == current) return GRB_OK;
+  int can = 0;
+  e = cudaDeviceCanAccessPeer(&can, current, peer_device);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (!can) return GRB_ERR_UNSUPPORTED;
+  e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    return GRB_OK;
+  }
+  return e == cudaSuccess ? GRB_OK : cuda_status(e);
+}
+
+int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* const* controls, uint64_t block_bytes, uint32_t rank,
+                            uint32_t world, void* out, uint64_t elems, uint32_t* status, void* cuda_stream) {
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (!partial || !receives || !controls || !out || !status || world < 1 || world > uint32_t(kPeerMaxRanks) || rank >= world) return GRB_ERR_ARGUMENT;
+  if (elems == 0 || (elems & 7u) || elems > 0xFFFFFFF8ull || block_bytes < 2 * elems || (block_bytes & 15u)) return GRB_ERR_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) || (reinterpret_cast<uintptr_t>(partial) & 15u) || out == partial) return GRB_ERR_ARGUMENT;
+  PeerArgs a{};
+  for (uint32_t r = 0; r < world; ++r) {
+    if (!receives[r] || !controls[r] || (reinterpret_cast<uintptr_t>(receives[r]) & 15u) || (reinterpret_cast<uintptr_t>(controls[r]) & 127u))
+      return GRB_ERR_ARGUMENT;
+    a.receive[r] = static_cast<uint8_t*>(receives[r]);
+    a.control[r] = static_cast<uint32_t*>(controls[r]);
+  }
+  a.partial = static_cast<const __nv_bfloat16*>(partial);
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.block_bytes = block_bytes;
+  a.elems = uint32_t(elems);
+  a.rank = rank;
+  a.world = world;
+  a.status = status;
+  const uint64_t vectors = elems >> 3;
+  const uint32_t ctas = uint32_t(std::min<uint64_t>(kPeerMaxCtas, (vectors + kPeerThreads - 1) / kPeerThreads));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(kPeerThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, peer_allreduce_kernel, a));
 }
 
 }  // extern "C"

@@ -9,7 +9,8 @@ The reference has no multi-GPU execution of a linear (its only multi-device code
 * Row parallel (O, down): rank r owns the weight columns [k0, k1), k0 and k1 multiples of 128 (one chunk of the
   resident layout), multiplies x[:, k0:k1] and the partial outputs are summed across ranks: NCCL all-reduce of
   the BF16 partials, or, with ``reduce="ordered"``, an all-gather followed by a sum in rank order, which
-  gives the same bits whatever the message size.
+  gives the same bits whatever the message size, or, with ``reduce="peer"``, the library's own kernel over peer
+  memory (``peer.PeerReducer``: rank-ordered FP32 sum, the same bits on every rank, capturable in a CUDA graph).
 
 ``local_factory(words) -> callable(x2d) -> y2d`` builds the per-rank linear; the default builds a
 ``ResidentWeight`` on the current CUDA device.  Tests inject a CPU stand-in to exercise the sharding and the
@@ -88,10 +89,13 @@ class ColumnParallelLinear:
 class RowParallelLinear:
     """y = sum over ranks of x[:, k0:k1] @ W[:, k0:k1].T."""
 
-    def __init__(self, words, rank: int, world: int, *, local_factory=None, reduce="nccl", group=None):
+    def __init__(self, words, rank: int, world: int, *, local_factory=None, reduce="nccl", group=None, peer=None, slot=None):
         words = np.asarray(words)
-        if reduce not in ("nccl", "ordered"):
-            raise ValueError("reduce must be 'nccl' or 'ordered'")
+        if reduce not in ("nccl", "ordered", "peer"):
+            raise ValueError("reduce must be 'nccl', 'ordered' or 'peer'")
+        if reduce == "peer" and (peer is None or slot is None):
+            raise ValueError("reduce='peer' needs a PeerReducer and the name of one of its slots")
+        self.peer, self.slot = peer, slot
         self.k0, self.k1 = row_range(words.shape[1], rank, world, CHUNK)
         if self.k1 <= self.k0:
             raise ValueError("more ranks than 128-column chunks")
@@ -108,6 +112,10 @@ class RowParallelLinear:
         if self.reduce == "nccl":
             dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
             return part
+        if self.reduce == "peer":
+            flat = part.reshape(-1, part.shape[-1])
+            self.peer.slot(self.slot, flat.shape[0], flat.shape[1]).copy_(flat)
+            return self.peer.reduce(self.slot, torch.empty_like(flat)).view(part.shape)
         parts = [torch.empty_like(part) for _ in range(self.world)]
         dist.all_gather(parts, part.contiguous(), group=self.group)
         total = parts[0].float()

@@ -199,6 +199,43 @@ int grb_bxr_gemv_static(const void* device_image, const bxr_header* header, cons
  * max dynamic smem, max threads}. */
 int grb_kernel_attributes(int which, int out[5]);
 
+/* ---------------------------------------------------------------------------------------------------
+ * 4. Row-parallel linears across the GPUs of one node: the sum of the per-GPU partial outputs.
+ * ------------------------------------------------------------------------------------------------- */
+
+/* The reference runs a linear on one device (its multi-device code places whole layers,
+ * glc_loader/tbe_device_map.py:46-56); a tensor-parallel deployment of the fused linears needs the partial outputs
+ * of the column-split weights (O and down projections) added across GPUs.  grb_peer_allreduce_bf16 does that over
+ * peer memory, one launch per rank, the same call on every rank in the same order:
+ *   partial      this rank's partial output (elems BF16, 16-byte aligned), written by the preceding kernel of `stream`;
+ *   receives[r]  rank r's receive area for this reduction as mapped into this process (CUDA IPC or any other peer
+ *                mapping; receives[rank] is the local one): 2 * world blocks of block_bytes (>= 2 * elems, a multiple
+ *                of 16), indexed [call parity][source rank]; never touched by the host;
+ *   controls[r]  rank r's control block (grb_peer_control_bytes() bytes, 128-byte aligned, zeroed once before the
+ *                first call, never touched by the host afterwards), mapped likewise; one block per rank serves all
+ *                reductions of that rank, which must then be issued one after another on one stream;
+ *   out          local result: BF16(sum over r in rank order of rank r's partial), FP32 accumulation, the same bits on
+ *                every rank; may not alias the partial.
+ * Every rank copies its partial into the peers' receive areas (posted stores over NVLink), announces it with a flag,
+ * waits for the peers' flags and adds.  The partial may be overwritten as soon as the launch has completed locally.
+ * The call allocates nothing and does not synchronise with the host; it can be captured in a CUDA graph (the call
+ * counter lives in the control block).  A peer that never makes the matching call shows as GRB_STATUS_TIMEOUT in
+ * *status after two seconds: nothing spins without a limit.  world <= 8, elems % 8 == 0.
+ * grb_peer_enable(device) enables access from the current device to a peer's memory (GRB_ERR_UNSUPPORTED if the
+ * two are not connected). */
+uint64_t grb_peer_control_bytes(void);
+int grb_peer_enable(int peer_device);
+/* Buffers the ranks of a node can map from one another (CUDA IPC).  grb_peer_alloc: a zeroed device allocation of
+ * its own on the current device and the 64-byte handle that names it; grb_peer_open: maps the allocation behind a
+ * handle received from another process for the current device; grb_peer_close / grb_peer_free undo them.  Set-up
+ * calls: they allocate and synchronise. */
+int grb_peer_alloc(uint64_t bytes, void** ptr, uint8_t handle[64]);
+int grb_peer_free(void* ptr);
+int grb_peer_open(const uint8_t handle[64], void** ptr);
+int grb_peer_close(void* ptr);
+int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* const* controls, uint64_t block_bytes, uint32_t rank,
+                            uint32_t world, void* out, uint64_t elems, uint32_t* status, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
