@@ -484,7 +484,8 @@ int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* co
   a.world = world;
   a.status = status;
   const uint64_t vectors = elems >> 3;
-  const uint32_t ctas = uint32_t(std::min<uint64_t>(kPeerMaxCtas, (vectors + kPeerThreads - 1) / kPeerThreads));
+  // a small message stays in one CTA (no wait for other CTAs' pushes); a large one spreads over up to kPeerMaxCtas
+  const uint32_t ctas = vectors <= 8 * kPeerThreads ? 1u : uint32_t(std::min<uint64_t>(kPeerMaxCtas, (vectors + 2 * kPeerThreads - 1) / (2 * kPeerThreads)));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(ctas);
   cfg.blockDim = dim3(kPeerThreads);

@@ -82,10 +82,13 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(const Peer
     for (uint32_t r = 0; r < kPeerMaxRanks; ++r)
       if (r < a.world && r != a.rank) reinterpret_cast<uint4*>(a.receive[r] + (parity * a.world + a.rank) * a.block_bytes)[v] = x;
   }
-  __threadfence_system();
   __syncthreads();
-  // 2. announce, by the CTA that completes the rank's push
-  if (threadIdx.x == 0) last = atomicAdd(mine + kPeerPushedAt, 1u) == gridDim.x - 1 ? 1u : 0u;
+  // 2. announce, by the CTA that completes the rank's push (one system-scope fence per CTA: it follows the CTA's
+  //    barrier, so it covers every thread's stores)
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    last = atomicAdd(mine + kPeerPushedAt, 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
   __syncthreads();
   if (last && threadIdx.x < a.world && threadIdx.x != a.rank) peer_post(a.control[threadIdx.x] + kPeerReadyAt + a.rank * kPeerFlagStride, call);
   // 3. wait for everybody's data, add
