@@ -53,36 +53,57 @@ class PeerReducer:
             block = (2 * int(elems) + 255) // 256 * 256
             self.offsets[name] = (at, int(elems), at + block, block)
             at += block * (1 + 2 * self.world)
-        # one device allocation of its own, zeroed (flags and call counter start at 0), mapped by every peer
-        self.bytes = at
+        # One device allocation of its own, zeroed (flags and call counter start at 0), mapped by every peer.  A
+        # failure on one rank must not leave the others waiting in a collective: every rank goes through the same
+        # collectives whatever happens locally, and all of them raise if any of them failed.
+        self.bytes, self.local_ptr, self.buffer, self.pointers, self.opened = at, None, None, [], []
+        error = None
         handle = (ctypes.c_uint8 * 64)()
         local = ctypes.c_void_p()
         with torch.cuda.device(self.device):
             rc = self.lib.grb_peer_alloc(at, ctypes.byref(local), handle)
         if rc != 0:
-            raise PeerError(f"grb_peer_alloc failed with code {rc}")
-        self.local_ptr = int(local.value)
-        self.buffer = torch.as_tensor(_RawDeviceBytes(self.local_ptr, at), device=self.device)   # a view, no copy
+            error = f"grb_peer_alloc failed with code {rc}"
+        else:
+            self.local_ptr = int(local.value)
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, (int(self.device.index), bytes(handle), at), group=group)
-        self.pointers, self.opened = [], []
-        for r, (peer_device, peer_handle, peer_bytes) in enumerate(gathered):
-            if peer_bytes != at:
-                raise PeerError("ranks disagree on the buffer size")
-            if r == self.rank:
-                self.pointers.append(self.local_ptr)
-                continue
-            mapped = ctypes.c_void_p()
-            with torch.cuda.device(self.device):
-                rc = self.lib.grb_peer_open((ctypes.c_uint8 * 64).from_buffer_copy(peer_handle), ctypes.byref(mapped))
-            if rc != 0:
-                raise PeerError(f"cannot map the buffer of rank {r} (device {peer_device}) from device {self.device.index}: code {rc}")
-            self.pointers.append(int(mapped.value))
-            self.opened.append(int(mapped.value))
+        dist.all_gather_object(gathered, (int(self.device.index), bytes(handle) if error is None else None, at), group=group)
+        if error is None:
+            for r, (peer_device, peer_handle, peer_bytes) in enumerate(gathered):
+                if peer_handle is None or peer_bytes != at:
+                    error = f"rank {r} has no buffer to map or one of another size"
+                    break
+                if r == self.rank:
+                    self.pointers.append(self.local_ptr)
+                    continue
+                mapped = ctypes.c_void_p()
+                with torch.cuda.device(self.device):
+                    rc = self.lib.grb_peer_open((ctypes.c_uint8 * 64).from_buffer_copy(peer_handle), ctypes.byref(mapped))
+                if rc != 0:
+                    error = f"cannot map the buffer of rank {r} (device {peer_device}) from device {self.device.index}: code {rc}"
+                    break
+                self.pointers.append(int(mapped.value))
+                self.opened.append(int(mapped.value))
+        agreed = torch.tensor([0 if error else 1], device=self.device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)   # also: nobody launches before everybody has mapped everything
+        if not int(agreed.item()):
+            self._release()
+            raise PeerError(error or "another rank could not set up its peer buffers")
+        self.buffer = torch.as_tensor(_RawDeviceBytes(self.local_ptr, at), device=self.device)   # a view, no copy
         self.controls = (ctypes.c_void_p * self.world)(*self.pointers)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
-        torch.cuda.synchronize(self.device)
-        dist.barrier(group=group)   # nobody launches before everybody has mapped everything
+
+    def _release(self):
+        import torch
+
+        with torch.cuda.device(self.device):
+            for p in self.opened:
+                self.lib.grb_peer_close(p)
+            self.opened = []
+            self.buffer = None
+            if self.local_ptr is not None:
+                self.lib.grb_peer_free(self.local_ptr)
+            self.local_ptr = None
 
     def close(self):
         """Unmaps the peers' buffers and frees the local one.  Collective: every rank calls it, none launches afterwards."""
@@ -92,15 +113,13 @@ class PeerReducer:
         if self.local_ptr is None:
             return
         torch.cuda.synchronize(self.device)
-        dist.barrier(group=self.group)
+        dist.barrier(group=self.group)   # nobody unmaps or frees what somebody may still be writing to
         with torch.cuda.device(self.device):
             for p in self.opened:
                 self.lib.grb_peer_close(p)
             self.opened = []
-            dist.barrier(group=self.group)   # nobody frees what somebody still has mapped
-            self.buffer = None
-            self.lib.grb_peer_free(self.local_ptr)
-        self.local_ptr = None
+        dist.barrier(group=self.group)   # nobody frees what somebody still has mapped
+        self._release()
 
     def slot(self, name: str, rows: int, cols: int):
         """The local slot as a BF16 [rows, cols] tensor: the linear's output buffer."""
