@@ -155,3 +155,34 @@ def test_window_full_size_images_reproduce_their_source_digest(orc, dev, shape, 
     r.gemm(x, y)
     ref = _reference_product(words, x)
     assert r.check_status() == 0 and ((y.float() - ref).abs().max() / ref.abs().max()).item() <= REL_TOL
+
+
+def _uneven_exceptions(orc):
+    """A 256 x 512 weight whose first chunk has ~150 weights outside every row window and whose other chunks have
+    none: the blobs of its wide-window image differ by more than the builder pads away."""
+    words = orc.synthetic_weight_words(256, 512, 11)
+    rng = np.random.default_rng(11)
+    rows, cols = rng.integers(0, 128, 150), rng.integers(0, 128, 150)
+    words[rows, cols] = 0x0100 | (words[rows, cols] & 0x807F)   # exponent 2: some 120 binades below the row's window
+    return words
+
+
+def test_wide_window_images_with_blobs_of_different_sizes(orc, dev):
+    """Blobs are padded to one size only when they differ little; otherwise the kernel's loader follows the offset
+    table.  Both paths must decode bit-exactly and multiply alike."""
+    from georefine_b200.resident import ResidentWeight
+
+    words = _uneven_exceptions(orc)
+    uneven = ResidentWeight.from_words(words, dev, max_m=64, workers=7, layout="window4")
+    even = ResidentWeight.from_words(orc.synthetic_weight_words(256, 512, 11), dev, max_m=64, workers=7, layout="window4")
+    assert uneven.header.mode == 3 and uneven.header.blob_stride16 == 0
+    assert even.header.mode == 3 and even.header.blob_stride16 * 16 >= 24640
+    assert np.array_equal(_u16(uneven.decode()), words)
+    g = torch.Generator().manual_seed(5)
+    x64 = (torch.randn(64, 512, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    y64 = uneven.linear(x64)
+    ref = _reference_product(words, x64)
+    assert float((y64.float() - ref).abs().max()) <= REL_TOL * float(ref.abs().max())
+    y1 = uneven.linear(x64[:1])
+    assert torch.equal(y1.view(torch.int16), y64[:1].view(torch.int16))   # rows do not depend on the batch size
+    assert uneven.check_status() == 0

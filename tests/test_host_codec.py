@@ -237,3 +237,22 @@ def test_window_image_entries_far_list_and_fallbacks(orc):
         resident.decode_image_host(bad)
     image, h = resident.build_image(noisy, 148, layout="window4")
     assert h.mode in (0, 1) and np.array_equal(resident.decode_image_host(image), noisy)
+
+
+def test_wide_window_blobs_share_one_size_unless_they_differ_much(orc):
+    """The builder pads the blobs of a wide-window image to one size (header blob_stride16) so that a kernel can
+    address blob b as b x size; an image whose blobs differ by more than 512 bytes keeps its offset table only."""
+    import numpy as np
+
+    from georefine_b200 import resident
+
+    words = orc.synthetic_weight_words(256, 512, 11)
+    image, header = resident.build_image(words, 7, layout="window4")
+    assert header.mode == 3 and header.blob_stride16 * 16 >= 24640
+    assert np.array_equal(resident.decode_image_host(image), words)
+    rng = np.random.default_rng(11)
+    rows, cols = rng.integers(0, 128, 150), rng.integers(0, 128, 150)
+    words[rows, cols] = 0x0100 | (words[rows, cols] & 0x807F)   # ~150 weights far below their row windows, all in one chunk
+    image, header = resident.build_image(words, 7, layout="window4")
+    assert header.mode == 3 and header.blob_stride16 == 0
+    assert np.array_equal(resident.decode_image_host(image), words)
