@@ -200,7 +200,9 @@ class CachedLinear:
         import torch
 
         self.device = torch.device(device)
-        workers = resident.sm_count(self.device) if workers is None else workers
+        if workers is None:
+            _, (rows, cols) = frame_identity(frame)
+            workers = resident.default_workers(rows, cols, resident.sm_count(self.device))
         image, header, self.cache_hit = image_for_frame(frame, workers, layout=layout, cache=cache)
         self.resident = resident.ResidentWeight(image, self.device, max_m=max_m, verify=False)
         self.shape = (int(header.rows), int(header.cols))

@@ -26,6 +26,23 @@ def sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
+def default_workers(rows: int, cols: int, sms: int) -> int:
+    """How many persistent CTAs an image is built for when the caller does not say: one per SM, except for small
+    weights with fewer 128-row blocks than SMs, where a multiple of the row-block count is better when it costs few
+    extra chunks per CTA: every row block is then cut into the same few whole CTAs (no CTA holds the tail of one row
+    block and the head of the next), which shortens the partial-tile exchange at the end of a launch (measured on a
+    B200: 5120 x 5120 with 120 instead of 148 CTAs 15.1 vs 16.7 us at M = 64, 17.9 vs 19.9 us at M = 128, level at M = 1;
+    5120 x 17408 with 120 CTAs is slower, 30.3 vs 28.0 us: there the streaming dominates)."""
+    row_blocks, chunks = -(-rows // 128), -(-cols // 128)
+    if row_blocks >= sms or row_blocks == 0:
+        return sms
+    per_cta = row_blocks * chunks / sms
+    aligned = row_blocks * (sms // row_blocks)
+    if per_cta <= 16 and row_blocks * chunks / aligned - per_cta <= 5:
+        return aligned
+    return sms
+
+
 def build_image(words, workers: int, *, threads: int = 0, layout: str = DEFAULT_LAYOUT, force_raw: bool = False,
                 source_sha256: bytes | None = None):
     """Host: BF16 words [rows, cols] -> (image bytes as uint8 array, header).
@@ -93,7 +110,7 @@ class ResidentWeight:
     @classmethod
     def from_words(cls, words, device, *, source_sha256=None, max_m=128, workers=None, layout=DEFAULT_LAYOUT, force_raw=False,
                    verify=True):
-        workers = sm_count(device) if workers is None else workers
+        workers = default_workers(int(words.shape[0]), int(words.shape[1]), sm_count(device)) if workers is None else workers
         image, _ = build_image(words, workers, layout=layout, force_raw=force_raw, source_sha256=source_sha256)
         return cls(image, device, max_m=max_m, verify=verify)
 
