@@ -231,6 +231,23 @@ class Layer:
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         return peer if int(flag.item()) else None
 
+    def peer_is_healthy(self):
+        """After the first eager steps: did every rank's peer reductions complete?  A wait that ran out (a peer that is
+        not there, a mapping that does not work) must not be paid two seconds at a time for the rest of the run: all
+        ranks fall back to NCCL together.  The slots stay where they are (the linears keep writing into them)."""
+        import torch
+        import torch.distributed as dist
+
+        if self.peer is None:
+            return True
+        bad = torch.tensor([1 if self.peer.check_status() else 0], device=self.device)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()):
+            self._retired_peer, self.peer, self.reduce_kind = self.peer, None, "nccl (the peer reduction reported a timeout)"
+            self.launches_per_step = len(LINEARS) * len(BATCHES)
+            return False
+        return True
+
     def result(self, e, m):
         """Where the finished output of a linear is."""
         return e["sum"][m] if (self.peer is not None and e["kind"] == "row") else e["y"][m]
@@ -447,6 +464,11 @@ def run_ours(args):
     # With more than one rank the step contains NCCL all-reduces; capturing those in a graph hung on this pool
     # (twice, at two ranks), so multi-rank runs replay graphs of the fused launches only and issue the
     # collectives eagerly between them (segmented_step).
+    if world > 1 and layer.peer is not None:
+        for _ in range(2):
+            layer.step()
+        torch.cuda.synchronize()
+        layer.peer_is_healthy()
     whole_graph = world == 1 or layer.peer is not None   # nothing of NCCL inside the step
     if not args.no_graph and whole_graph:
         try:
