@@ -53,103 +53,52 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
   return a;
 }
 
-// Opt every instantiation into its dynamic shared memory once per process and device.
-template <int MODE, int NB>
-cudaError_t prepare() {
+// One launcher for the three fused kernels (bxr_, bxw_, bxq_kernel): opts the instantiation into its dynamic shared
+// memory once per process and device, then launches one persistent CTA per worker.
+// Programmatic stream serialisation: the kernel may begin (table and blob loads, decoding) while the tail of the
+// previous kernel in the stream is still running; it waits in-kernel before touching x, y or the scratch.
+template <auto Kernel, uint32_t kSmemBytes, int kThreads>
+int launch_fused(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
   static std::mutex mu;
   static bool done[64] = {false};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  std::lock_guard<std::mutex> lock(mu);
-  if (dev < 64 && done[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(bxr_kernel<MODE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BxrSmem<MODE, NB>::alloc));
-  if (e == cudaSuccess && dev < 64) done[dev] = true;
-  return e;
-}
-
-template <int MODE, int NB>
-int launch(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
-  cudaError_t e = prepare<MODE, NB>();
   if (e != cudaSuccess) return cuda_status(e);
-  const int threads = MODE == kUmma ? kThreadsUmma : kThreadsSimt;
-  // Programmatic stream serialisation: this kernel may begin (table and blob loads, decoding) while the tail of
-  // the previous kernel in the stream is still running; it waits in-kernel before touching x, y or the scratch.
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+      e = cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes));
+      if (e != cudaSuccess) return cuda_status(e);
+      if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(a.workers);
-  cfg.blockDim = dim3(threads);
-  cfg.dynamicSmemBytes = BxrSmem<MODE, NB>::alloc;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, bxr_kernel<MODE, NB>, a, tmap));
+  return cuda_status(cudaLaunchKernelEx(&cfg, Kernel, a, tmap));
 }
 
-// Window-mode images run bxw_kernel: same arguments, its own shared-memory plan.
-template <int MODE, int NB>
-cudaError_t prepare_window() {
-  static std::mutex mu;
-  static bool done[64] = {false};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  std::lock_guard<std::mutex> lock(mu);
-  if (dev < 64 && done[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(bxw_kernel<MODE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BxwSmem<MODE, NB>::alloc));
-  if (e == cudaSuccess && dev < 64) done[dev] = true;
-  return e;
-}
+template <int MODE>
+constexpr int kFusedThreads = MODE == kUmma ? kThreadsUmma : kThreadsSimt;
 
 template <int MODE, int NB>
-int launch_window(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
-  cudaError_t e = prepare_window<MODE, NB>();
-  if (e != cudaSuccess) return cuda_status(e);
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(a.workers);
-  cfg.blockDim = dim3(MODE == kUmma ? kThreadsUmma : kThreadsSimt);
-  cfg.dynamicSmemBytes = BxwSmem<MODE, NB>::alloc;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, bxw_kernel<MODE, NB>, a, tmap));
+int launch(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {  // entropy-coded and raw images
+  return launch_fused<bxr_kernel<MODE, NB>, BxrSmem<MODE, NB>::alloc, kFusedThreads<MODE>>(a, tmap, stream);
 }
-
-// Wide-window images run bxq_kernel.
 template <int MODE, int NB>
-cudaError_t prepare_wide() {
-  static std::mutex mu;
-  static bool done[64] = {false};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  std::lock_guard<std::mutex> lock(mu);
-  if (dev < 64 && done[dev]) return cudaSuccess;
-  e = cudaFuncSetAttribute(bxq_kernel<MODE, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BxqSmem<MODE, NB>::alloc));
-  if (e == cudaSuccess && dev < 64) done[dev] = true;
-  return e;
+int launch_window(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {  // 3-bit window images
+  return launch_fused<bxw_kernel<MODE, NB>, BxwSmem<MODE, NB>::alloc, kFusedThreads<MODE>>(a, tmap, stream);
 }
-
 template <int MODE, int NB>
-int launch_wide(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
-  cudaError_t e = prepare_wide<MODE, NB>();
-  if (e != cudaSuccess) return cuda_status(e);
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(a.workers);
-  cfg.blockDim = dim3(MODE == kUmma ? kThreadsUmma : kThreadsSimt);
-  cfg.dynamicSmemBytes = BxqSmem<MODE, NB>::alloc;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cuda_status(cudaLaunchKernelEx(&cfg, bxq_kernel<MODE, NB>, a, tmap));
+int launch_wide(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {  // 4-bit window images
+  return launch_fused<bxq_kernel<MODE, NB>, BxqSmem<MODE, NB>::alloc, kFusedThreads<MODE>>(a, tmap, stream);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -378,8 +327,13 @@ int grb_bxr_gemv_static(const void* image, const bxr_header* h, const void* x, i
   const uint64_t tile_rows = h->mode == BXR_MODE_CODED ? kGemvMaxM : 16;
   const uint64_t need = counter_bytes(h) + uint64_t(h->partial_slots) * tile_rows * BXR_ROWS * 4;
   if (need > kStaticScratchBytes) return GRB_ERR_STATIC_LIMIT;
+  if (m > uint32_t(kGemvMaxM)) return GRB_ERR_UNSUPPORTED;
   void* scratch = nullptr;
   int st = static_scratch_address(&scratch);
+  if (st) return st;
+  // Every argument is checked before the first thing goes onto the stream: a refused call leaves the stream, the
+  // output and the shared array exactly as they were.
+  st = check_linear(image, h, x, ldx, m, y, ldy, scratch, kStaticScratchBytes, status, uint32_t(tile_rows));
   if (st) return st;
   // The array keeps whatever the previous call left: the per-row-block counters must start at zero.
   const cudaError_t e = cudaMemsetAsync(scratch, 0, counter_bytes(h), static_cast<cudaStream_t>(cuda_stream));

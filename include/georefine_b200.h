@@ -180,9 +180,10 @@ int grb_bxr_gemv(const void* device_image, const bxr_header* header, const void*
  * GPU that loads the library, held until the process exits).  The call makes no cudaMalloc, cudaFree or other
  * allocating call.
  *
- *  - Limit: images whose GEMV scratch (one counter per 128-row block plus 4 KiB per shared partial tile)
- *    exceeds the array are refused with GRB_ERR_STATIC_LIMIT and nothing is launched.  A 34816 x 5120 weight
- *    built for 148 workers needs about 1.7 MiB.
+ *  - Limit: images whose GEMV scratch (one counter per 128-row block plus 4 KiB per shared partial tile, 8 KiB for
+ *    the window layouts) exceeds the array are refused with GRB_ERR_STATIC_LIMIT.  A 34816 x 5120 weight built for
+ *    148 workers needs about 1.7 MiB.  Every refusal (this one, a batch above 8, a null or misaligned pointer, a bad
+ *    stride) comes before anything is put on the stream: the output and the array are left as they were.
  *  - First use: the first call on each device looks up the array's device address (with that device current)
  *    and keeps it; make that first call outside any stream capture.
  *  - Sharing: every call on a device uses the same array.  The counters are cleared on the given stream at
@@ -194,9 +195,10 @@ int grb_bxr_gemv_static(const void* device_image, const bxr_header* header, cons
                         void* y, int64_t ldy, const void* bias, uint32_t* status, void* cuda_stream);
 
 /* Registers, spills and shared memory of the compiled kernels, for tuning records (the reference reads the
- * same from its card in bi_kernel_attrs, gs/bi_csrc/bi_gemm.cuh:1104-1121).  which: 0 BCTX decode, 1 BXR
- * decode, 2 GEMV (m=1), 3 GEMM (N tile 16), 4 GEMM (N tile 128).  out = {registers, local bytes, static smem,
- * max dynamic smem, max threads}. */
+ * same from its card in bi_kernel_attrs, gs/bi_csrc/bi_gemm.cuh:1104-1121).  which: 0 BCTX decode; entropy-coded
+ * images: 1 decode twin, 2 GEMV (m=1), 3 GEMM (batch tile 16), 4 GEMM (batch tile 128); 3-bit window images: 5 decode
+ * twin, 6 GEMM (tile 16), 7 GEMM (tile 128); 4-bit window images: 8 decode twin, 9 GEMM (tile 16), 10 GEMM (tile 128).
+ * out = {registers, local bytes, static smem, max dynamic smem, max threads}. */
 int grb_kernel_attributes(int which, int out[5]);
 
 /* ---------------------------------------------------------------------------------------------------
