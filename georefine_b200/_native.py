@@ -23,7 +23,7 @@ VOIDP = ctypes.c_void_p
 EXPORTS = (
     "bcx_encode", "bcx_frequencies", "bcx_decode", "bcx_decode_compact", "bcx_free", "bcx_pack6", "bcx_unpack6",
     "bcx_checkpoint", "grb_bctx_build_lookup", "grb_bctx_decode_words", "bxr_build", "bxr_free", "bxr_decode_host",
-    "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_kernel_attributes",
+    "bxr_validate", "bxr_layout_version", "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_kernel_attributes",
     "grb_static_scratch_bytes", "grb_bxr_gemv_static", "grb_peer_control_bytes", "grb_peer_enable", "grb_peer_allreduce_bf16",
     "grb_peer_alloc", "grb_peer_free", "grb_peer_open", "grb_peer_close",
 )
@@ -39,7 +39,8 @@ class BxrHeader(ctypes.Structure):
     _fields_ = [("magic", ctypes.c_uint32), ("mode", ctypes.c_uint32), ("rows", ctypes.c_uint32),
                 ("cols", ctypes.c_uint32), ("row_blocks", ctypes.c_uint32), ("chunks", ctypes.c_uint32),
                 ("workers", ctypes.c_uint32), ("items", ctypes.c_uint32), ("partial_slots", ctypes.c_uint32),
-                ("blob_stride16", ctypes.c_uint32), ("lut_at", ctypes.c_uint64), ("base_at", ctypes.c_uint64),
+                ("blob_stride16", ctypes.c_uint32), ("layout_version", ctypes.c_uint32),
+                ("reserved0", ctypes.c_uint32), ("lut_at", ctypes.c_uint64), ("base_at", ctypes.c_uint64),
                 ("items_at", ctypes.c_uint64), ("worker_items_at", ctypes.c_uint64), ("states_at", ctypes.c_uint64),
                 ("blob_index_at", ctypes.c_uint64), ("blobs_at", ctypes.c_uint64), ("total_bytes", ctypes.c_uint64),
                 ("coded_bytes", ctypes.c_uint64), ("source_sha256", ctypes.c_uint8 * 32)]
@@ -71,6 +72,9 @@ def _declare(lib):
     lib.bxr_free.argtypes = [VOIDP]
     lib.bxr_free.restype = None
     lib.bxr_decode_host.argtypes = [U8P, u64, U16P]
+    lib.bxr_validate.argtypes = [U8P, u64]
+    lib.bxr_layout_version.argtypes = []
+    lib.bxr_layout_version.restype = u32
     lib.grb_bxr_workspace_bytes.argtypes = [ctypes.POINTER(BxrHeader), u32]
     lib.grb_bxr_workspace_bytes.restype = u64
     lib.grb_bxr_decode.argtypes = [VOIDP, ctypes.POINTER(BxrHeader), VOIDP, VOIDP, VOIDP]
@@ -90,9 +94,10 @@ def _declare(lib):
     lib.grb_peer_free.argtypes = [VOIDP]
     lib.grb_peer_open.argtypes = [U8P, ctypes.POINTER(VOIDP)]
     lib.grb_peer_close.argtypes = [VOIDP]
-    lib.grb_peer_allreduce_bf16.argtypes = [VOIDP, ctypes.POINTER(VOIDP), ctypes.POINTER(VOIDP), u64, u32, u32, VOIDP, u64, VOIDP, VOIDP]
+    lib.grb_peer_allreduce_bf16.argtypes = [VOIDP, ctypes.POINTER(VOIDP), ctypes.POINTER(VOIDP), u64, u32, u32, VOIDP, u64, u64, VOIDP, VOIDP]
     for name in EXPORTS:
-        if name not in ("bcx_free", "bxr_free", "grb_bxr_workspace_bytes", "grb_static_scratch_bytes", "grb_peer_control_bytes"):
+        if name not in ("bcx_free", "bxr_free", "grb_bxr_workspace_bytes", "grb_static_scratch_bytes", "grb_peer_control_bytes",
+                        "bxr_layout_version"):
             getattr(lib, name).restype = ci
 
 

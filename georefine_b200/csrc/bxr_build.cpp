@@ -460,9 +460,83 @@ bool window4_unblob(const uint8_t* blob, uint64_t blob_bytes, const uint8_t* bas
   return true;
 }
 
+// Structural check of an image before any of its offsets is followed, on the host or on the GPU: header fields, every
+// array inside the image, the work partition (it must be the one this library computes for the shape and worker
+// count: the kernels derive part of it themselves), the blob index and the per-mode size limits of a blob.  Cheap:
+// it reads the header, the item list and the blob index, never the blobs.
+bool image_is_well_formed(const uint8_t* img, uint64_t bytes) {
+  if (!img || bytes < sizeof(bxr_header)) return false;
+  bxr_header h;
+  std::memcpy(&h, img, sizeof h);
+  if (h.magic != BXR_MAGIC || h.layout_version != BXR_LAYOUT_VERSION || h.mode > BXR_MODE_WINDOW4) return false;
+  if (h.total_bytes != bytes || !h.rows || !h.cols || !h.workers || h.workers > 4096) return false;
+  if (h.row_blocks != (h.rows + BXR_ROWS - 1) / BXR_ROWS || h.chunks != (h.cols + BXR_COLS - 1) / BXR_COLS) return false;
+  const uint64_t nblobs = uint64_t(h.row_blocks) * h.chunks;
+  if (nblobs > 0xFFFFFFFEull) return false;
+  const bool coded = h.mode == BXR_MODE_CODED;
+  auto inside = [&](uint64_t at, uint64_t size, uint64_t align) {
+    return at >= sizeof(bxr_header) && (at % align) == 0 && size <= bytes && at <= bytes - size;
+  };
+  if (!inside(h.base_at, uint64_t(h.row_blocks) * BXR_ROWS, 1)) return false;
+  if (coded && !inside(h.lut_at, 4ull * BXR_PROB_TOTAL, 16)) return false;
+  if (!inside(h.items_at, sizeof(bxr_item) * uint64_t(h.items), 16)) return false;
+  if (!inside(h.worker_items_at, 4ull * (h.workers + 1ull), 4)) return false;
+  if (coded && !inside(h.states_at, 4ull * BXR_STREAMS * h.items, 16)) return false;
+  if (!inside(h.blob_index_at, 4ull * (nblobs + 1), 4)) return false;
+  if (!inside(h.blobs_at, 0, 16)) return false;
+  // the arrays follow one another in the builder's order and none reaches into the next
+  const uint64_t begin[7] = {h.lut_at, h.base_at, h.items_at, h.worker_items_at, h.states_at, h.blob_index_at, h.blobs_at};
+  const uint64_t size[6] = {coded ? 4ull * BXR_PROB_TOTAL : 0, uint64_t(h.row_blocks) * BXR_ROWS, sizeof(bxr_item) * uint64_t(h.items),
+                            4ull * (h.workers + 1ull), coded ? 4ull * BXR_STREAMS * h.items : 0, 4ull * (nblobs + 1)};
+  for (int i = 0; i < 6; ++i)
+    if (begin[i] > begin[i + 1] || size[i] > begin[i + 1] - begin[i]) return false;
+  // the work partition
+  const Plan plan = make_plan(h.rows, h.cols, h.workers);
+  if (plan.items.size() != h.items || plan.partial_slots != h.partial_slots) return false;
+  if (std::memcmp(img + h.items_at, plan.items.data(), sizeof(bxr_item) * plan.items.size()) != 0) return false;
+  if (std::memcmp(img + h.worker_items_at, plan.worker_items.data(), 4ull * (h.workers + 1ull)) != 0) return false;
+  // the blob index: ascending, inside the image, every blob within the limits of its mode
+  const auto* index = reinterpret_cast<const uint32_t*>(img + h.blob_index_at);
+  uint64_t lo = 0, hi = 0;
+  switch (h.mode) {
+    case BXR_MODE_RAW: lo = hi = BXR_RAW_TILE_BYTES; break;
+    case BXR_MODE_WINDOW: lo = BXW_LIST_AT; hi = BXR_BLOB_MAX; break;
+    case BXR_MODE_WINDOW4: lo = BXQ_LIST_AT; hi = BXQ_BLOB_MAX; break;
+    default: lo = BXR_WORDS_AT + 4; hi = BXR_BLOB_MAX; break;
+  }
+  if (index[0] != 0) return false;
+  for (uint64_t b = 0; b < nblobs; ++b) {
+    if (index[b + 1] < index[b]) return false;
+    const uint64_t size = uint64_t(index[b + 1] - index[b]) << 4;
+    if (size < lo || size > hi) return false;
+    if (h.blob_stride16 && index[b] != b * h.blob_stride16) return false;
+  }
+  if (h.blob_stride16 && (h.mode != BXR_MODE_WINDOW4 || index[nblobs] != nblobs * h.blob_stride16)) return false;
+  if (h.blobs_at + (uint64_t(index[nblobs]) << 4) != bytes) return false;
+  // row windows
+  const uint32_t base_max = h.mode == BXR_MODE_WINDOW4 ? BXQ_BASE_MAX : h.mode == BXR_MODE_WINDOW ? BXW_BASE_MAX : 241u;
+  const uint8_t* base = img + h.base_at;
+  for (uint64_t r = 0; r < uint64_t(h.row_blocks) * BXR_ROWS; ++r)
+    if (base[r] > base_max) return false;
+  return true;
+}
+
 }  // namespace
 
 extern "C" {
+
+uint32_t bxr_layout_version(void) { return BXR_LAYOUT_VERSION; }
+
+// 0 when the image is structurally sound (see image_is_well_formed), 1 otherwise.  Never throws, never reads outside
+// [image, image + image_bytes).
+int bxr_validate(const uint8_t* image, uint64_t image_bytes) {
+  try {
+    return image_is_well_formed(image, image_bytes) ? 0 : 1;
+  } catch (...) {
+    return 1;
+  }
+}
+
 
 void bxr_free(void* p) { std::free(p); }
 
@@ -645,6 +719,7 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
       }
     }
     h.blob_stride16 = blob_stride16;
+    h.layout_version = BXR_LAYOUT_VERSION;
     std::vector<uint32_t> index(nblobs + 1);
     uint64_t run = 0;
     for (uint32_t b = 0; b < nblobs; ++b) { index[b] = uint32_t(run >> 4); run += blobs[b].size(); }
@@ -683,7 +758,7 @@ int bxr_decode_host(const uint8_t* img, uint64_t bytes, uint16_t* out) {
     if (!img || !out || bytes < sizeof(bxr_header)) return 1;
     bxr_header h;
     std::memcpy(&h, img, sizeof h);
-    if (h.magic != BXR_MAGIC || h.total_bytes != bytes || !h.rows || !h.cols || h.mode > BXR_MODE_WINDOW4) return 1;
+    if (!image_is_well_formed(img, bytes)) return 1;   // every offset followed below has been checked
     const auto* items = reinterpret_cast<const bxr_item*>(img + h.items_at);
     const auto* index = reinterpret_cast<const uint32_t*>(img + h.blob_index_at);
     auto put = [&](uint32_t row, uint32_t col, uint16_t w) {

@@ -42,6 +42,10 @@
 #include <stdint.h>
 
 #define BXR_MAGIC 0x31525842u /* "BXR1" */
+/* Bumped whenever a blob layout, the work partition or the header changes: an image of another version is refused by
+ * bxr_validate (and by the disk cache, whose key includes it) instead of being streamed by kernels that no longer
+ * understand it. */
+#define BXR_LAYOUT_VERSION 2u
 #define BXR_ROWS 128
 #define BXR_COLS 128
 #define BXR_PHASES 4       /* lanes per row: phase q owns chunk columns [32q, 32q+32) */
@@ -157,6 +161,8 @@ typedef struct bxr_header {
   uint32_t workers, items;
   uint32_t partial_slots;         /* FP32 partial tiles the workspace must hold */
   uint32_t blob_stride16;         /* nonzero: every blob has this size (16-byte units) and blob b starts at b * size */
+  uint32_t layout_version;        /* BXR_LAYOUT_VERSION of the builder */
+  uint32_t reserved0;
   uint64_t lut_at;                /* u32[4096] slot records (absent in raw mode) */
   uint64_t base_at;               /* u8[row_blocks*128] exponent base per row */
   uint64_t items_at;              /* bxr_item[items] */

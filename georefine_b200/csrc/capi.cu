@@ -25,7 +25,7 @@ uint32_t batch_tile(uint32_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ?
 uint64_t counter_bytes(const bxr_header* h) { return (uint64_t(h->row_blocks) * 4 + 255) & ~uint64_t(255); }
 
 bool header_ok(const bxr_header* h) {
-  return h && h->magic == BXR_MAGIC && h->rows && h->cols && h->workers && h->mode <= BXR_MODE_WINDOW4 &&
+  return h && h->magic == BXR_MAGIC && h->layout_version == BXR_LAYOUT_VERSION && h->rows && h->cols && h->workers && h->mode <= BXR_MODE_WINDOW4 &&
          h->row_blocks == (h->rows + BXR_ROWS - 1) / BXR_ROWS && h->chunks == (h->cols + BXR_COLS - 1) / BXR_COLS;
 }
 
@@ -418,7 +418,7 @@ int grb_peer_enable(int peer_device) {
 }
 
 int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* const* controls, uint64_t block_bytes, uint32_t rank,
-                            uint32_t world, void* out, uint64_t elems, uint32_t* status, void* cuda_stream) {
+                            uint32_t world, void* out, uint64_t elems, uint64_t wait_limit_ns, uint32_t* status, void* cuda_stream) {
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (!partial || !receives || !controls || !out || !status || world < 1 || world > uint32_t(kPeerMaxRanks) || rank >= world) return GRB_ERR_ARGUMENT;
   if (elems == 0 || (elems & 7u) || elems > 0xFFFFFFF8ull || block_bytes < 2 * elems || (block_bytes & 15u)) return GRB_ERR_ARGUMENT;
@@ -437,6 +437,7 @@ int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* co
   a.rank = rank;
   a.world = world;
   a.status = status;
+  a.wait_limit_ns = wait_limit_ns ? wait_limit_ns : kWaitLimitNs;
   const uint64_t vectors = elems >> 3;
   // a small message stays in one CTA (no wait for other CTAs' pushes); a large one spreads over up to kPeerMaxCtas
   const uint32_t ctas = vectors <= 8 * kPeerThreads ? 1u : uint32_t(std::min<uint64_t>(kPeerMaxCtas, (vectors + 2 * kPeerThreads - 1) / (2 * kPeerThreads)));

@@ -11,8 +11,11 @@
 // One barrier per call is enough because the receive slots alternate with the call's parity: a rank can be writing
 // call k + 2 into a peer's slot only after that peer has announced call k + 1, i.e. after it finished reading call k.
 // The call's number lives in device memory and is advanced by the kernel itself, so a launch can be replayed from a
-// CUDA graph.  Waits are polls with a time limit; on expiry the status word gets kStatusTimeout and the kernel
-// finishes without waiting further (its output is then to be discarded).  No multicast, no TMA.
+// CUDA graph.  Waits are polls with a time limit (a launch argument); on expiry the status word gets kStatusTimeout
+// and the kernel finishes without waiting further: nothing is added, the output is left as it was, the tickets are
+// cleared and the call number still advances, so the context stays usable.  After a timeout the ranks no longer agree
+// on the call number: the caller zeroes every rank's control block before the group is used again.
+// No multicast, no TMA.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -41,6 +44,7 @@ struct PeerArgs {
   uint32_t elems;                      // multiple of 8
   uint32_t rank, world;
   uint32_t* status;
+  unsigned long long wait_limit_ns;    // how long a rank waits for its peers' flags before it gives up
 };
 
 __device__ __forceinline__ uint32_t peer_poll(const uint32_t* p) {
@@ -52,13 +56,13 @@ __device__ __forceinline__ void peer_post(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Waits until the flag has reached `call`; false after the time limit.
-__device__ __forceinline__ bool peer_wait(const uint32_t* flag, uint32_t call) {
+__device__ __forceinline__ bool peer_wait(const uint32_t* flag, uint32_t call, unsigned long long limit_ns) {
   if (int32_t(peer_poll(flag) - call) >= 0) return true;
   const unsigned long long t0 = global_ns();
   for (;;) {
     for (int i = 0; i < 32; ++i)
       if (int32_t(peer_poll(flag) - call) >= 0) return true;
-    if (global_ns() - t0 > kWaitLimitNs) return false;
+    if (global_ns() - t0 > limit_ns) return false;
   }
 }
 
@@ -83,16 +87,19 @@ __global__ void __launch_bounds__(kPeerThreads) peer_allreduce_kernel(const Peer
       if (r < a.world && r != a.rank) reinterpret_cast<uint4*>(a.receive[r] + (parity * a.world + a.rank) * a.block_bytes)[v] = x;
   }
   __syncthreads();
-  // 2. announce, by the CTA that completes the rank's push (one system-scope fence per CTA: it follows the CTA's
-  //    barrier, so it covers every thread's stores)
+  // 2. announce, by the CTA that completes the rank's push.  Release side: one system-scope fence per CTA after the
+  //    CTA's barrier (it covers every thread's stores), then the ticket.  Acquire side: the CTA that draws the last
+  //    ticket fences again before its threads post the flags, so that every other CTA's pushes are ordered before them.
   if (threadIdx.x == 0) {
     __threadfence_system();
-    last = atomicAdd(mine + kPeerPushedAt, 1u) == gridDim.x - 1 ? 1u : 0u;
+    const bool completes = atomicAdd(mine + kPeerPushedAt, 1u) == gridDim.x - 1;
+    if (completes) __threadfence_system();
+    last = completes ? 1u : 0u;
   }
   __syncthreads();
   if (last && threadIdx.x < a.world && threadIdx.x != a.rank) peer_post(a.control[threadIdx.x] + kPeerReadyAt + a.rank * kPeerFlagStride, call);
   // 3. wait for everybody's data, add
-  if (threadIdx.x < a.world && threadIdx.x != a.rank && !peer_wait(mine + kPeerReadyAt + threadIdx.x * kPeerFlagStride, call)) {
+  if (threadIdx.x < a.world && threadIdx.x != a.rank && !peer_wait(mine + kPeerReadyAt + threadIdx.x * kPeerFlagStride, call, a.wait_limit_ns)) {
     ok_all = 0;
     atomicOr(a.status, kStatusTimeout);
   }

@@ -7,13 +7,14 @@ that changes the content, writes renamed into place last, a completion marker, p
 "full" verification, a failed entry moved aside and never fatal) and spreads first-time conversion over CPU workers
 (``glc_serve/context_parallel_startup.py``).  This module does the same for resident images.
 
-Layout under the cache root, one entry per (source digest, shape, layout, workers)::
+Layout under the cache root, one entry per (source digest, shape, layout, workers, layout version of the library)::
 
     <root>/<key[:2]>/<key>.bxr        the image, written to <key>.bxr.partial-<host>-<pid>-<nonce> and renamed
     <root>/<key[:2]>/<key>.json       the entry's description, written last: its presence marks the entry complete
 
 An entry is served only if its description matches the request, the file has the recorded size and SHA-256, the
-image's own header agrees (shape, workers, source digest) and - with ``verify="full"`` - the host twin of the GPU
+image passes the library's structural check (``bxr_validate``: layout version, every offset and extent, the work
+partition, the blob index), its header agrees (shape, workers, source digest) and - with ``verify="full"`` - the host twin of the GPU
 decoder reproduces the source digest from it.  Anything else moves the entry aside and reports a miss.
 """
 from __future__ import annotations
@@ -49,9 +50,18 @@ def default_cache_root() -> Path:
     return (Path(xdg).expanduser() if xdg else Path.home() / ".cache") / "georefine-b200" / "images"
 
 
+def layout_version() -> int:
+    """The resident layout version of the loaded library: part of every key, so entries written by a build with
+    another blob layout or work partition are never looked at."""
+    from . import _native
+
+    return int(_native.lib().bxr_layout_version())
+
+
 def cache_key(source_sha256: str, shape, layout: str, workers: int) -> str:
-    material = {"schema": SCHEMA, "cache_format": CACHE_FORMAT, "source_sha256": source_sha256,
-                "shape": [int(shape[0]), int(shape[1])], "layout": layout, "workers": int(workers)}
+    material = {"schema": SCHEMA, "cache_format": CACHE_FORMAT, "layout_version": layout_version(),
+                "source_sha256": source_sha256, "shape": [int(shape[0]), int(shape[1])], "layout": layout,
+                "workers": int(workers)}
     return hashlib.sha256(json.dumps(material, sort_keys=True, separators=(",", ":")).encode()).hexdigest()
 
 
@@ -98,8 +108,9 @@ class ImageCache:
                 self.stats["misses"] += 1
                 return None
             meta = json.loads(meta_path.read_text(encoding="utf-8"))
-            want = {"schema": SCHEMA, "cache_format": CACHE_FORMAT, "source_sha256": source_sha256,
-                    "shape": [int(shape[0]), int(shape[1])], "layout": layout, "workers": int(workers)}
+            want = {"schema": SCHEMA, "cache_format": CACHE_FORMAT, "layout_version": layout_version(),
+                    "source_sha256": source_sha256, "shape": [int(shape[0]), int(shape[1])], "layout": layout,
+                    "workers": int(workers)}
             for name, value in want.items():
                 if meta.get(name) != value:
                     raise ImageCacheError(f"description field {name} differs")
@@ -108,6 +119,7 @@ class ImageCache:
             image = np.fromfile(image_path, dtype=np.uint8)
             if hashlib.sha256(image.tobytes()).hexdigest() != meta.get("image_sha256"):
                 raise ImageCacheError("image SHA-256 differs from its description")
+            resident.validate_image(image)   # raises ValueError: offsets, partition, blob index, layout version
             h = resident.header_of(image)
             if (h.total_bytes != image.size or (h.rows, h.cols) != tuple(shape) or h.workers != workers
                     or bytes(h.source_sha256).hex() != source_sha256):
@@ -143,7 +155,8 @@ class ImageCache:
                 f.flush()
                 os.fsync(f.fileno())
             os.replace(partial, image_path)
-            meta = {"schema": SCHEMA, "cache_format": CACHE_FORMAT, "source_sha256": source, "shape": list(shape),
+            meta = {"schema": SCHEMA, "cache_format": CACHE_FORMAT, "layout_version": int(h.layout_version),
+                    "source_sha256": source, "shape": list(shape),
                     "layout": layout, "workers": workers, "mode": int(h.mode), "image_bytes": len(data),
                     "image_sha256": hashlib.sha256(data).hexdigest(), "coded_bytes": int(h.coded_bytes)}
             tmp = meta_path.with_name(meta_path.name + f".partial-{uuid.uuid4().hex[:8]}")

@@ -6,7 +6,7 @@ CUDA IPC and maps theirs.  A row-parallel linear writes its partial output into 
 ``PeerReducer.reduce(slot, out)`` then launches ``grb_peer_allreduce_bf16`` (``csrc/peer_reduce.cuh``): every rank
 copies its partial into the peers' receive areas, announces it with a flag, waits for the peers' flags and adds all
 partials in rank order (FP32): the same bits on every rank.  The launch allocates nothing, does not touch the host
-and may be captured in a CUDA graph, unlike a NCCL collective on this pool.
+and may be captured in a CUDA graph.
 
 The reference has no counterpart (it runs a linear on one device, ``glc_loader/tbe_device_map.py:46-56``).
 """
@@ -32,7 +32,7 @@ class PeerReducer:
     """``slots`` = {name: number of BF16 elements}; every rank must construct it with the same arguments and call
     ``reduce`` in the same order.  Construction is a collective over ``group`` (IPC handles are exchanged)."""
 
-    def __init__(self, slots: dict, *, device=None, group=None):
+    def __init__(self, slots: dict, *, device=None, group=None, wait_limit_ns: int = 0):
         import torch
         import torch.distributed as dist
 
@@ -40,6 +40,7 @@ class PeerReducer:
             raise PeerError("torch.distributed is not initialised")
         self.lib = _native.lib()
         self.group = group
+        self.wait_limit_ns = int(wait_limit_ns)   # 0: the library's default (two seconds)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > 8:
             raise PeerError("at most 8 ranks")
@@ -141,7 +142,7 @@ class PeerReducer:
         receives = (ctypes.c_void_p * self.world)(*[p + receive_at for p in self.pointers])
         stream = torch.cuda.current_stream(self.device) if stream is None else stream
         rc = self.lib.grb_peer_allreduce_bf16(self.local_ptr + at, receives, self.controls, block, self.rank, self.world,
-                                              out.data_ptr(), n, self.status.data_ptr(), stream.cuda_stream)
+                                              out.data_ptr(), n, self.wait_limit_ns, self.status.data_ptr(), stream.cuda_stream)
         if rc != 0:
             raise PeerError(f"grb_peer_allreduce_bf16 failed with code {rc}")
         return out

@@ -76,6 +76,14 @@ def header_of(image) -> _native.BxrHeader:
     return _native.BxrHeader.from_buffer_copy(image[:ctypes.sizeof(_native.BxrHeader)].tobytes())
 
 
+def validate_image(image) -> None:
+    """Structural check of an image (layout version, offsets, work partition, blob index) before anything follows an
+    offset inside it; raises ValueError.  Cheap: the blobs themselves are not read."""
+    a = np.ascontiguousarray(image, dtype=np.uint8)
+    if _native.lib().bxr_validate(a.ctypes.data_as(_native.U8P), a.size):
+        raise ValueError("resident image is malformed or was built by another version of the layout")
+
+
 def decode_image_host(image) -> np.ndarray:
     """Host twin of the GPU decoder; used to bind an image to its source digest before upload."""
     h = header_of(image)
@@ -92,6 +100,7 @@ class ResidentWeight:
     def __init__(self, image: np.ndarray, device, *, max_m: int = 128, verify: bool = True):
         import torch
 
+        validate_image(image)   # always: the kernels follow the image's offsets without further checks
         self.header = header_of(image)
         h = self.header
         if verify:

@@ -139,8 +139,19 @@ int bxr_build(const uint16_t* words, uint32_t rows, uint32_t cols, uint32_t work
               uint32_t layout, const uint8_t* source_sha256, uint8_t** image, uint64_t* image_bytes);
 void bxr_free(void* p);
 
+/* Structural check of an image before any offset inside it is followed, by the host twin or by a kernel: layout
+ * version (bxr_layout_version(), bumped on every format change), header fields, every array inside
+ * [image, image + image_bytes), the work partition (it must be the one this library computes for the shape and worker
+ * count), an ascending blob index and the per-mode size limits of every blob.  Reads the header, the item list and the
+ * blob index only.  0 sound, 1 malformed.  Loaders call it on every image that did not come straight out of bxr_build
+ * (a disk cache, a file): the reference's transcode cache makes the same kind of check on its entries
+ * (gs/transcode_cache.py) before trusting them. */
+int bxr_validate(const uint8_t* image, uint64_t image_bytes);
+uint32_t bxr_layout_version(void);
+
 /* Host twin of the GPU decoder, used to bind an image to its source digest before upload (the check the
- * reference makes at cr/bitexact_context_gpu.py:104-105).  0 ok, 1 malformed image, 2 corrupt stream. */
+ * reference makes at cr/bitexact_context_gpu.py:104-105).  Runs bxr_validate first.  0 ok, 1 malformed image,
+ * 2 corrupt stream. */
 int bxr_decode_host(const uint8_t* image, uint64_t image_bytes, uint16_t* words);
 
 /* Bytes of caller-owned device scratch the fused entry points need for this image and batch tile:
@@ -222,7 +233,9 @@ int grb_kernel_attributes(int which, int out[5]);
  * waits for the peers' flags and adds.  The partial may be overwritten as soon as the launch has completed locally.
  * The call allocates nothing and does not synchronise with the host; it can be captured in a CUDA graph (the call
  * counter lives in the control block).  A peer that never makes the matching call shows as GRB_STATUS_TIMEOUT in
- * *status after two seconds: nothing spins without a limit.  world <= 8, elems % 8 == 0.
+ * *status after wait_limit_ns nanoseconds (0 = the default, two seconds): nothing spins without a limit, the kernel
+ * returns by itself, `out` is left as it was and the context stays usable.  The ranks then disagree on the call
+ * number: zero every rank's control block before the group reduces again.  world <= 8, elems % 8 == 0.
  * grb_peer_enable(device) enables access from the current device to a peer's memory (GRB_ERR_UNSUPPORTED if the
  * two are not connected). */
 uint64_t grb_peer_control_bytes(void);
@@ -236,7 +249,7 @@ int grb_peer_free(void* ptr);
 int grb_peer_open(const uint8_t handle[64], void** ptr);
 int grb_peer_close(void* ptr);
 int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* const* controls, uint64_t block_bytes, uint32_t rank,
-                            uint32_t world, void* out, uint64_t elems, uint32_t* status, void* cuda_stream);
+                            uint32_t world, void* out, uint64_t elems, uint64_t wait_limit_ns, uint32_t* status, void* cuda_stream);
 
 #ifdef __cplusplus
 }
