@@ -1,19 +1,24 @@
 """Benchmark of the fused decode-GEMM path on the hybrid-decoder linear shapes (hidden 5120).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--layout window4|window|rans]
 
 One step = the four linears of a decoder layer (QKV 5120->7168, O 5120->5120, gate|up 5120->2x17408,
 down 17408->5120), each at batch M = 1, 64 and 128: twelve fused decode-GEMM launches over synthetic
 weights N(0, 0.02) x LogNormal(0, 0.25) per row (seed 1) held in HBM as compressed resident images.
 The coded working set (~440 MB) is larger than the L2, so no flush is needed between iterations.
 
-metric  fused decode-GEMM effective BF16 weight bandwidth: dense BF16 bytes of the weights the step
-        multiplies by (2*N*K per launch) divided by the step time, GB/s, whole job.
-value   inputs resident in HBM, CUDA events, max over ranks.
-e2e     the same step through ResidentWeight.linear with activations in pinned host memory copied in and
-        the down-projection outputs copied back every step.
+metric    fused decode-GEMM effective BF16 weight bandwidth: dense BF16 bytes of the weights the step
+          multiplies by (2*N*K per launch) divided by the step time, GB/s, whole job.
+value     inputs resident in HBM, CUDA events around exactly K steps, max over ranks; the K-step region is
+          repeated until at least half a second has been timed and the median region is reported.
+roofline  algorithmic bytes of the step (coded images + activations in + outputs out) over the same
+          ms_per_step, against the measured copy bandwidth.
+e2e       the same step through the descriptor call with activations in pinned host memory copied in and
+          the down-projection outputs copied back every step.
+parity    outside the timed region: the decode twin reproduces every weight's digest, every output is
+          within 1e-2 (relative) of the FP32 product, rows are bitwise equal across M.
 With --gpus N (torchrun) the layer is tensor-parallel: QKV and gate|up split by weight rows (no traffic), O
-and down by weight columns followed by an NCCL all-reduce of the BF16 partials; total work is fixed
+and down by weight columns followed by the sum of the BF16 partials across GPUs; total work is fixed
 (strong scaling).  --impl reference times the reference's own CPU decode + matmul on a bounded sample.
 """
 from __future__ import annotations
@@ -41,13 +46,13 @@ LINEARS = [("qkv", 7168, HIDDEN, "col", [5120, 1024, 1024]), ("o", HIDDEN, HIDDE
            ("gate_up", 2 * FFN, HIDDEN, "col", [FFN, FFN]), ("down", HIDDEN, FFN, "row", None)]
 BATCHES = (1, 64, 128)
 SEED = 1
-# dram__bytes_read+write over algorithmic bytes of one launch, from the ncu captures summarised under profiles/, each
-# on the step's top launch (gate|up at M = 128) unless noted: window4 layout 270.1 MB read + 4.5 MB written for
-# 278.9 MB algorithmic (profiles/bxq_kernel_gemm_m128_gate_up_34816x5120.md; part of y is still in L2 when the launch
-# ends, the FP32 partial tiles of split row blocks stay in L2 or in shared memory); window layout 261.4 + 14.2 MB for
-# 260.8 MB (profiles/bxw_kernel_gemm_m128_gate_up_34816x5120.md); rans layout, down projection at M = 1: 122.2 + 3.4 MB
-# for 122.0 MB (profiles/bxr_kernel_gemm_m1_down_5120x17408.md).
+REL_TOL = 1e-2
+MIN_TIMED_SECONDS = 0.5
+# dram__bytes_read + dram__bytes_write over the algorithmic bytes of one launch, from one ncu capture per layout of the
+# step's largest launch (gate|up at M = 128; the entropy-coded layout: the down projection at M = 1).  Below 1 where
+# part of y is still in the L2 when the launch ends and the FP32 partial tiles never reach DRAM.
 DRAM_TRAFFIC_RATIO = {"window4": 0.984, "window": 1.057, "rans": 1.03}
+KERNEL_OF = {"window4": "bxq_kernel", "window": "bxw_kernel", "rans": "bxr_kernel"}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -78,33 +83,47 @@ def measured_hbm_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clock and throttle-reason samples taken while the timed region runs."""
+    """nvidia-smi clock and throttle-reason samples, each stamped with its arrival time.  Started before the weights
+    are built (the tool takes a while to produce its first line on a machine with many GPUs), read over the window of
+    the timed region only."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.thread = index, None, [], None
 
-    def __enter__(self):
+    def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
+            self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
         return self
 
-    def __exit__(self, *exc):
-        if self.proc is not None:
-            time.sleep(0.15)
-            self.proc.terminate()
-            self.thread.join(timeout=2)
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.monotonic(), line))
 
-    def summary(self):
+    def wait_first_sample(self, seconds=8.0):
+        t0 = time.monotonic()
+        while self.proc is not None and not self.lines and time.monotonic() - t0 < seconds:
+            time.sleep(0.02)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            if self.thread is not None:
+                self.thread.join(timeout=2)
+
+    def summary(self, t0, t1):
+        """Over [t0, t1] (monotonic seconds), widened by one sampling period on either side."""
         sm, mx, reasons = [], [], set()
-        for line in self.lines:
+        for at, line in list(self.lines):
+            if at < t0 - 0.03 or at > t1 + 0.05:
+                continue
             f = [v.strip() for v in line.split(",")]
             if len(f) < 9:
                 continue
@@ -118,15 +137,15 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"], "samples": 0}
-        busy = [v for v in sm if v >= 0.5 * max(sm)] or sm
-        return {"sm_mhz": float(np.median(busy)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
 # ------------------------------------------------------------------------------------------------ CPU arm
 def cpu_reference_run(sample_rows, steps, warmup, threads):
     """The reference's CPU path on slabs of the benchmark weights: decode every frame, then F.linear at every
-    batch size.  Returns (value in GB/s, description).  Uses oracle/_ref (the reference's coder compiled from
-    its sources) when it was built, else the plain-C oracle port."""
+    batch size.  Returns (GB/s, seconds per step, description); the description splits the CPU seconds into decode
+    and matmul.  Uses oracle/_ref (the reference's coder compiled from its sources) when it was built, else the
+    plain-C oracle port."""
     import torch
     import torch.nn.functional as F
 
@@ -148,51 +167,64 @@ def cpu_reference_run(sample_rows, steps, warmup, threads):
 
     def one(job):
         k, frame = job
-        total = 0.0
-        for m in BATCHES:
+        decode_s = matmul_s = 0.0
+        for m in BATCHES:          # the reference decodes the whole weight on every forward call
+            t0 = time.perf_counter()
             w = torch.from_numpy(coder.decode(frame).view(np.int16)).view(torch.bfloat16)
-            total += float(F.linear(xs[(m, k)], w).float().abs().sum())
-        return total
+            t1 = time.perf_counter()
+            F.linear(xs[(m, k)], w)
+            decode_s += t1 - t0
+            matmul_s += time.perf_counter() - t1
+        return decode_s, matmul_s
 
     def step():
         with ThreadPoolExecutor(threads) as pool:
-            return sum(pool.map(one, frames))
+            parts = list(pool.map(one, frames))
+        return sum(p[0] for p in parts), sum(p[1] for p in parts)
 
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
+    decode_s = matmul_s = 0.0
     for _ in range(steps):
-        step()
+        d, mm = step()
+        decode_s += d
+        matmul_s += mm
     dt = (time.perf_counter() - t0) / max(steps, 1)
     sample = f"first {sample_rows} rows of each of the four weights as {slab}-row BCTX frames, decode + F.linear at M=1,64,128"
-    return dense_bytes / dt / 1e9, dt, {"kind": kind, "cores": threads, "sample": sample}
+    return dense_bytes / dt / 1e9, dt, {"kind": kind, "cores": threads, "sample": sample,
+                                        "decode_cpu_seconds_per_step": round(decode_s / max(steps, 1), 3),
+                                        "matmul_cpu_seconds_per_step": round(matmul_s / max(steps, 1), 3)}
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
 class Layer:
     """The four linears of one decoder layer on this rank, as resident images (tensor-parallel when world > 1)."""
 
-    def __init__(self, rank, world, device, layout="window4"):
+    def __init__(self, rank, world, device, layout="window4", weights=None, with_peer=True):
         import torch
 
         from georefine_b200 import tp
         from georefine_b200.resident import ResidentWeight
 
         self.rank, self.world, self.device = rank, world, device
-        weights = all_weights()
+        weights = dict(all_weights() if weights is None else weights)
         self.entries = []
         for name, n, k, kind, members in LINEARS:
             w = weights.pop(name)
             if kind == "col":
-                local = np.concatenate([w[lo:hi] for lo, hi in tp.column_parallel_rows(members, rank, world)], axis=0)
+                spans = tp.column_parallel_rows(members, rank, world)
+                local = np.concatenate([w[lo:hi] for lo, hi in spans], axis=0)
                 k0, k1 = 0, k
             else:
+                spans = [(0, n)]
                 k0, k1 = tp.row_range(k, rank, world, tp.CHUNK)
                 local = w[:, k0:k1]
-            res = ResidentWeight.from_words(np.ascontiguousarray(local), device, max_m=max(BATCHES), verify=False, layout=layout)
-            self.entries.append({"name": name, "kind": kind, "n": n, "k": k, "k0": k0, "k1": k1, "res": res,
-                                 "y": {m: torch.empty(m, res.N, device=device, dtype=torch.bfloat16) for m in BATCHES}})
-            del w, local
+            local = np.ascontiguousarray(local)
+            res = ResidentWeight.from_words(local, device, max_m=max(BATCHES), verify=False, layout=layout)
+            self.entries.append({"name": name, "kind": kind, "n": n, "k": k, "k0": k0, "k1": k1, "res": res, "spans": spans,
+                                 "words": local, "y": {m: torch.empty(m, res.N, device=device, dtype=torch.bfloat16) for m in BATCHES}})
+            del w
         g = torch.Generator().manual_seed(SEED + 1)
         self.x_host = {(m, k): torch.randn(m, k, generator=g).to(torch.bfloat16).pin_memory() for m in BATCHES for k in (HIDDEN, FFN)}
         self.x = {key: v.to(device) for key, v in self.x_host.items()}
@@ -200,11 +232,11 @@ class Layer:
         self.xv = {(m, e["name"]): self.x[(m, e["k"])][:, e["k0"]:e["k1"]] for m in BATCHES for e in self.entries}
         self.launches_per_step = len(LINEARS) * len(BATCHES)
         # More than one rank: the partial outputs of the column-split linears (O, down) are summed over peer memory by
-        # the library's own kernel, which - unlike a NCCL collective on this pool - can be captured in a CUDA graph.
-        # The linear writes its partial into the reducer's slot (e["y"]), the sum lands in e["sum"].  NCCL is the
-        # fallback if the buffers cannot be mapped on every rank.
+        # the library's own kernel, which can be captured in a CUDA graph with the fused launches.  The linear writes its
+        # partial into the reducer's slot (e["y"]), the sum lands in e["sum"].  NCCL is the fallback if the buffers cannot
+        # be mapped on every rank.
         self.peer, self.reduce_kind = None, "none"
-        if world > 1:
+        if world > 1 and with_peer:
             self.peer, self.reduce_kind = self._peer_reducer(), "nccl"
             if self.peer is not None:
                 self.reduce_kind = "peer"
@@ -267,21 +299,12 @@ class Layer:
         """What one launch must move: the coded image once, the activations in, the outputs out."""
         return e["res"].coded_bytes + 2 * m * (e["k1"] - e["k0"]) + 2 * m * e["res"].N
 
-    def call(self, e, m, x):
-        import torch.distributed as dist
-
-        y = e["y"][m]
-        e["res"].gemm(x[:, e["k0"]:e["k1"]], y)
-        if e["kind"] == "row" and self.world > 1:
-            self.all_reduce(e, m)
-        return self.result(e, m)
-
     def step(self):
         for m in BATCHES:
             for e in self.entries:
-                self.call(e, m, self.x[(m, e["k"])])
-
-    # (call() slices x per launch; the end-to-end loop below uses the views prepared once in self.xv)
+                e["res"].gemm(self.xv[(m, e["name"])], e["y"][m])
+                if e["kind"] == "row" and self.world > 1:
+                    self.all_reduce(e, m)
 
     def segmented_step(self):
         """Multi-rank step as CUDA graphs of the fused launches with the NCCL all-reduces launched between them
@@ -320,7 +343,6 @@ class Layer:
         """Host buffers in, host buffers out, through the descriptor call `weight(x, y)` a serving engine makes:
         every activation is copied from pinned host memory first, the down projection's output is copied back."""
         import torch
-        import torch.distributed as dist
 
         for m in BATCHES:
             for k in (HIDDEN, FFN):
@@ -374,56 +396,147 @@ class Layer:
     def status(self):
         return sum(e["res"].check_status() for e in self.entries) + (self.peer.check_status() if self.peer is not None else 0)
 
+    # ---- checks outside the timed region --------------------------------------------------------------------
+    def parity(self):
+        """This rank's images and outputs against FP32 arithmetic on the source words: the decode twin must reproduce
+        the digest of the words the image was built from; every fused product must be within REL_TOL of the FP32
+        product (relative to the call's largest magnitude); rows must be bitwise the same at every batch size."""
+        import hashlib
 
-def timed(fn, steps, warmup, world):
+        import torch
+
+        worst, rows_equal, digests = 0.0, True, True
+        for e in self.entries:
+            res = e["res"]
+            got = res.decode(check=False).view(torch.int16).cpu().numpy().view(np.uint16)
+            digests = digests and hashlib.sha256(got.tobytes()).digest() == hashlib.sha256(e["words"].tobytes()).digest()
+            w = torch.from_numpy(e["words"].view(np.int16)).view(torch.bfloat16).to(self.device)
+            top = None
+            for m in sorted(BATCHES, reverse=True):
+                x = self.xv[(m, e["name"])]
+                y = torch.empty(m, res.N, device=self.device, dtype=torch.bfloat16)
+                res.gemm(x, y)
+                ref = x.float() @ w.float().T
+                worst = max(worst, float((y.float() - ref).abs().max() / ref.abs().max()))
+                # the same leading rows of the activations at every batch size? they are separate draws: compare the
+                # rows of a batch cut from the largest one instead
+                if top is None:
+                    top = (x, y.clone())
+                else:
+                    ycut = torch.empty(m, res.N, device=self.device, dtype=torch.bfloat16)
+                    res.gemm(top[0][:m], ycut)
+                    rows_equal = rows_equal and bool(torch.equal(ycut.view(torch.int16), top[1][:m].view(torch.int16)))
+            del w
+        return {"max_rel": float(f"{worst:.3e}"), "tolerance": REL_TOL, "rows_equal": bool(rows_equal), "decode_digests_ok": bool(digests),
+                "status_word": self.status()}
+
+    def tp_parity(self, full_weights):
+        """More than one rank: the summed outputs of the column-split linears (O, down) on this rank against the FP32
+        product with the WHOLE weight, computed on this GPU alone."""
+        import torch
+
+        worst = 0.0
+        for e in self.entries:
+            if e["kind"] != "row":
+                continue
+            w = torch.from_numpy(full_weights[e["name"]].view(np.int16)).view(torch.bfloat16).to(self.device)
+            for m in BATCHES:
+                ref = self.x[(m, e["k"])].float() @ w.float().T
+                got = self.result(e, m).float()
+                worst = max(worst, float((got - ref).abs().max() / ref.abs().max()))
+            del w
+        return {"max_rel": float(f"{worst:.3e}"), "tolerance": REL_TOL, "checked": "summed O and down outputs vs the one-GPU FP32 product"}
+
+
+def timed_regions(fn, steps, warmup, world, min_seconds=MIN_TIMED_SECONDS, max_regions=400):
+    """W warm-up steps, then regions of exactly K steps, each bracketed by a barrier and a device synchronise on both
+    sides and timed with CUDA events (max over ranks), repeated until min_seconds have been timed.  Returns the list of
+    per-region milliseconds per step and the (monotonic) host times around the whole measurement."""
     import torch
     import torch.distributed as dist
 
+    def region():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
     for _ in range(warmup):
         fn()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return float(ms.item())
+    t0 = time.monotonic()
+    out = [region()]
+    want = int(min(max_regions, max(1, -(-min_seconds * 1e3 // max(out[0] * steps, 1e-6)))))   # same on every rank
+    while len(out) < want:
+        out.append(region())
+    return out, t0, time.monotonic()
 
 
-def kernel_times(layer, steps):
-    """Per-launch durations of the fused kernel (CUDA events around every launch on the launching stream)."""
+def launch_times(layer):
+    """Microseconds of every (linear, batch size) launch in a stream of such launches, rotating over enough copies of
+    the image that the weights never come from the L2 (the practice of the reference's tuner,
+    glc_serve/tbe_desc.py:160-175)."""
     import torch
 
-    per = {}
-    for _ in range(steps):
+    from georefine_b200 import tune
+
+    out = {}
+    for e in layer.entries:
+        res = e["res"]
+        copies = [res] + [res.clone() for _ in range(tune.copies_for(res.coded_bytes) - 1)]
         for m in BATCHES:
-            for e in layer.entries:
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                x = layer.x[(m, e["k"])][:, e["k0"]:e["k1"]]
-                a.record()
-                e["res"].gemm(x, e["y"][m])
-                b.record()
-                per.setdefault((e["name"], m), []).append((a, b))
-    # the CUDA-core GEMV at M = 1, for the record (not part of the timed step: its rows are M-invariant only
-    # among M = 1..8, while the step compares M = 1, 64 and 128 bit for bit)
-    for _ in range(steps):
-        for e in layer.entries:
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            x = layer.x[(1, e["k"])][:, e["k0"]:e["k1"]]
-            a.record()
-            e["res"].gemv(x, e["y"][1])
-            b.record()
-            per.setdefault((e["name"], "gemv1"), []).append((a, b))
+            x, y = layer.xv[(m, e["name"])], e["y"][m]
+            reps = max(20, int(1e9 // res.coded_bytes))
+            out[(e["name"], m)] = tune.rotation_us(lambda i: copies[i].gemm(x, y), len(copies), reps)
+        del copies
+        torch.cuda.empty_cache()
+    return out
+
+
+def dense_times(layer):
+    """The dense BF16 yardsticks on the same GPU and the same (local) weights: the library's own GEMV at M = 1 and
+    torch.matmul at every batch size, rotating over copies like launch_times."""
+    import torch
+
+    from georefine_b200 import tune
+    from georefine_b200.dense import dense_gemv
+
+    own, lib = {}, {}
+    for e in layer.entries:
+        w = torch.from_numpy(e["words"].view(np.int16)).view(torch.bfloat16).to(layer.device)
+        copies = [w] + [w.clone() for _ in range(tune.copies_for(w.numel() * 2) - 1)]
+        reps = max(20, int(1e9 // (w.numel() * 2)))
+        for m in BATCHES:
+            x, y = layer.xv[(m, e["name"])].contiguous(), torch.empty(m, w.shape[0], device=layer.device, dtype=torch.bfloat16)
+            lib[(e["name"], m)] = tune.rotation_us(lambda i: torch.matmul(x, copies[i].T, out=y), len(copies), reps)
+            if m == 1:
+                own[e["name"]] = tune.rotation_us(lambda i: dense_gemv(copies[i], x, y), len(copies), reps)
+        del copies, w
+        torch.cuda.empty_cache()
+    return own, lib
+
+
+def capture(step, eager_steps=2):
+    """The step as one CUDA graph (the entry points neither allocate nor synchronise)."""
+    import torch
+
+    for _ in range(eager_steps):
+        step()
     torch.cuda.synchronize()
-    return {key: float(np.mean([a.elapsed_time(b) for a, b in evs])) for key, evs in per.items()}
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    return graph.replay
 
 
 def _deadline(seconds):
@@ -443,7 +556,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    _deadline(300)
+    _deadline(540)
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -452,18 +565,18 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device: the fused path has no CPU fallback")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    clocks = ClockSampler(local).start()
     if world > 1:
         import datetime
 
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
-    layer = Layer(rank, world, device, layout=args.layout)
+    weights = all_weights()
+    layer = Layer(rank, world, device, layout=args.layout, weights=weights)
 
-    # The timed step is replayed from a CUDA graph (the entry points neither allocate nor synchronise), so the
-    # host's launch cost is not part of `value`; the e2e figure below goes through the eager public API.
+    # The timed step is replayed from a CUDA graph, so the host's launch cost is not part of `value`; the e2e figure
+    # below goes through the public descriptor call.  NCCL collectives are never captured: with the NCCL fallback
+    # multi-rank runs replay graphs of the fused launches only and issue the collectives eagerly between them.
     step_fn, launch = layer.step, "eager"
-    # With more than one rank the step contains NCCL all-reduces; capturing those in a graph hung on this pool
-    # (twice, at two ranks), so multi-rank runs replay graphs of the fused launches only and issue the
-    # collectives eagerly between them (segmented_step).
     if world > 1 and layer.peer is not None:
         for _ in range(2):
             layer.step()
@@ -472,13 +585,7 @@ def run_ours(args):
     whole_graph = world == 1 or layer.peer is not None   # nothing of NCCL inside the step
     if not args.no_graph and whole_graph:
         try:
-            for _ in range(2):
-                layer.step()
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                layer.step()
-            step_fn, launch = graph.replay, "cuda_graph" + (" (peer-memory all-reduce inside)" if world > 1 else "")
+            step_fn, launch = capture(layer.step), "cuda_graph" + (" (peer-memory all-reduce inside)" if world > 1 else "")
         except Exception as exc:  # noqa: BLE001
             launch = f"eager (graph capture failed: {type(exc).__name__})"
         if world > 1:   # every rank must replay the same thing: one failed capture sends all of them to eager launches
@@ -493,8 +600,11 @@ def run_ours(args):
         seg = layer.segmented_step()
         if seg is not None:
             step_fn, launch = seg, "cuda_graph segments + eager all-reduce"
-    with ClockSampler(local) as clocks:
-        ms = timed(step_fn, args.steps, args.warmup, world)
+    clocks.wait_first_sample()
+    regions, t_begin, t_end = timed_regions(step_fn, args.steps, args.warmup, world)
+    clock_summary = clocks.summary(t_begin, t_end)
+    ms = float(np.median(regions))
+
     e2e_fn, e2e_launch = layer.step_e2e, "eager"
     if not args.no_graph and whole_graph:
         try:
@@ -507,30 +617,22 @@ def run_ours(args):
             dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
             if not int(agreed.item()):
                 e2e_fn, e2e_launch = layer.step_e2e, "eager (graph capture failed on some rank)"
-    ms_e2e = timed(e2e_fn, args.steps, args.warmup, world)
+    e2e_regions, _, _ = timed_regions(e2e_fn, args.steps, args.warmup, world)
+    ms_e2e = float(np.median(e2e_regions))
     y_check = [layer.y_host[m].clone() for m in BATCHES]
     layer.step_e2e()                                     # the eager public-API path must land the same outputs
     e2e_same = all(bool((a.view(torch.int16) == layer.y_host[m].view(torch.int16)).all()) for a, m in zip(y_check, BATCHES))
-    ktimes = kernel_times(layer, max(2, min(args.steps, 10)))
+    tp_check = layer.tp_parity(weights) if world > 1 else None
     status = layer.status()
+    clocks.stop()
 
     dense = layer.dense_bytes_per_step()
     peak, peak_kind = measured_hbm_peak()
-    algo = sum(layer.algorithmic_bytes(e, m) for m in BATCHES for e in layer.entries)
-    gemv_ms = sum(ktimes.pop((e["name"], "gemv1")) for e in layer.entries)
-    gemv_bytes = sum(layer.algorithmic_bytes(e, 1) for e in layer.entries)
-    ksum = sum(ktimes.values())
-    achieved = algo / (ksum * 1e-3) / 1e9
-    per_m = {}
-    for m in BATCHES:
-        t = sum(ktimes[(e["name"], m)] for e in layer.entries)
-        coded = sum(layer.algorithmic_bytes(e, m) for e in layer.entries)
-        per_m[str(m)] = {"kernel_ms": round(t, 4), "effective_bf16_GBps": round(dense / len(BATCHES) / world / t / 1e6, 1),
-                         "coded_GBps": round(coded / t / 1e6, 1), "frac_of_hbm_peak": round(coded / t / 1e6 / peak, 4),
-                         "linears_only_tok_s_64_layers": round(m / (64 * t * 1e-3), 1)}
-    top = max(ktimes, key=ktimes.get)
-    top_e = next(e for e in layer.entries if e["name"] == top[0])
-    top_bytes = layer.algorithmic_bytes(top_e, top[1])
+    algo = sum(layer.algorithmic_bytes(e, m) for m in BATCHES for e in layer.entries)     # this rank's bytes per step
+    achieved = algo / (ms * 1e-3) / 1e9
+    top_e = max(layer.entries, key=lambda e: e["res"].coded_bytes)
+    top_bytes = layer.algorithmic_bytes(top_e, max(BATCHES))
+    mhz = clock_summary["sm_mhz"]
     line = {
         "metric": METRIC, "value": round(dense / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -539,21 +641,76 @@ def run_ours(args):
                                "seed 1, fused decode-GEMM at M=1,64,128", "parallelism": f"tp{world}",
                    "l2": "coded working set ~440 MB exceeds the 126 MB L2; no flush between iterations",
                    "resident_format": "BXR1/" + args.layout, "launch": launch, "all_reduce": layer.reduce_kind, "status_word": status},
+        "timing": {"regions": len(regions), "steps_per_region": args.steps, "timed_seconds": round(sum(regions) * args.steps / 1e3, 3),
+                   "ms_per_step_median": round(ms, 4), "ms_per_step_min": round(min(regions), 4), "ms_per_step_max": round(max(regions), 4),
+                   "ms_times_sm_mhz": None if not mhz else round(ms * mhz, 1)},
         "e2e": {"value": round(dense / (ms_e2e * 1e-3) / 1e9, 2), "unit": UNIT, "ms_per_step": round(ms_e2e, 4),
                 "h2d_bytes_per_step": sum(2 * m * (HIDDEN + FFN) for m in BATCHES), "d2h_bytes_per_step": sum(2 * m * HIDDEN for m in BATCHES),
-                "launch": e2e_launch, "outputs_match_eager_path": e2e_same},
-        "gpu_launches": layer.launches_per_step * args.steps,
+                "launch": e2e_launch, "outputs_match_eager_path": e2e_same, "regions": len(e2e_regions)},
+        "gpu_launches": layer.launches_per_step * args.steps * len(regions),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": round(top_bytes * DRAM_TRAFFIC_RATIO[args.layout]), "peak_source": peak_kind,
-                     "kernel": {"window4": "bxq_kernel", "window": "bxw_kernel", "rans": "bxr_kernel"}[args.layout] + "<kUmma, NB> (all 12 launches of a step; algorithmic bytes = coded image + x + y per launch)",
-                     "top_launch": {"linear": top[0], "m": top[1], "ms": round(ktimes[top], 4), "algorithmic_bytes": top_bytes,
-                                    "GBps": round(top_bytes / ktimes[top] / 1e6, 1)}},
-        "per_m": per_m,
-        "gemv_m1": {"kernel_ms": round(gemv_ms, 4), "coded_GBps": round(gemv_bytes / gemv_ms / 1e6, 1),
-                    "frac_of_hbm_peak": round(gemv_bytes / gemv_ms / 1e6 / peak, 4),
-                    "note": "grb_bxr_gemv outside the timed step: CUDA-core kernel for the rans layout, the tensor-core kernel at its narrowest tile for the window layouts"},
-        "clocks": clocks.summary(),
+                     "algorithmic_bytes_per_step": algo,
+                     "how": "achieved = algorithmic_bytes_per_step (this rank's coded images + x + y of the 12 launches) / ms_per_step; "
+                            "traffic = DRAM bytes of the step's largest launch (gate|up at M=128): its algorithmic bytes x the "
+                            "dram read+write ratio of one ncu capture of that launch",
+                     "kernel": KERNEL_OF[args.layout] + "<kUmma, NB>, the 12 launches of a step"},
+        "clocks": clock_summary,
     }
+    # ---- outside the timed region: parity, per-launch breakdown, dense yardsticks, the other layouts
+    line["parity"] = layer.parity()
+    if tp_check is not None:
+        line["tp_parity"] = tp_check
+    ktimes = launch_times(layer)
+    per_m = {}
+    for m in BATCHES:
+        t = sum(ktimes[(e["name"], m)] for e in layer.entries) * 1e-3
+        coded = sum(layer.algorithmic_bytes(e, m) for e in layer.entries)
+        per_m[str(m)] = {"kernel_ms": round(t, 4), "effective_bf16_GBps": round(dense / len(BATCHES) / world / t / 1e6, 1),
+                         "coded_GBps": round(coded / t / 1e6, 1), "frac_of_hbm_peak": round(coded / t / 1e6 / peak, 4),
+                         "linears_only_tok_s_64_layers": round(m / (64 * t * 1e-3), 1)}
+    line["per_m"] = per_m
+    line["per_launch"] = {f"{name}:{m}": {"us": round(us, 2), "algorithmic_bytes": layer.algorithmic_bytes(next(e for e in layer.entries if e["name"] == name), m),
+                                          "frac_of_hbm_peak": round(layer.algorithmic_bytes(next(e for e in layer.entries if e["name"] == name), m) / us / 1e3 / peak, 4)}
+                          for (name, m), us in ktimes.items()}
+    top = (top_e["name"], max(BATCHES))
+    line["roofline"]["top_launch"] = {"linear": top[0], "m": top[1], "us": round(ktimes[top], 2), "algorithmic_bytes": top_bytes,
+                                      "GBps": round(top_bytes / ktimes[top] / 1e3, 1), "frac": round(top_bytes / ktimes[top] / 1e3 / peak, 4),
+                                      "how": "in a stream of such launches over rotating copies of the image"}
+    own, lib = dense_times(layer)
+    fused_m1 = {e["name"]: ktimes[(e["name"], 1)] for e in layer.entries}
+    line["dense_gemv"] = {
+        "own_kernel_us_m1": {k: round(v, 2) for k, v in own.items()}, "torch_matmul_us": {f"{k[0]}:{k[1]}": round(v, 2) for k, v in lib.items()},
+        "fused_us_m1": {k: round(v, 2) for k, v in fused_m1.items()},
+        "speedup_vs_own_gemv_m1": {k: round(own[k] / fused_m1[k], 3) for k in own},
+        "speedup_vs_own_gemv_m1_step": round(sum(own.values()) / sum(fused_m1.values()), 3),
+        "speedup_vs_torch_matmul": {str(m): round(sum(lib[(e["name"], m)] for e in layer.entries) / sum(ktimes[(e["name"], m)] for e in layer.entries), 3)
+                                    for m in BATCHES},
+        "target": "> 1.3x a dense BF16 GEMV on the same GPU",
+        "own_gemv_GBps_m1": {e["name"]: round(2 * e["words"].size / own[e["name"]] / 1e3, 1) for e in layer.entries}}
+    if world == 1 and not args.skip_layouts:
+        line["per_layout"] = {args.layout: {"value": line["value"], "ms_per_step": line["ms_per_step"], "roofline_frac": line["roofline"]["frac"],
+                                            "bytes_per_weight": round(sum(e["res"].coded_bytes for e in layer.entries) / sum(e["words"].size for e in layer.entries), 4)}}
+        del layer
+        torch.cuda.empty_cache()
+        for other in ("window4", "window", "rans"):
+            if other == args.layout:
+                continue
+            alt = Layer(rank, world, device, layout=other, weights=weights)
+            fn = alt.step if args.no_graph else capture(alt.step)
+            r, _, _ = timed_regions(fn, args.steps, args.warmup, world, min_seconds=0.2)
+            t = float(np.median(r))
+            a = sum(alt.algorithmic_bytes(e, m) for m in BATCHES for e in alt.entries)
+            gate_up = next(e for e in alt.entries if e["name"] == "gate_up")
+            us1 = launch_times_one(alt, gate_up, 1)
+            line["per_layout"][other] = {"value": round(dense / (t * 1e-3) / 1e9, 2), "ms_per_step": round(t, 4),
+                                         "roofline_frac": round(a / (t * 1e-3) / 1e9 / peak, 4),
+                                         "bytes_per_weight": round(sum(e["res"].coded_bytes for e in alt.entries) / sum(e["words"].size for e in alt.entries), 4),
+                                         "gate_up_m1_us": round(us1, 2),
+                                         "gate_up_m1_frac": round(alt.algorithmic_bytes(gate_up, 1) / us1 / 1e3 / peak, 4),
+                                         "status_word": alt.status()}
+            del alt
+            torch.cuda.empty_cache()
     if rank == 0 and world == 1:
         value, dt, info = cpu_reference_run(sample_rows=2048, steps=1, warmup=0, threads=os.cpu_count() or 1)
         line["cpu_baseline"] = {"value": round(value, 4), "unit": UNIT, **info, "seconds": round(dt, 2)}
@@ -563,93 +720,13 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_case(args):
-    """One kernel on one synthetic weight, a few launches: the command the ncu summaries under profiles/ use."""
-    import torch
+def launch_times_one(layer, e, m):
+    from georefine_b200 import tune
 
-    from georefine_b200.resident import ResidentWeight
-
-    kind, m, shape = args.case.split(":")
-    m, (n, k) = int(m), map(int, shape.lower().split("x"))
-    words = synthetic_words(torch.Generator().manual_seed(SEED), n, k)
-    if kind == "bctx":   # indexed decode of the unchanged BCTX streams; the second field is the restart stride
-        from georefine_b200 import codec
-        from georefine_b200.gpu import CudaContextTensor
-
-        t = CudaContextTensor(codec.encode(words), stride=m, device="cuda:0", fused=False)
-        ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for i in range(max(args.steps, 1)):
-            if i == max(args.steps, 1) - 1:
-                ev[0].record()
-            out = t.decode(check=False)
-        ev[1].record()
-        torch.cuda.synchronize()
-        us = ev[0].elapsed_time(ev[1]) * 1e3
-        print(json.dumps({"case": args.case, "frame_bytes": t.frame_bytes, "last_decode_us": round(us, 1),
-                          "dense_GBps": round(2 * n * k / us / 1e3, 1), "status_word": int(t.error.item())}))
-        return
-    w = ResidentWeight.from_words(words, torch.device("cuda:0"), verify=False, max_m=max(m, 8), layout=args.layout)
-    x = torch.randn(m, k, device="cuda:0").to(torch.bfloat16)
-    y = torch.empty(m, n, device="cuda:0", dtype=torch.bfloat16)
-    t0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for i in range(max(args.steps, 1)):
-        if i == max(args.steps, 1) - 1:
-            t0[0].record()
-        if kind == "decode":
-            w.decode(check=False)
-        else:
-            getattr(w, kind)(x, y)
-    t0[1].record()
-    torch.cuda.synchronize()
-    print(json.dumps({"case": args.case, "layout": args.layout, "mode": w.mode, "coded_bytes": w.coded_bytes, "last_launch_us": round(t0[0].elapsed_time(t0[1]) * 1e3, 2),
-                      "status_word": w.check_status()}))
-
-
-def run_sweep(args):
-    """Same-GPU comparison table: every benchmark shape (and the 4096 x 4096 parity shape) at M = 1, 8, 64, 128.
-    Each timing rotates over enough copies of the weight to exceed the L2 (>= 400 MB per rotation)."""
-    import torch
-
-    from georefine_b200.resident import ResidentWeight
-
-    dev = torch.device("cuda:0")
-    g = torch.Generator().manual_seed(SEED)
-
-    def timeit(fn, copies, reps):
-        for i in range(max(6, copies)):
-            fn(i % copies)
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(reps):
-            fn(i % copies)
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / reps * 1e3
-
-    for name, n, k in [(nm, n, k) for nm, n, k, _, _ in LINEARS] + [("config0", 4096, 4096)]:
-        words = synthetic_words(g, n, k)
-        res = ResidentWeight.from_words(words, dev, verify=False, max_m=128, layout=args.layout)
-        coded, dense = res.coded_bytes, 2 * n * k
-        images = [res] + [res.clone() for _ in range(max(2, -(-400_000_000 // coded)) - 1)]
-        wd = [torch.from_numpy(words.view(np.int16)).view(torch.bfloat16).to(dev)]
-        wd += [wd[0].clone() for _ in range(max(2, -(-400_000_000 // dense)) - 1)]
-        reps = max(20, int(2e9 // coded))
-        row = {"shape": name, "N": n, "K": k, "layout": args.layout, "coded_bytes": coded, "ratio": round(dense / coded, 3)}
-        for m in (1, 8, 64, 128):
-            x = torch.randn(m, k, device=dev).to(torch.bfloat16)
-            y = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-            us = timeit(lambda i: images[i].gemm(x, y), len(images), reps)
-            row[f"gemm_M{m}"] = {"us": round(us, 1), "coded_GBps": round(coded / us / 1e3), "effective_GBps": round(dense / us / 1e3)}
-            if m <= 8:
-                us = timeit(lambda i: images[i].gemv(x, y), len(images), reps)
-                row[f"gemv_M{m}"] = {"us": round(us, 1), "coded_GBps": round(coded / us / 1e3), "effective_GBps": round(dense / us / 1e3)}
-            us = timeit(lambda i: torch.matmul(x, wd[i].T, out=y), len(wd), reps)
-            row[f"torch_dense_M{m}"] = {"us": round(us, 1), "GBps": round(dense / us / 1e3)}
-        row["status_word"] = sum(im.check_status() for im in images)
-        print(json.dumps(row), flush=True)
-        del images, wd, res
-        torch.cuda.empty_cache()
+    res = e["res"]
+    copies = [res] + [res.clone() for _ in range(tune.copies_for(res.coded_bytes) - 1)]
+    x, y = layer.xv[(m, e["name"])], e["y"][m]
+    return tune.rotation_us(lambda i: copies[i].gemm(x, y), len(copies), max(20, int(1e9 // res.coded_bytes)))
 
 
 def run_reference(args):
@@ -670,22 +747,15 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
-    ap.add_argument("--sweep", action="store_true", help="per shape and batch size: fused gemm / gemv against torch.matmul on "
-                                                        "the dense weights, one JSON line per shape")
     ap.add_argument("--layout", choices=("rans", "window", "window4"), default="window4",
                     help="resident layout of the weights: fixed 4-bit window codes (default), fixed 3-bit window codes, or "
                          "entropy-coded exponent streams")
-    ap.add_argument("--case", default=None, help="profiling aid: KIND:M:NxK (KIND = gemm, gemv or decode) runs that one "
-                                                 "launch --steps times on a synthetic weight and exits")
+    ap.add_argument("--skip-layouts", action="store_true", help="do not time the other two layouts after the main run")
     args = ap.parse_args()
-    if args.case:
-        return run_case(args)
-    if args.sweep:
-        return run_sweep(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -24,7 +24,7 @@ EXPORTS = (
     "bcx_encode", "bcx_frequencies", "bcx_decode", "bcx_decode_compact", "bcx_free", "bcx_pack6", "bcx_unpack6",
     "bcx_checkpoint", "grb_bctx_build_lookup", "grb_bctx_decode_words", "bxr_build", "bxr_free", "bxr_decode_host",
     "bxr_validate", "bxr_layout_version", "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_kernel_attributes",
-    "grb_static_scratch_bytes", "grb_bxr_gemv_static", "grb_peer_control_bytes", "grb_peer_enable", "grb_peer_allreduce_bf16",
+    "grb_static_scratch_bytes", "grb_bxr_gemv_static", "grb_dense_gemv_bf16", "grb_peer_control_bytes", "grb_peer_enable", "grb_peer_allreduce_bf16",
     "grb_peer_alloc", "grb_peer_free", "grb_peer_open", "grb_peer_close",
 )
 
@@ -87,6 +87,8 @@ def _declare(lib):
     lib.grb_static_scratch_bytes.restype = u64
     lib.grb_bxr_gemv_static.argtypes = [VOIDP, ctypes.POINTER(BxrHeader), VOIDP, ctypes.c_int64, u32, VOIDP, ctypes.c_int64,
                                         VOIDP, VOIDP, VOIDP]
+    lib.grb_dense_gemv_bf16.argtypes = [VOIDP, ctypes.c_int64, u32, u32, VOIDP, ctypes.c_int64, u32, VOIDP, ctypes.c_int64,
+                                        VOIDP, VOIDP]
     lib.grb_peer_control_bytes.argtypes = []
     lib.grb_peer_control_bytes.restype = u64
     lib.grb_peer_enable.argtypes = [ci]

@@ -13,6 +13,7 @@
 #include "bxw_kernels.cuh"
 #include "bxq_kernels.cuh"
 #include "peer_reduce.cuh"
+#include "dense_gemv.cuh"
 
 namespace {
 
@@ -164,6 +165,28 @@ int gemv_m(const BxrArgs& a, cudaStream_t stream) {
   return launch<kGemv, M>(a, none, stream);
 }
 
+template <int M, bool WIDE>
+int dense_launch_as(const DenseArgs& a, uint32_t groups, uint32_t sms, cudaStream_t stream) {
+  // whole waves of resident CTAs; the CTAs walk the remaining row groups with a grid stride
+  static int resident = 0;   // per SM; the same on every device of a process (one architecture)
+  if (!resident) {
+    int n = 0;
+    const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, dense_gemv_kernel<M, WIDE>, kDenseThreads, 0);
+    if (e != cudaSuccess) return cuda_status(e);
+    resident = n > 0 ? n : 1;
+  }
+  const uint32_t ctas = std::min<uint32_t>(groups, sms * uint32_t(resident));
+  dense_gemv_kernel<M, WIDE><<<ctas, kDenseThreads, 0, stream>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
+template <int M>
+int dense_launch(const DenseArgs& a, uint32_t groups, uint32_t sms, cudaStream_t stream) {
+  // 256-bit loads need rows that start on 32-byte boundaries and a whole number of 32-byte pieces per row
+  const bool wide = (reinterpret_cast<uintptr_t>(a.w) & 31) == 0 && (a.ldw & 15) == 0 && (a.cols & 15) == 0;
+  return wide ? dense_launch_as<M, true>(a, groups, sms, stream) : dense_launch_as<M, false>(a, groups, sms, stream);
+}
+
 }  // namespace
 
 extern "C" {
@@ -289,6 +312,53 @@ int grb_bxr_gemv(const void* image, const bxr_header* h, const void* x, int64_t 
     case 6: return gemv_m<6>(a, stream);
     case 7: return gemv_m<7>(a, stream);
     default: return gemv_m<8>(a, stream);
+  }
+}
+
+// ---- dense BF16 GEMV --------------------------------------------------------------------------------
+int grb_dense_gemv_bf16(const void* w, int64_t ldw, uint32_t rows, uint32_t cols, const void* x, int64_t ldx, uint32_t m, void* y,
+                        int64_t ldy, const void* bias, void* cuda_stream) {
+  if (!w || !x || !y || !rows || !cols || !m) return GRB_ERR_ARGUMENT;
+  if (m > 8) return GRB_ERR_UNSUPPORTED;
+  if ((cols & 7) || ldw < int64_t(cols) || ldx < int64_t(cols) || ldy < int64_t(rows) || (ldw & 7) || (ldx & 7) ||
+      (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
+    return GRB_ERR_ARGUMENT;
+  static std::mutex mu;
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e);
+  if (dev < 0 || dev >= 64) return GRB_ERR_UNSUPPORTED;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!sms[dev]) {
+      e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return cuda_status(e);
+    }
+  }
+  DenseArgs a{};
+  a.w = static_cast<const __nv_bfloat16*>(w);
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.ldw = ldw;
+  a.ldx = ldx;
+  a.ldy = ldy;
+  a.rows = rows;
+  a.cols = cols;
+  a.slices = dense_slices(rows, cols, uint32_t(sms[dev]));
+  const uint32_t groups = (rows + kDenseWarps / a.slices - 1) / (kDenseWarps / a.slices);
+  const uint32_t ctas = uint32_t(sms[dev]);
+  const auto stream = static_cast<cudaStream_t>(cuda_stream);
+  switch (m) {
+    case 1: return dense_launch<1>(a, groups, ctas, stream);
+    case 2: return dense_launch<2>(a, groups, ctas, stream);
+    case 3: return dense_launch<3>(a, groups, ctas, stream);
+    case 4: return dense_launch<4>(a, groups, ctas, stream);
+    case 5: return dense_launch<5>(a, groups, ctas, stream);
+    case 6: return dense_launch<6>(a, groups, ctas, stream);
+    case 7: return dense_launch<7>(a, groups, ctas, stream);
+    default: return dense_launch<8>(a, groups, ctas, stream);
   }
 }
 

@@ -117,9 +117,18 @@ class ResidentWeight:
         self.reserve(max_m)
 
     @classmethod
-    def from_words(cls, words, device, *, source_sha256=None, max_m=128, workers=None, layout=DEFAULT_LAYOUT, force_raw=False,
-                   verify=True):
-        workers = default_workers(int(words.shape[0]), int(words.shape[1]), sm_count(device)) if workers is None else workers
+    def from_words(cls, words, device, *, source_sha256=None, max_m=128, workers=None, layout=None, force_raw=False,
+                   verify=True, tune=None):
+        """Builds the image on the host and uploads it.  ``layout`` / ``workers`` left to None come from ``tune`` (a
+        mapping {(N, K): (layout, workers)} as ``georefine_b200.tune.load_tune`` returns it) when it knows the shape,
+        else from the defaults: the 4-bit window layout and ``default_workers``."""
+        rows, cols = int(words.shape[0]), int(words.shape[1])
+        if tune and (rows, cols) in tune:
+            tuned_layout, tuned_workers = tune[(rows, cols)]
+            layout = tuned_layout if layout is None else layout
+            workers = tuned_workers if workers is None else workers
+        layout = DEFAULT_LAYOUT if layout is None else layout
+        workers = default_workers(rows, cols, sm_count(device)) if workers is None else workers
         image, _ = build_image(words, workers, layout=layout, force_raw=force_raw, source_sha256=source_sha256)
         return cls(image, device, max_m=max_m, verify=verify)
 

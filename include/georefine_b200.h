@@ -180,6 +180,16 @@ int grb_bxr_gemv(const void* device_image, const bxr_header* header, const void*
                  int64_t ldy, const void* bias, void* workspace, uint64_t workspace_bytes, uint32_t* status,
                  void* cuda_stream);
 
+/* y[m, n] = bf16( sum_k x[m, k] * W[n, k] (+ bias[n]) ) for a DENSE BF16 weight W [rows, cols] (row stride ldw), m <= 8.
+ * Replaces miv_gemv_out / linear, gs/miv_gemv.py:125-191,916-959, with its numerical contract: lanes walk 16-byte
+ * vectors in increasing k, eight FMAs per vector in element order, xor butterfly, K slices added in slice order, bias
+ * in FP32, one rounding; rows of y are bitwise independent of m (1..8).  The number of K slices depends on the shape
+ * and the SM count only.  It is the dense yardstick the fused kernels are compared with, and the linear for weights
+ * that are kept uncompressed.  cols % 8 == 0, ldw % 8 == 0, ldx % 8 == 0, W and x 16-byte aligned.  No allocation, no
+ * host synchronisation. */
+int grb_dense_gemv_bf16(const void* w, int64_t ldw, uint32_t rows, uint32_t cols, const void* x, int64_t ldx, uint32_t m,
+                        void* y, int64_t ldy, const void* bias, void* cuda_stream);
+
 /* grb_bxr_gemv without caller-provided scratch.  This entry point has no counterpart in the reference.
  *
  * It is for callers that are not in a position to allocate device memory at all: a plugin loaded into a

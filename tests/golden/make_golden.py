@@ -32,7 +32,10 @@ sys.path.insert(0, str(ROOT))
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", "/root/reference"))
+    named = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT")
+    if not named:
+        raise SystemExit("usage: make_golden.py <checkout of the reference project>   (or set REFERENCE_ROOT)")
+    ref_root = Path(named)
     os.environ["BITEXACT_CONTEXT_CACHE_DIR"] = tempfile.mkdtemp(prefix="bctx-golden-")
     sys.path.insert(0, str(ref_root / "context-runtime"))
     from georefine_context_runtime import bitexact_context_codec as ref  # noqa: E402

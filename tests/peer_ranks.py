@@ -3,7 +3,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P tests/peer_ranks.py
 
 Every rank writes a rank-dependent BF16 pattern into its slot, all ranks reduce, every rank checks the result against
-the sum computed locally in rank order (bit-exact), eagerly and replayed from a CUDA graph, then times the call."""
+the sum computed locally in rank order (bit-exact), eagerly and replayed from a CUDA graph, and a row-parallel linear
+summed this way is compared with the product of the whole weight."""
 import os
 import sys
 
@@ -78,38 +79,11 @@ def main():
     if red2.check_status():
         failures += 1
     red2.close()
-    # timing: eager calls, large and small
-    timing = {}
-    for name in ("small", "large"):
-        rows, cols = shapes[name]
-        out = torch.empty(rows, cols, dtype=torch.bfloat16, device=device)
-        for _ in range(5):
-            red.reduce(name, out)
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(50):
-            red.reduce(name, out)
-        e1.record()
-        torch.cuda.synchronize()
-        timing[name] = e0.elapsed_time(e1) / 50 * 1e3
-        y = torch.empty(rows, cols, dtype=torch.bfloat16, device=device)
-        for _ in range(5):
-            dist.all_reduce(y)
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(50):
-            dist.all_reduce(y)
-        e1.record()
-        torch.cuda.synchronize()
-        timing[name + "_nccl"] = e0.elapsed_time(e1) / 50 * 1e3
     status = red.check_status()
     bad = torch.tensor([failures + (1 if status else 0)], device=device)
     dist.all_reduce(bad)
     if rank == 0:
-        print(f"peer all-reduce: world {world}, failures {int(bad.item())}, status {status}, us per call: "
-              + ", ".join(f"{k} {v:.1f}" for k, v in timing.items()), flush=True)
+        print(f"peer all-reduce: world {world}, failures {int(bad.item())}, status {status}", flush=True)
     red.close()
     dist.barrier()
     dist.destroy_process_group()
