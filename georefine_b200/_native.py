@@ -23,7 +23,7 @@ VOIDP = ctypes.c_void_p
 EXPORTS = (
     "bcx_encode", "bcx_frequencies", "bcx_decode", "bcx_decode_compact", "bcx_free", "bcx_pack6", "bcx_unpack6",
     "bcx_checkpoint", "grb_bctx_build_lookup", "grb_bctx_decode_words", "bxr_build", "bxr_free", "bxr_decode_host",
-    "bxr_validate", "bxr_layout_version", "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_kernel_attributes",
+    "bxr_validate", "bxr_layout_version", "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_bxr_gemm_next", "grb_kernel_attributes",
     "grb_static_scratch_bytes", "grb_bxr_gemv_static", "grb_dense_gemv_bf16", "grb_peer_control_bytes", "grb_peer_enable", "grb_peer_allreduce_bf16",
     "grb_peer_alloc", "grb_peer_free", "grb_peer_open", "grb_peer_close",
 )
@@ -82,6 +82,7 @@ def _declare(lib):
               VOIDP, VOIDP]
     lib.grb_bxr_gemm.argtypes = linear
     lib.grb_bxr_gemv.argtypes = linear
+    lib.grb_bxr_gemm_next.argtypes = linear + [VOIDP, ctypes.POINTER(BxrHeader)]
     lib.grb_kernel_attributes.argtypes = [ci, ctypes.POINTER(ci * 5)]
     lib.grb_static_scratch_bytes.argtypes = []
     lib.grb_static_scratch_bytes.restype = u64

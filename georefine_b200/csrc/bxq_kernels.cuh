@@ -27,6 +27,7 @@ constexpr int kWideWarpEpilogue = 20;  // 4 warps: warp % 4 = the tensor-memory 
 // at NB = 128 there is room for one, and the issuers wait for the drain at an item boundary while the decoders fill
 // the operand stages.  Columns [256, 512): the decoded weights of kWideStages chunks, 64 columns each (two 128 x 64
 // atoms, two BF16 per column).
+constexpr int kWideNextBlobs = 8;      // blobs per CTA of the next launch that a finishing CTA asks the L2 for
 constexpr uint32_t kWideTmemCols = 512;
 constexpr uint32_t kWideOperandCol = 256;
 constexpr int kWideStages = 4;
@@ -104,6 +105,19 @@ __device__ __forceinline__ void bxq_patch(uint32_t (&out)[16], uint32_t column, 
 #pragma unroll
   for (int i = 0; i < 16; ++i)
     if (reg == uint32_t(i)) out[i] = (out[i] & ~(0x7F80u << sh)) | (exponent & 0xFFu) << (7 + sh);
+}
+
+// The work of a CTA is a contiguous range of the (row block, chunk) sequence; an item is the part of it that lies in
+// one row block.  Everything but the epilogue needs only the geometry of an item, which follows from the range by
+// arithmetic: no load stands between the start of a CTA and its first blob, window base and multiply.  (The item
+// list in the image holds the same geometry plus the partial-tile bookkeeping - part, parts, slot - which the
+// epilogue reads with plenty of time to spare; bxr_validate checks that the two agree.)
+struct WideSpan {
+  uint32_t row_block, chunk_begin, chunk_end;
+};
+__device__ __forceinline__ WideSpan wide_span(uint32_t unit, uint32_t unit_end, uint32_t chunks) {
+  const uint32_t rb = unit / chunks, c0 = unit - rb * chunks;
+  return {rb, c0, min(chunks, c0 + (unit_end - unit))};
 }
 
 // The closing reduction of a split row block, by the (kDecoderWarps + 4) x 32 threads that have nothing else left
@@ -199,6 +213,57 @@ __device__ __forceinline__ void bxq_reduce_row_block(const BxrArgs& args, const 
   }
 }
 
+// The closing reduction of a row block whose parts belong to the CTAs of one thread-block cluster (the partition is
+// "aligned": workers = row blocks x P, CTA rank r of cluster b owns part r of row block b, in K order).  Every CTA has
+// left its FP32 tile at the start of its shared memory; after the cluster barrier each CTA adds the P tiles of ITS share
+// of the batch columns (m = rank, rank + P, ...) in rank order - its own from local shared memory, the others over
+// distributed shared memory - and writes y.  No partial tile goes to global memory, no counter, no fence, and the work
+// of the reduction is spread over the P SMs.  t = index of the calling thread among the (kDecoderWarps + 4) x 32.
+template <int NB>
+__device__ __forceinline__ void bxq_reduce_in_cluster(const BxrArgs& args, uint32_t row_block, uint32_t smem, uint32_t t) {
+  constexpr uint32_t kThreads = (kDecoderWarps + 4) * 32;
+  const uint32_t parts = args.cluster, rank = cluster_rank();
+  const uint32_t mcols = (args.m + 7) & ~7u;
+  const uint32_t mine = rank < mcols ? (mcols - rank + parts - 1) / parts : 0;  // batch columns rank, rank + P, ... below mcols
+  for (uint32_t i = t; i < mine * 32; i += kThreads) {
+    const uint32_t m = rank + (i >> 5) * parts, at = (m << 5) | (i & 31);
+    const uint32_t row4 = row_block * BXR_ROWS + (i & 31) * 4;
+    if (m >= args.m || row4 >= args.rows) continue;
+    uint4 u[8];  // every part's piece first (independent loads in flight), then the sum in K order
+#pragma unroll
+    for (uint32_t p = 0; p < 8; ++p)
+      if (p < parts) u[p] = p == rank ? lds128(smem + at * 16) : lds128_cluster(cluster_map(smem + at * 16, p));
+    // part 0 is taken as it is: adding it to zero would lose the sign of a -0
+    float f[4] = {__uint_as_float(u[0].x), __uint_as_float(u[0].y), __uint_as_float(u[0].z), __uint_as_float(u[0].w)};
+#pragma unroll
+    for (uint32_t p = 1; p < 8; ++p)
+      if (p < parts) {
+        f[0] = __fadd_rn(f[0], __uint_as_float(u[p].x));
+        f[1] = __fadd_rn(f[1], __uint_as_float(u[p].y));
+        f[2] = __fadd_rn(f[2], __uint_as_float(u[p].z));
+        f[3] = __fadd_rn(f[3], __uint_as_float(u[p].w));
+      }
+    if (args.bias)
+      for (int k = 0; k < 4; ++k)
+        if (row4 + k < args.rows) f[k] = __fadd_rn(f[k], __bfloat162float(args.bias[row4 + k]));
+    __nv_bfloat16* dst = args.y + size_t(m) * args.ldy + row4;
+    if (row4 + 3 < args.rows && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+      __nv_bfloat162 lo, hi;
+      lo.x = __float2bfloat16_rn(f[0]);
+      lo.y = __float2bfloat16_rn(f[1]);
+      hi.x = __float2bfloat16_rn(f[2]);
+      hi.y = __float2bfloat16_rn(f[3]);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = packed;
+    } else {
+      for (int k = 0; k < 4; ++k)
+        if (row4 + k < args.rows) dst[k] = __float2bfloat16_rn(f[k]);
+    }
+  }
+}
+
 template <int MODE, int NB>
 __global__ void __launch_bounds__(MODE == kUmma ? kThreadsUmma : kThreadsSimt, 1)
 bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
@@ -224,6 +289,13 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   constexpr uint32_t kXN = L::kX ? L::kX : 1;
   constexpr uint32_t kAccBufs = NB <= 64 ? 2 : 1;  // items whose accumulators fit tensor memory at once
 
+  // The blob loader's own barriers first of all (blobs of one size: it needs nothing else to start its copies): their
+  // fences complete while the CTA's share of the work is being computed.
+  if (warp == kWideWarpLoader && args.blob_stride16 && lane == 0) {
+    for (uint32_t n = 0; n < uint32_t(L::kIn); ++n) mbar_init(bar_in_full + 8 * n, 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
   // Work of this CTA, known from the arguments alone; the blob loader asks for its first offsets before anything
   // else so that the first copy can leave as soon as the barriers exist.
   const uint64_t units = uint64_t(args.row_blocks) * args.chunks;
@@ -235,12 +307,16 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     first_i0 = __ldg(args.blob_index + mine);
     first_i1 = __ldg(args.blob_index + mine + 1);
   }
-  // The CTA's item list and its first item: asked for now, needed after the set-up.
-  const uint32_t item_begin = __ldg(args.worker_items + worker), item_end = __ldg(args.worker_items + worker + 1);
-  bxr_item first_item = {};
-  if (item_begin < item_end) first_item = args.items[item_begin];
-  uint32_t first_base = 0;  // decoders: the window base of this thread's row in the first item
-  if (warp < kDecoderWarps && item_begin < item_end) first_base = args.base[first_item.row_block * BXR_ROWS + (warp & 3) * 32 + lane];
+  const uint32_t unit_end = unit_begin + unit_count;
+  // Decoders: the window base of this thread's row in the CTA's first item, asked for before anything else.
+  uint32_t first_base = 0;
+  if (warp < kDecoderWarps && unit_count) first_base = args.base[(unit_begin / args.chunks) * BXR_ROWS + (warp & 3) * 32 + lane];
+  // Epilogue: where the CTA's items are in the image's list (their partial-tile bookkeeping); needed much later.
+  uint32_t item_begin = 0, item_end = 0;
+  if (MODE == kUmma && warp >= kWideWarpEpilogue) {
+    item_begin = __ldg(args.worker_items + worker);
+    item_end = __ldg(args.worker_items + worker + 1);
+  }
   // An SM runs the launches of a stream back to back, so whatever a CTA does before its first multiply is not hidden
   // behind the previous launch on the SM that finished last.  The longest wait in it is the first blob's trip from
   // HBM: with blobs of one size the loader needs nothing but its own barriers to start it, and sets those up itself.
@@ -249,9 +325,6 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t bytes = args.blob_stride16 << 4;
     if (bytes <= BXQ_BLOB_MAX && bytes >= BXQ_LIST_AT) early = min(unit_count, uint32_t(L::kIn));
     if (lane == 0) {
-      for (uint32_t n = 0; n < uint32_t(L::kIn); ++n) mbar_init(bar_in_full + 8 * n, 1);
-      mbar_fence_init();
-      fence_proxy_async_smem();
       const uint64_t once = l2_policy_evict_first();
       for (uint32_t u = 0; u < early; ++u) {
         mbar_arrive_expect_tx(bar_in_full + 8 * u, bytes);
@@ -307,10 +380,13 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     // this lane's 16 operand columns: lane = row, columns = its 32 weights inside the chunk's atom
     const uint32_t operand_at = ((rg * 32u) << 16) + kWideOperandCol + (q >> 1) * 32 + (q & 1) * 16;
     bool live = true;
-    for (uint32_t it = item_begin; it < item_end && live; ++it) {
-      const bxr_item item = it == item_begin ? first_item : args.items[it];
+    uint32_t next_base = first_base;
+    for (uint32_t u = unit_begin; u < unit_end && live;) {
+      const WideSpan item = wide_span(u, unit_end, args.chunks);
+      u += item.chunk_end - item.chunk_begin;
       const uint32_t row = item.row_block * BXR_ROWS + r;
-      const uint32_t base2 = uint32_t(it == item_begin ? first_base : args.base[row]) * 0x00800080u;
+      const uint32_t base2 = next_base * 0x00800080u;
+      if (u < unit_end) next_base = args.base[row + BXR_ROWS];  // the next item's base: on its way while this item is decoded
       for (uint32_t c = item.chunk_begin; c < item.chunk_end; ++c) {
         if (!ctx.wait(bar_in_full + 8 * s, ph)) { live = false; break; }
         const uint32_t blob = smem + L::in + s * BXQ_BLOB_MAX;
@@ -394,6 +470,17 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       }
       if (!live) break;
     }
+    // Every load of this CTA is on its way: from here on it asks HBM for nothing.  Ask the L2 for what the next launch
+    // of the stream will want first - the leading blobs of its CTAs w, w + workers, ... (consecutive in memory) - so
+    // that they arrive during this launch's tail and the next launch's set-up.
+    if (MODE == kUmma && args.next_blobs && lane == 0 && !ctx.aborted()) {
+      for (uint32_t w2 = worker; w2 < args.next_workers; w2 += args.workers) {
+        const uint32_t b0 = uint32_t(uint64_t(args.next_units) * w2 / args.next_workers);
+        const uint32_t b1 = uint32_t(uint64_t(args.next_units) * (w2 + 1) / args.next_workers);
+        const uint32_t n = min(b1 - b0, uint32_t(kWideNextBlobs));
+        for (uint32_t b = 0; b < n; ++b) bulk_prefetch_l2(args.next_blobs + size_t(b0 + b) * args.next_blob_bytes, args.next_blob_bytes);
+      }
+    }
     // after an abort: give copies still in flight a bounded time to land before the CTA exits
     if (ctx.aborted() && lane == 0)
       for (uint32_t u = (issued > uint32_t(L::kIn) ? issued - L::kIn : 0); u < issued; ++u) mbar_wait(bar_in_full + 8 * (u % L::kIn), (u / L::kIn) & 1);
@@ -409,9 +496,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       grid_dependency_wait();
       const uint64_t stay = l2_policy_evict_last();  // every CTA reads the same activation tiles
       bool live = true;
-      uint32_t it_v = item_begin, c_v = 0;  // cursor of the chunk to request: item and chunk inside it
-      bxr_item item_v = first_item;
-      c_v = item_v.chunk_begin;
+      uint32_t c_v = unit_begin % args.chunks;  // the chunk (column block) to request next: wraps at the end of a row block
       auto multiplied = [&](uint32_t c) { return ctx.wait(bar_op_empty + 8 * (c % kOpN), (c / kOpN) & 1); };
       for (uint32_t v = 0; v < unit_count + L::kXLag && live; ++v) {
         if (ctx.aborted()) break;
@@ -428,10 +513,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           mbar_arrive_expect_tx(bar_x_full + 8 * sx, L::kXStage);
           tma_load_2d(stage, &tmap_x, int(c_v * BXR_COLS), 0, bar_x_full + 8 * sx, stay);
           tma_load_2d(stage + NB * 128, &tmap_x, int(c_v * BXR_COLS + 64), 0, bar_x_full + 8 * sx, stay);
-          if (++c_v == item_v.chunk_end && it_v + 1 < item_end) {
-            item_v = args.items[++it_v];
-            c_v = item_v.chunk_begin;
-          }
+          if (++c_v == args.chunks) c_v = 0;
         }
       }
     }
@@ -444,8 +526,9 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t which = warp == kWideWarpMma2 ? 1u : 0u;
     uint32_t n_item = 0, so = 0, pho = 0, sx = 0;
     bool live = true;
-    for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
-      const bxr_item item = it == item_begin ? first_item : args.items[it];
+    for (uint32_t u = unit_begin; u < unit_end && live; ++n_item) {
+      const WideSpan item = wide_span(u, unit_end, args.chunks);
+      u += item.chunk_end - item.chunk_begin;
       const uint32_t buf = n_item % kAccBufs, use = n_item / kAccBufs;
       if (ctx.aborted() || !ctx.wait(bar_acc_empty + 8 * buf, (use & 1) ^ 1)) { live = false; break; }
       tc_fence_after();
@@ -485,8 +568,10 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     bool live = true, early_taken = false;
     const uint64_t stay = l2_policy_evict_last();  // partial tiles are read back within the launch
     grid_dependency_wait();  // bias, y, partial tiles and counters may belong to the previous kernel
+    bxr_item item = {};
+    if (item_begin < item_end) item = args.items[item_begin];
     for (uint32_t it = item_begin; it < item_end && live; ++it, ++n_item) {
-      const bxr_item item = it == item_begin ? first_item : args.items[it];
+      if (it != item_begin) item = args.items[it];
       const uint32_t buf = n_item % kAccBufs, use = n_item / kAccBufs;
       if (ctx.aborted() || !ctx.wait(bar_acc_full + 8 * buf, use & 1)) { live = false; break; }
       tc_fence_after();
@@ -500,10 +585,11 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       // the usual case, they were finished long ago as some CTA's first item - this tile never goes to memory at
       // all: no store, no fence, no counter update on the tail of the kernel.
       const bool final_item = it + 1 == item_end;
-      const bool keep = item.parts > 1 && final_item;
+      const bool in_cluster = args.cluster > 1;  // the CTA's one item is a part of its cluster's row block
+      const bool keep = item.parts > 1 && (final_item || in_cluster);
       const uint32_t tile = smem;           // [batch row][128 weight rows] FP32, like a partial tile in memory
       uint32_t arrived = 0;
-      if (keep && e == 0 && lane == 0) arrived = ld_relaxed_gpu(args.counters + item.row_block);  // answer used after the drain; fenced there
+      if (keep && !in_cluster && e == 0 && lane == 0) arrived = ld_relaxed_gpu(args.counters + item.row_block);  // answer used after the drain; fenced there
       // A lane holds one weight row and kStep batch columns; y and the partial tiles keep the rows of one batch
       // column together.  Stored from the registers that is one narrow store instruction per column, and the
       // store queue, not the memory, sets the pace (a 128-column drain took 4 400 to 10 000 cycles).  So the
@@ -568,7 +654,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
-      if (item.parts > 1) {
+      if (item.parts > 1 && !in_cluster) {
         // `prev` = how many tiles of the row block were in memory before this one; the CTA that completes the set
         // reduces it.  Flag words: misc + 8 and misc + 12.
         uint32_t prev;
@@ -621,9 +707,23 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     if (lane == 0) mbar_arrive(bar_final);
   }
 
+  if (MODE == kUmma && args.cluster > 1) {
+    // One cluster per row block: every CTA's tile is in its shared memory once its epilogue is through; the cluster
+    // barrier makes the tiles visible to the peers, the second one keeps every CTA's shared memory alive until the
+    // peers have read it.  Every thread of every CTA gets here on every path (all other waits are bounded).
+    const bool worker_thread = warp < kDecoderWarps || warp >= kWideWarpEpilogue;
+    const bool drained = worker_thread ? ctx.wait(bar_final, 0) : true;
+    __syncwarp();
+    cluster_sync();
+    if (worker_thread && drained && unit_count)
+      bxq_reduce_in_cluster<NB>(args, unit_begin / args.chunks, smem, (warp < kDecoderWarps ? warp : warp - 4) * 32 + lane);
+    __syncwarp();
+    cluster_sync();
+  }
+
   // Row blocks whose last partial tile came from this CTA are reduced by the 16 decoder warps and the 4 epilogue
   // warps together, once the epilogue has drained the CTA's last item.
-  if (MODE == kUmma && (warp < kDecoderWarps || warp >= kWideWarpEpilogue)) {
+  if (MODE == kUmma && args.cluster <= 1 && (warp < kDecoderWarps || warp >= kWideWarpEpilogue)) {
     if (ctx.wait(bar_final, 0)) {
       uint32_t fetched = 0;  // tiles brought in so far: position in the two-buffer ring
 #pragma unroll 1

@@ -73,6 +73,12 @@ struct BxrArgs {
   uint32_t* counters;          // [row_blocks], zero between calls
   uint16_t* dense;             // kDense: rows x cols words
   uint32_t* status;
+  uint32_t cluster;            // bxq_kernel: > 1 = launched as clusters of this many CTAs, one cluster per row block
+  // bxq_kernel, optional: the image the NEXT launch in the stream will read (blobs of one size).  A CTA whose own
+  // loads have all been issued asks the L2 for the first blobs of the next launch's CTAs, so that HBM keeps working
+  // through this launch's tail and the next launch's prologue.
+  const uint8_t* next_blobs;
+  uint32_t next_blob_bytes, next_units, next_workers;
 };
 
 template <int MODE, int NB>

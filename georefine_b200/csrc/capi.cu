@@ -59,7 +59,7 @@ BxrArgs view_of(const void* image, const bxr_header* h) {
 // Programmatic stream serialisation: the kernel may begin (table and blob loads, decoding) while the tail of the
 // previous kernel in the stream is still running; it waits in-kernel before touching x, y or the scratch.
 template <auto Kernel, uint32_t kSmemBytes, int kThreads>
-int launch_fused(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {
+int launch_fused(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream, uint32_t cluster = 1) {
   static std::mutex mu;
   static bool done[64] = {false};
   int dev = 0;
@@ -78,12 +78,27 @@ int launch_fused(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream)
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster > 1) {  // consecutive CTAs form a thread-block cluster (the grid is a multiple of it)
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+  }
   return cuda_status(cudaLaunchKernelEx(&cfg, Kernel, a, tmap));
+}
+
+// Aligned partitions - workers = row blocks x P with 2 <= P <= 8 - run the 4-bit window kernel as one thread-block
+// cluster of P CTAs per row block: the K parts of a row block are then added over distributed shared memory.
+uint32_t cluster_of(const BxrArgs& a) {
+  if (!a.window4 || a.workers % a.row_blocks) return 1;
+  const uint32_t p = a.workers / a.row_blocks;
+  return (p >= 2 && p <= 8 && a.chunks >= p) ? p : 1;
 }
 
 template <int MODE>
@@ -98,8 +113,9 @@ int launch_window(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream
   return launch_fused<bxw_kernel<MODE, NB>, BxwSmem<MODE, NB>::alloc, kFusedThreads<MODE>>(a, tmap, stream);
 }
 template <int MODE, int NB>
-int launch_wide(const BxrArgs& a, const CUtensorMap& tmap, cudaStream_t stream) {  // 4-bit window images
-  return launch_fused<bxq_kernel<MODE, NB>, BxqSmem<MODE, NB>::alloc, kFusedThreads<MODE>>(a, tmap, stream);
+int launch_wide(BxrArgs a, const CUtensorMap& tmap, cudaStream_t stream) {  // 4-bit window images
+  a.cluster = MODE == kUmma ? cluster_of(a) : 1;
+  return launch_fused<bxq_kernel<MODE, NB>, BxqSmem<MODE, NB>::alloc, kFusedThreads<MODE>>(a, tmap, stream, a.cluster);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -257,6 +273,12 @@ static int check_linear(const void* image, const bxr_header* h, const void* x, i
 
 int grb_bxr_gemm(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
                  const void* bias, void* ws, uint64_t ws_bytes, uint32_t* status, void* cuda_stream) {
+  return grb_bxr_gemm_next(image, h, x, ldx, m, y, ldy, bias, ws, ws_bytes, status, cuda_stream, nullptr, nullptr);
+}
+
+int grb_bxr_gemm_next(const void* image, const bxr_header* h, const void* x, int64_t ldx, uint32_t m, void* y, int64_t ldy,
+                      const void* bias, void* ws, uint64_t ws_bytes, uint32_t* status, void* cuda_stream, const void* next_image,
+                      const bxr_header* next_header) {
   const uint32_t tile = batch_tile(m > 128 ? 128 : m);
   int st = check_linear(image, h, x, ldx, m, y, ldy, ws, ws_bytes, status, tile);
   if (st) return st;
@@ -268,6 +290,13 @@ int grb_bxr_gemm(const void* image, const bxr_header* h, const void* x, int64_t 
   a.status = status;
   a.ldx = ldx;
   a.ldy = ldy;
+  // The hint is used where it is cheap to follow: both images in the 4-bit window layout with blobs of one size.
+  if (next_image && header_ok(next_header) && a.window4 && next_header->mode == BXR_MODE_WINDOW4 && next_header->blob_stride16) {
+    a.next_blobs = static_cast<const uint8_t*>(next_image) + next_header->blobs_at;
+    a.next_blob_bytes = next_header->blob_stride16 << 4;
+    a.next_units = next_header->row_blocks * next_header->chunks;
+    a.next_workers = next_header->workers;
+  }
   // Batches above one tile are processed as consecutive tiles: one pass over the weights per 128 rows.
   for (uint32_t m0 = 0; m0 < m; m0 += 128) {
     a.m = m - m0 < 128 ? m - m0 : 128;

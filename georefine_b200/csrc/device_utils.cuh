@@ -119,6 +119,10 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
       "l"(tmap), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Hint: bring [src, src + bytes) into the L2 (16-byte aligned, a multiple of 16 bytes); nothing waits for it.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 // 1-D bulk copy shared -> global (same alignment rules), tracked by the issuing thread's bulk group; the wait
 // returns once the group's writes are complete.
 __device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
@@ -260,6 +264,30 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t n) {
 // has completed and its memory is visible.  Both are no-ops for a launch without the attribute.
 __device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---- thread-block clusters --------------------------------------------------------------------------
+// Barrier over every thread of every CTA of the cluster.  Arrival releases what the thread wrote (its own shared
+// memory included), the wait acquires what the others released: after it a CTA may read its peers' shared memory.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address of `local` (a shared address of this CTA) in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ uint4 lds128_cluster(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");

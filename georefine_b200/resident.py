@@ -114,6 +114,7 @@ class ResidentWeight:
         self.status = torch.zeros(1, device=self.device, dtype=torch.int32)
         self.max_m = 0
         self.workspace = None
+        self.next_weight = None     # see then()
         self.reserve(max_m)
 
     @classmethod
@@ -140,6 +141,7 @@ class ResidentWeight:
         other.image = self.image.clone()
         other.status = self.status.clone()
         other.workspace = self.workspace.clone()
+        other.next_weight = None
         return other
 
     # -- bookkeeping (the numerators of the roofline) ----------------------------------------------------
@@ -194,7 +196,7 @@ class ResidentWeight:
             raise ValueError(f"resident decode reported status {self.status.item()}")
         return out
 
-    def _run(self, entry, x, y, bias):
+    def _run(self, entry, x, y, bias, extra=()):
         import torch
 
         if x.dim() != 2 or y.dim() != 2 or x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16:
@@ -208,7 +210,7 @@ class ResidentWeight:
             raise ValueError(f"batch of {m} rows exceeds the reserved scratch ({self.max_m}); call reserve() first")
         args = (self.image.data_ptr(), ctypes.byref(self.header), x.data_ptr(), x.stride(0), m, y.data_ptr(), y.stride(0),
                 None if bias is None else bias.data_ptr(), self.workspace.data_ptr(), self.workspace.numel(),
-                self.status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream)
+                self.status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream, *extra)
         if torch.cuda.current_device() == self.device.index:   # the usual case: skip the device switch
             st = entry(*args)
         else:
@@ -217,9 +219,20 @@ class ResidentWeight:
         if st:
             _native.check(st, entry.__name__)
 
+    def then(self, next_weight):
+        """Tells this weight which one the stream multiplies by next (None: nobody).  A hint for the kernel: while a
+        launch over this weight winds down, the L2 is asked for the first blobs of the next one.  Returns
+        ``next_weight`` so that a layer can be chained in one line: ``qkv.then(o).then(gate_up).then(down)``."""
+        self.next_weight = next_weight
+        return next_weight
+
     def gemm(self, x, y, bias=None):
         """tcgen05 path, any M; rows of y are bitwise independent of M."""
-        self._run(_native.lib().grb_bxr_gemm, x, y, bias)
+        nxt = self.next_weight
+        if nxt is None:
+            self._run(_native.lib().grb_bxr_gemm, x, y, bias)
+        else:
+            self._run(_native.lib().grb_bxr_gemm_next, x, y, bias, extra=(nxt.image.data_ptr(), ctypes.byref(nxt.header)))
 
     def gemv(self, x, y, bias=None):
         """CUDA-core path, M <= 8; rows of y are bitwise independent of M within 1..8."""

@@ -77,11 +77,20 @@ def copies_for(nbytes: int) -> int:
     return max(2, -(-ROTATION_BYTES // max(int(nbytes), 1)))
 
 
+def chained_copies(weight: "resident.ResidentWeight"):
+    """Enough copies of the image to exceed the L2 in one rotation, each told that the next one follows it (the hint a
+    serving engine gives with ``then``)."""
+    copies = [weight.clone() for _ in range(copies_for(weight.coded_bytes))]
+    for a, b in zip(copies, copies[1:] + copies[:1]):
+        a.then(b)
+    return copies
+
+
 def time_weight(weight: "resident.ResidentWeight", m: int, *, reps: int | None = None, entry: str = "gemm", copies=None) -> float:
     """Microseconds per fused launch at batch m, in a stream of such launches over rotating copies of the image."""
     import torch
 
-    images = copies if copies is not None else [weight] + [weight.clone() for _ in range(copies_for(weight.coded_bytes) - 1)]
+    images = copies if copies is not None else chained_copies(weight)
     x = torch.randn(m, weight.K, device=weight.device).to(torch.bfloat16)
     y = torch.empty(m, weight.N, device=weight.device, dtype=torch.bfloat16)
     reps = reps or max(20, int(2e9 // weight.coded_bytes))
@@ -101,7 +110,7 @@ def tune_shape(rows: int, cols: int, device, *, ms=(1, 64, 128), layouts=(reside
         for w in (worker_candidates(rows, cols, sms) if workers is None else workers):
             res = resident.ResidentWeight.from_words(words, device, max_m=max(ms), workers=w, layout=layout, verify=False)
             built = {v: k for k, v in resident.LAYOUTS.items()}[res.mode]
-            copies = [res] + [res.clone() for _ in range(copies_for(res.coded_bytes) - 1)]
+            copies = chained_copies(res)
             total = 0.0
             for m in ms:
                 us = time_weight(res, m, reps=reps, copies=copies)

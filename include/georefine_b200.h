@@ -180,6 +180,15 @@ int grb_bxr_gemv(const void* device_image, const bxr_header* header, const void*
                  int64_t ldy, const void* bias, void* workspace, uint64_t workspace_bytes, uint32_t* status,
                  void* cuda_stream);
 
+/* grb_bxr_gemm with a hint: next_image / next_header name the resident image the NEXT fused launch of the same stream
+ * will read (the order of the linears of a decoder layer is fixed, so an engine knows it; the reference's engine fixes
+ * the same order when it captures a whole decode step, gs/fastdec.py:706-956).  CTAs that have issued their last load
+ * ask the L2 for the first blobs of the next launch, so that HBM keeps working through this launch's tail and the next
+ * launch's set-up.  Only a hint: results do not depend on it; NULL (or an image in another layout) means no hint. */
+int grb_bxr_gemm_next(const void* device_image, const bxr_header* header, const void* x, int64_t ldx, uint32_t m, void* y,
+                      int64_t ldy, const void* bias, void* workspace, uint64_t workspace_bytes, uint32_t* status,
+                      void* cuda_stream, const void* next_device_image, const bxr_header* next_header);
+
 /* y[m, n] = bf16( sum_k x[m, k] * W[n, k] (+ bias[n]) ) for a DENSE BF16 weight W [rows, cols] (row stride ldw), m <= 8.
  * Replaces miv_gemv_out / linear, gs/miv_gemv.py:125-191,916-959, with its numerical contract: lanes walk 16-byte
  * vectors in increasing k, eight FMAs per vector in element order, xor butterfly, K slices added in slice order, bias

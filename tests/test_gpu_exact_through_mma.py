@@ -134,3 +134,38 @@ def test_split_row_blocks_and_uneven_blobs_stay_exact(orc, dev, layout):
         r = _resident(words, dev, layout, workers=7)
         assert r.header.mode == 3 and r.header.blob_stride16 == 0
         _assert_same_words(_columns_through_the_product(r, words, 64, dev), words)
+
+
+@pytest.mark.parametrize("parts", [2, 3, 4, 5, 8])
+def test_row_blocks_reduced_inside_a_thread_block_cluster(orc, dev, parts):
+    """An aligned partition (workers = row blocks x P, 2 <= P <= 8) runs the 4-bit window kernel as one cluster of P CTAs
+    per row block, whose partial tiles are added over distributed shared memory instead of through global memory.  The
+    words must come through exactly, the order of additions must be the K order of the other path (same bits as an
+    image cut for one CTA per row block would give only up to rounding, so the comparison is with FP32 arithmetic), and
+    rows must not depend on the batch size."""
+    from georefine_b200.resident import ResidentWeight
+
+    words = exceptions_in_every_decoder_warp(orc, 300, 2048, 21)       # 3 row blocks (the last one ragged), 16 chunks
+    r = ResidentWeight.from_words(words, dev, layout="window4", workers=3 * parts, max_m=256)
+    assert r.mode == 3 and r.header.workers == 3 * parts and r.header.partial_slots == 3 * parts
+    for m in TILES:
+        _assert_same_words(_columns_through_the_product(r, words, m, dev), words)
+    g = torch.Generator().manual_seed(parts)
+    x = torch.randn(200, 2048, generator=g).to(torch.bfloat16).to(dev)
+    bias = torch.randn(300, generator=g).to(torch.bfloat16).to(dev)
+    w = torch.from_numpy(words.view(np.int16)).view(torch.bfloat16).to(dev).float()
+    ref = x.float() @ w.T + bias.float()
+    rows = {}
+    for m in (1, 5, 16, 64, 128, 200):
+        y = torch.full((m, 300), float("nan"), device=dev, dtype=torch.bfloat16)
+        r.gemm(x[:m].contiguous(), y, bias)
+        assert r.check_status() == 0
+        assert float((y.float() - ref[:m]).abs().max()) <= 1e-2 * float(ref.abs().max())
+        rows[m] = y.view(torch.int16).cpu().numpy()
+    assert all(np.array_equal(v, rows[200][:m]) for m, v in rows.items())
+    # the same weight cut for a worker count that is no multiple of the row blocks takes the other path (partial tiles in
+    # global memory): same K order inside a row block only when the cuts coincide, so compare to rounding
+    other = ResidentWeight.from_words(words, dev, layout="window4", workers=3 * parts + 1, max_m=256)
+    y2 = torch.empty(200, 300, device=dev, dtype=torch.bfloat16)
+    other.gemm(x, y2, bias)
+    assert float((y2.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max())

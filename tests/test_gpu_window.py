@@ -186,3 +186,26 @@ def test_wide_window_images_with_blobs_of_different_sizes(orc, dev):
     y1 = uneven.linear(x64[:1])
     assert torch.equal(y1.view(torch.int16), y64[:1].view(torch.int16))   # rows do not depend on the batch size
     assert uneven.check_status() == 0
+
+
+def test_next_weight_hint_changes_nothing_but_the_timing(orc, dev):
+    """`then()` tells a weight which image the stream reads next; the kernel uses it for an L2 prefetch only."""
+    from georefine_b200.resident import ResidentWeight
+
+    a = ResidentWeight.from_words(orc.synthetic_weight_words(512, 1024, 51), dev, layout="window4")
+    b = ResidentWeight.from_words(orc.synthetic_weight_words(640, 512, 52), dev, layout="window4")
+    c = ResidentWeight.from_words(orc.synthetic_weight_words(256, 640, 53), dev, layout="window")     # other layout: hint ignored
+    x = torch.randn(64, 1024, device=dev).to(torch.bfloat16)
+    plain = [torch.empty(64, 512, device=dev, dtype=torch.bfloat16), torch.empty(64, 640, device=dev, dtype=torch.bfloat16),
+             torch.empty(64, 256, device=dev, dtype=torch.bfloat16)]
+    a(x, plain[0]); b(plain[0], plain[1]); c(plain[1], plain[2])
+    assert a.then(b) is b and b.then(c) is c and c.then(a) is a
+    hinted = [torch.empty_like(t) for t in plain]
+    for _ in range(3):
+        a(x, hinted[0]); b(hinted[0], hinted[1]); c(hinted[1], hinted[2])
+    torch.cuda.synchronize()
+    assert all(torch.equal(p.view(torch.int16), h.view(torch.int16)) for p, h in zip(plain, hinted))
+    assert a.check_status() == 0 and b.check_status() == 0 and c.check_status() == 0
+    a.then(None)
+    a(x, hinted[0])
+    assert torch.equal(plain[0].view(torch.int16), hinted[0].view(torch.int16))
