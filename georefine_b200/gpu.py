@@ -23,24 +23,33 @@ def _p(a, t):
     return a.ctypes.data_as(ctypes.POINTER(t))
 
 
-def checkpoints(stream, freq, rows, columns, shape, nr, nc, stride, main=None):
-    """(states, offsets, symbols) of one stream: the decoder state and byte offset before every stride-th symbol."""
-    n = math.prod(shape)
+def _walk_stream(stream, table, row_class, col_class, shape, nr, nc, stride, conditioning):
+    """One serial pass of the host coder over a stream (``bcx_checkpoint``): the symbols, and the decoder's state and
+    byte offset in front of every ``stride``-th symbol.  ``conditioning`` = the main symbols when the stream is the
+    conditional residual stream, else None."""
+    rows, cols = shape
+    count = rows * cols
+    blocks = -(-count // stride)
+    states, offsets = np.empty(blocks, dtype=np.uint32), np.empty(blocks, dtype=np.uint32)
+    symbols = np.empty(count, dtype=np.uint16)
     data = np.frombuffer(bytes(stream), dtype=np.uint8).copy() if len(stream) else np.zeros(1, dtype=np.uint8)
-    states = np.empty((n + stride - 1) // stride, dtype=np.uint32)
-    offsets = np.empty_like(states)
-    out = np.empty(n, dtype=np.uint16)
-    freq = np.ascontiguousarray(freq, dtype="<u4")
-    rows = np.ascontiguousarray(rows, dtype=np.uint8)
-    columns = np.ascontiguousarray(columns, dtype=np.uint8)
-    context = _native.U16P() if main is None else _p(np.ascontiguousarray(main, dtype=np.uint16), ctypes.c_uint16)
-    status = _native.lib().bcx_checkpoint(_p(data, ctypes.c_uint8), len(stream), n, *shape, _p(rows, ctypes.c_uint8),
-                                          _p(columns, ctypes.c_uint8), nr, nc, int(main is not None), context,
-                                          _p(freq, ctypes.c_uint32), stride, _p(states, ctypes.c_uint32),
-                                          _p(offsets, ctypes.c_uint32), _p(out, ctypes.c_uint16))
+    table = np.ascontiguousarray(table, dtype="<u4")
+    row_class = np.ascontiguousarray(row_class, dtype=np.uint8)
+    col_class = np.ascontiguousarray(col_class, dtype=np.uint8)
+    kind = 0 if conditioning is None else 1
+    context = _native.U16P() if conditioning is None else _p(np.ascontiguousarray(conditioning, dtype=np.uint16), ctypes.c_uint16)
+    status = _native.lib().bcx_checkpoint(_p(data, ctypes.c_uint8), len(stream), count, rows, cols, _p(row_class, ctypes.c_uint8),
+                                          _p(col_class, ctypes.c_uint8), nr, nc, kind, context, _p(table, ctypes.c_uint32), stride,
+                                          _p(states, ctypes.c_uint32), _p(offsets, ctypes.c_uint32), _p(symbols, ctypes.c_uint16))
     if status:
         raise base.CodecError(f"checkpoint validation failed ({status})")
-    return states, offsets, out
+    return states, offsets, symbols
+
+
+def checkpoints(stream, freq, rows, columns, shape, nr, nc, stride, main=None):
+    """(states, offsets, symbols) of one stream, under the name and argument order of the reference's helper
+    (bitexact_context_gpu.py:51-63)."""
+    return _walk_stream(stream, freq, rows, columns, tuple(shape), nr, nc, stride, main)
 
 
 def index_frame(frame: bytes, stride: int = 1024, *, keep_words: bool = False):
@@ -110,25 +119,22 @@ class CudaContextTensor:
 
         if not torch.cuda.is_available():
             raise RuntimeError("CUDA is required")
-        indexed = index_frame(frame, stride, keep_words=fused)
-        self.shape = indexed["shape"]
-        self.n = math.prod(self.shape)
-        self.stride = stride
-        self.mode, self.nr, self.nc = indexed["mode"], indexed["nr"], indexed["nc"]
-        self.source_sha256 = indexed["source_sha256"]
-        self.frame_sha256 = indexed["frame_sha256"]
-        self.frame_bytes = indexed["frame_bytes"]
         self.device = torch.device(device)
-        self.buffers = {}
+        self.stride = stride
+        indexed = index_frame(frame, stride, keep_words=fused)
         words = indexed.pop("words", None)
-        for name, array in indexed.items():
-            if isinstance(array, np.ndarray):
-                self.buffers[name] = torch.from_numpy(array).to(self.device)
-        for name in ("main", "residual"):
-            if name + "_freq" in indexed:
-                cum, bucket = _lookup_tables(indexed[name + "_freq"])
-                self.buffers[name + "_cum"] = torch.from_numpy(cum).to(self.device)
-                self.buffers[name + "_bucket"] = torch.from_numpy(bucket).to(self.device)
+        # identity and geometry, as the loader checks them (bitexact_context_serving.py:560-569)
+        for name in ("shape", "mode", "nr", "nc", "source_sha256", "frame_sha256", "frame_bytes"):
+            setattr(self, name, indexed[name])
+        self.n = math.prod(self.shape)
+        # every array of the index goes to the device under its own name; coded streams get their lookup tables
+        self.buffers = {name: torch.from_numpy(array).to(self.device) for name, array in indexed.items() if isinstance(array, np.ndarray)}
+        for kind in ("main", "residual"):
+            table = indexed.get(kind + "_freq")
+            if table is not None:
+                cum, bucket = _lookup_tables(table)
+                self.buffers[kind + "_cum"] = torch.from_numpy(cum).to(self.device)
+                self.buffers[kind + "_bucket"] = torch.from_numpy(bucket).to(self.device)
         self.error = torch.zeros((), device=self.device, dtype=torch.int32)
         self.resident = None
         if fused and words is not None:
@@ -182,18 +188,24 @@ class CudaContextTensor:
         return self._decode_blocks(check=check)[:self.n].reshape(self.shape)
 
     def gather_rows(self, ids, *, check=True):
+        """Rows ``ids`` (any shape) as BF16 [..., cols].  When a row is a whole number of restart blocks only the blocks of
+        the requested rows are decoded; otherwise (raw frames, strides that do not divide the row) the tensor is decoded
+        once and indexed."""
         import torch
 
+        rows, cols = self.shape
         ids = ids.to(device=self.device, dtype=torch.int64)
         if ids.numel() == 0:
-            return torch.empty((*ids.shape, self.shape[1]), device=self.device, dtype=torch.bfloat16)
-        if torch.any((ids < 0) | (ids >= self.shape[0])).item():
+            return torch.empty((*ids.shape, cols), device=self.device, dtype=torch.bfloat16)
+        lowest, highest = torch.aminmax(ids)
+        if int(lowest) < 0 or int(highest) >= rows:
             raise IndexError("embedding row outside tensor")
-        if self.mode == 1 or self.shape[1] % self.stride:
+        blocks_per_row, ragged = divmod(cols, self.stride)
+        if self.mode == 1 or ragged:
             return self.decode(check=check)[ids]
-        per_row = self.shape[1] // self.stride
-        blocks = (ids.reshape(-1, 1) * per_row + torch.arange(per_row, device=self.device)).reshape(-1)
-        return self._decode_blocks(blocks, check=check).reshape(*ids.shape, self.shape[1])
+        first_block = ids.reshape(-1, 1) * blocks_per_row
+        wanted = (first_block + torch.arange(blocks_per_row, device=self.device)).reshape(-1)
+        return self._decode_blocks(wanted, check=check).reshape(*ids.shape, cols)
 
     # -- fused linear --------------------------------------------------------------------------------
     def linear(self, x, out=None, bias=None):
