@@ -26,6 +26,7 @@ EXPORTS = (
     "bxr_validate", "bxr_layout_version", "grb_bxr_workspace_bytes", "grb_bxr_decode", "grb_bxr_gemm", "grb_bxr_gemv", "grb_bxr_gemm_next", "grb_kernel_attributes",
     "grb_static_scratch_bytes", "grb_bxr_gemv_static", "grb_dense_gemv_bf16", "grb_peer_control_bytes", "grb_peer_enable", "grb_peer_allreduce_bf16",
     "grb_peer_alloc", "grb_peer_free", "grb_peer_open", "grb_peer_close",
+    "grb_rmsnorm_bf16", "grb_silu_mul_bf16", "grb_argmax_bf16", "grb_attn_decode_bf16",
 )
 
 
@@ -53,6 +54,14 @@ class BctxTensor(ctypes.Structure):
                 ("main_states", VOIDP), ("main_offsets", VOIDP), ("main_cum", VOIDP), ("main_bucket", VOIDP),
                 ("residual_stream", VOIDP), ("residual_bytes", ctypes.c_uint64), ("residual_states", VOIDP),
                 ("residual_offsets", VOIDP), ("residual_cum", VOIDP), ("residual_bucket", VOIDP)]
+
+
+class AttnStep(ctypes.Structure):
+    _fields_ = [("qkv", VOIDP), ("ldq", ctypes.c_int64), ("cos_table", VOIDP), ("sin_table", VOIDP), ("row_seq", VOIDP),
+                ("row_pos", VOIDP), ("page_table", VOIDP), ("max_pages", ctypes.c_uint32), ("k_pages", VOIDP), ("v_pages", VOIDP),
+                ("q", VOIDP), ("part_acc", VOIDP), ("part_ml", VOIDP), ("out", VOIDP), ("rows", ctypes.c_uint32),
+                ("nq", ctypes.c_uint32), ("nkv", ctypes.c_uint32), ("head_dim", ctypes.c_uint32), ("max_splits", ctypes.c_uint32),
+                ("scaling", ctypes.c_float)]
 
 
 def _declare(lib):
@@ -90,6 +99,11 @@ def _declare(lib):
                                         VOIDP, VOIDP, VOIDP]
     lib.grb_dense_gemv_bf16.argtypes = [VOIDP, ctypes.c_int64, u32, u32, VOIDP, ctypes.c_int64, u32, VOIDP, ctypes.c_int64,
                                         VOIDP, VOIDP]
+    lib.grb_rmsnorm_bf16.argtypes = [VOIDP, ctypes.c_int64, VOIDP, ctypes.c_int64, VOIDP, VOIDP, ctypes.c_int64, u32, u32,
+                                     ctypes.c_float, ci, VOIDP]
+    lib.grb_silu_mul_bf16.argtypes = [VOIDP, ctypes.c_int64, VOIDP, ctypes.c_int64, u32, u32, VOIDP]
+    lib.grb_argmax_bf16.argtypes = [VOIDP, ctypes.c_int64, u32, u32, VOIDP, VOIDP]
+    lib.grb_attn_decode_bf16.argtypes = [ctypes.POINTER(AttnStep), VOIDP]
     lib.grb_peer_control_bytes.argtypes = []
     lib.grb_peer_control_bytes.restype = u64
     lib.grb_peer_enable.argtypes = [ci]

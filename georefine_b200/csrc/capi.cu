@@ -14,6 +14,7 @@
 #include "bxq_kernels.cuh"
 #include "peer_reduce.cuh"
 #include "dense_gemv.cuh"
+#include "decode_ops.cuh"
 
 namespace {
 
@@ -203,6 +204,12 @@ int dense_launch(const DenseArgs& a, uint32_t groups, uint32_t sms, cudaStream_t
   return wide ? dense_launch_as<M, true>(a, groups, sms, stream) : dense_launch_as<M, false>(a, groups, sms, stream);
 }
 
+template <int G>
+int attn_split_launch(const AttnArgs& a, cudaStream_t stream) {
+  attn_split_kernel<G><<<dim3(a.max_splits, a.nkv, a.rows), kAttnThreads, 0, stream>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
 }  // namespace
 
 extern "C" {
@@ -389,6 +396,85 @@ int grb_dense_gemv_bf16(const void* w, int64_t ldw, uint32_t rows, uint32_t cols
     case 7: return dense_launch<7>(a, groups, ctas, stream);
     default: return dense_launch<8>(a, groups, ctas, stream);
   }
+}
+
+// ---- decode-step kernels around the fused linears --------------------------------------------------------
+int grb_rmsnorm_bf16(void* h, int64_t ldh, const void* delta, int64_t ldd, const void* weight, void* out, int64_t ldo, uint32_t rows,
+                     uint32_t hidden, float eps, int unit_offset, void* cuda_stream) {
+  if (!h || !weight || !out || !rows || !hidden) return GRB_ERR_ARGUMENT;
+  if ((hidden & 7) || hidden > uint32_t(kRmsThreads * kRmsVectors * 8) || ldh < int64_t(hidden) || ldo < int64_t(hidden) || (ldh & 7) ||
+      (ldo & 7) || (delta && (ldd < int64_t(hidden) || (ldd & 7))))
+    return GRB_ERR_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(delta)) & 15)
+    return GRB_ERR_ARGUMENT;
+  rmsnorm_kernel<<<rows, kRmsThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<__nv_bfloat16*>(h), ldh, static_cast<const __nv_bfloat16*>(delta), ldd, static_cast<const __nv_bfloat16*>(weight),
+      static_cast<__nv_bfloat16*>(out), ldo, hidden, eps, unit_offset);
+  return cuda_status(cudaGetLastError());
+}
+
+int grb_silu_mul_bf16(const void* gate_up, int64_t ldg, void* out, int64_t ldo, uint32_t rows, uint32_t f, void* cuda_stream) {
+  if (!gate_up || !out || !rows || !f || (f & 7) || ldg < 2 * int64_t(f) || ldo < int64_t(f) || (ldg & 7) || (ldo & 7)) return GRB_ERR_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) return GRB_ERR_ARGUMENT;
+  if (rows > 65535) return GRB_ERR_UNSUPPORTED;
+  silu_mul_kernel<<<dim3(((f >> 3) + 255) / 256, rows), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), ldg, static_cast<__nv_bfloat16*>(out), ldo, f);
+  return cuda_status(cudaGetLastError());
+}
+
+int grb_argmax_bf16(const void* logits, int64_t ld, uint32_t rows, uint32_t vocab, int32_t* out, void* cuda_stream) {
+  if (!logits || !out || !rows || !vocab || ld < int64_t(vocab) || (ld & 7) || (reinterpret_cast<uintptr_t>(logits) & 15)) return GRB_ERR_ARGUMENT;
+  argmax_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab, out);
+  return cuda_status(cudaGetLastError());
+}
+
+int grb_attn_decode_bf16(const grb_attn_step* s, void* cuda_stream) {
+  if (!s || !s->qkv || !s->cos_table || !s->sin_table || !s->row_seq || !s->row_pos || !s->page_table || !s->k_pages || !s->v_pages ||
+      !s->q || !s->part_acc || !s->part_ml || !s->out)
+    return GRB_ERR_ARGUMENT;
+  if (!s->rows || !s->nq || !s->nkv || !s->max_pages || !s->max_splits || s->nq % s->nkv || s->head_dim != uint32_t(kAttnDim))
+    return GRB_ERR_ARGUMENT;
+  if (s->ldq < int64_t(s->nq + 2 * s->nkv) * kAttnDim || (s->ldq & 7) ||
+      ((reinterpret_cast<uintptr_t>(s->qkv) | reinterpret_cast<uintptr_t>(s->q) | reinterpret_cast<uintptr_t>(s->k_pages) |
+        reinterpret_cast<uintptr_t>(s->v_pages) | reinterpret_cast<uintptr_t>(s->part_acc)) & 15))
+    return GRB_ERR_ARGUMENT;
+  if (s->rows > 65535 || s->nq + 2 * s->nkv > 65535 || s->max_splits > s->max_pages) return GRB_ERR_UNSUPPORTED;
+  AttnArgs a{};
+  a.qkv = static_cast<const __nv_bfloat16*>(s->qkv);
+  a.ldq = s->ldq;
+  a.cos_table = static_cast<const __nv_bfloat16*>(s->cos_table);
+  a.sin_table = static_cast<const __nv_bfloat16*>(s->sin_table);
+  a.row_seq = s->row_seq;
+  a.row_pos = s->row_pos;
+  a.page_table = s->page_table;
+  a.max_pages = s->max_pages;
+  a.k_pages = static_cast<__nv_bfloat16*>(s->k_pages);
+  a.v_pages = static_cast<__nv_bfloat16*>(s->v_pages);
+  a.q = static_cast<__nv_bfloat16*>(s->q);
+  a.part_acc = s->part_acc;
+  a.part_ml = s->part_ml;
+  a.out = static_cast<__nv_bfloat16*>(s->out);
+  a.rows = s->rows;
+  a.nq = s->nq;
+  a.nkv = s->nkv;
+  a.max_splits = s->max_splits;
+  a.scaling = s->scaling;
+  const auto stream = static_cast<cudaStream_t>(cuda_stream);
+  attn_prep_kernel<<<dim3(a.rows, a.nq + 2 * a.nkv), kAttnDim, 0, stream>>>(a);
+  int st = cuda_status(cudaGetLastError());
+  if (st) return st;
+  switch (a.nq / a.nkv) {
+    case 1: st = attn_split_launch<1>(a, stream); break;
+    case 2: st = attn_split_launch<2>(a, stream); break;
+    case 4: st = attn_split_launch<4>(a, stream); break;
+    case 5: st = attn_split_launch<5>(a, stream); break;
+    case 8: st = attn_split_launch<8>(a, stream); break;
+    default: return GRB_ERR_UNSUPPORTED;
+  }
+  if (st) return st;
+  attn_combine_kernel<<<dim3(a.rows, a.nq), kAttnDim, 0, stream>>>(a);
+  return cuda_status(cudaGetLastError());
 }
 
 // ---- allocation-free variant ----------------------------------------------------------------------

@@ -270,6 +270,50 @@ int grb_peer_close(void* ptr);
 int grb_peer_allreduce_bf16(const void* partial, void* const* receives, void* const* controls, uint64_t block_bytes, uint32_t rank,
                             uint32_t world, void* out, uint64_t elems, uint64_t wait_limit_ns, uint32_t* status, void* cuda_stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * 5. The other kernels of a batched decode step (everything between the fused linears).  BF16 in and out, FP32
+ *    arithmetic, every row computed by CTAs of its own in a fixed order, so a row does not depend on the batch it is in.
+ *    No allocation, no host synchronisation.
+ * ------------------------------------------------------------------------------------------------- */
+
+/* Replaces rmsnorm_kernel, gs/fastdec_kernels.cu:83-110.  If delta: h = bf16(h + delta), written back (the residual
+ * add).  out = bf16(h * rsqrt(mean(h^2) + eps) * (unit_offset ? 1 + weight : weight)).  hidden % 8 == 0, <= 16384. */
+int grb_rmsnorm_bf16(void* h, int64_t ldh, const void* delta, int64_t ldd, const void* weight, void* out, int64_t ldo,
+                     uint32_t rows, uint32_t hidden, float eps, int unit_offset, void* cuda_stream);
+
+/* Replaces silu_mul_kernel, gs/fastdec_kernels.cu:451-459: out[r, i] = bf16(bf16(silu(gate_up[r, i])) * gate_up[r, f + i]). */
+int grb_silu_mul_bf16(const void* gate_up, int64_t ldg, void* out, int64_t ldo, uint32_t rows, uint32_t f, void* cuda_stream);
+
+/* Replaces argmax_kernel, gs/fastdec_kernels.cu:462-488: index of the first maximum of every row. */
+int grb_argmax_bf16(const void* logits, int64_t ld, uint32_t rows, uint32_t vocab, int32_t* out, void* cuda_stream);
+
+/* One attention step over a paged KV cache: rotary embedding of the query and key heads and the append of keys and
+ * values at each row's position, then decode attention in splits of 256 positions merged in split order.  Replaces
+ * attn_prep / attn_split / attn_combine, gs/fastdec_kernels.cu:324-448, and their batched twins with a page table
+ * (gs/bidec.py:71-81).  Plain grouped-query attention with head dimension 128: no per-head norm, no output gate.
+ * Row r is position row_pos[r] of the sequence in slot row_seq[r]; several rows of one sequence at consecutive
+ * positions (a prompt chunk, a speculative verify) are handled in one call: all appends happen before any read.
+ * A page holds 256 positions of one sequence as [kv head][256][128]; page_table[slot * max_pages + p / 256] names it. */
+typedef struct grb_attn_step {
+  const void* qkv;            /* BF16 [rows][ldq]: nq query heads | nkv key heads | nkv value heads */
+  int64_t ldq;
+  const void* cos_table;      /* BF16 [positions][128] (second half repeats the first, the rotate-half convention) */
+  const void* sin_table;
+  const int32_t* row_seq;     /* [rows] */
+  const int32_t* row_pos;     /* [rows] */
+  const int32_t* page_table;  /* [slots][max_pages] */
+  uint32_t max_pages;
+  void* k_pages;              /* BF16 [pages][nkv][256][128] */
+  void* v_pages;
+  void* q;                    /* scratch: BF16 [rows][nq][128] */
+  float* part_acc;            /* scratch: [rows][nq][max_splits][128] */
+  float* part_ml;             /* scratch: [rows][nq][max_splits][2] */
+  void* out;                  /* BF16 [rows][nq * 128] */
+  uint32_t rows, nq, nkv, head_dim, max_splits;   /* head_dim must be 128; nq / nkv in {1, 2, 4, 5, 8} */
+  float scaling;              /* 1 / sqrt(head_dim) */
+} grb_attn_step;
+int grb_attn_decode_bf16(const grb_attn_step* step, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif
