@@ -739,6 +739,101 @@ def launch_times_one(layer, e, m):
     return tune.rotation_us(lambda i: copies[i].gemm(x, y), len(copies), max(20, int(1e9 // res.coded_bytes)))
 
 
+def run_decode(args):
+    """Whole-stack decode throughput (BASELINE.json configs 2 and 3): the 64-layer random-init decoder (hidden 5120, 40
+    query / 8 KV heads x 128, FFN 17408, vocabulary 152064) with compressed weights, continuous batching at the given
+    numbers of concurrent sequences, a 2048-token context per sequence and 128 generated tokens, from random token IDs.
+    The context's KV entries are synthetic (random pages written directly: processing 128 x 2048 prompt tokens would
+    take longer than the measurement and is not what the configuration times); every timed step is the engine's real
+    step - embedding, 64 x (norm, QKV, rotary + append, paged attention, O, norm, gate|up, SwiGLU, down), final norm,
+    output head, arg-max, device-side advance - replayed from one CUDA graph.  Layers beyond --distinct-layers reuse
+    device copies of the first ones (the same bytes stream from HBM; building 64 distinct layers on the host takes
+    minutes).  One JSON line: tok/s per configuration, with the weight and KV bytes a step streams."""
+    import torch
+
+    from georefine_b200 import serve
+
+    _deadline(1500)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = serve.DecoderConfig(layers=args.layers)
+    t0 = time.time()
+    weights = serve.DecoderWeights.synthetic(cfg, dev, seed=SEED, distinct_layers=args.distinct_layers, max_m=128)
+    build_s = time.time() - t0
+    seqs = [int(v) for v in args.seqs.split(",")]
+    context, generate, k = 2048, 128, 5
+    spec_rows = max(seqs) * (k + 1)
+    d = serve.BatchDecoder(weights, max_rows=spec_rows if args.spec else max(seqs), max_slots=max(seqs), max_context=context + generate + 2 * k + 2, device=dev)
+    for part in d.kv.view(-1, d.kv.shape[-3] * d.kv.shape[-2] * d.kv.shape[-1]).split(4096):
+        part.uniform_(-0.5, 0.5)                                   # a synthetic context in every page
+    peak, peak_kind = measured_hbm_peak()
+    g = torch.Generator().manual_seed(SEED)
+    line = {"metric": "decode_tokens_per_second", "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{cfg.layers}-layer decoder hidden={cfg.hidden} heads={cfg.heads}/{cfg.kv_heads}x{cfg.head_dim} ffn={cfg.ffn} "
+                                   f"vocab={cfg.vocab}, {context}-token context, {generate} generated tokens, random token IDs",
+                       "distinct_layers": weights.notes["distinct_layers"], "resident_format": "BXR1/window4", "launch": "cuda_graph per row bucket",
+                       "host_build_seconds": round(build_s, 1)},
+            "weight_bytes_per_step": weights.streamed_bytes(), "results": {}}
+    clocks = ClockSampler(0).start()
+    for n in seqs:
+        b = serve.Batcher(d)
+        for _ in range(n):                                         # admit n sequences whose context is already "in the cache"
+            slot = d.open_slot()
+            d.ensure_pages(slot, context + generate + 2 * k + 1)
+            b.active[slot] = {"pos": context, "tokens": [int(torch.randint(0, cfg.vocab, (1,), generator=g))]}
+        b._dirty = True
+        for _ in range(3):                                         # warm-up steps (captures the bucket's graph)
+            b.step(fetch=False)
+        b.sync_tokens()
+        for s in b.active.values():
+            s["pos"], s["tokens"] = context, s["tokens"][-1:]
+        b._dirty = True
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_begin = time.monotonic()
+        e0.record()
+        for _ in range(generate):
+            b.step(fetch=False)
+        e1.record()
+        torch.cuda.synchronize()
+        t_end = time.monotonic()
+        ms = e0.elapsed_time(e1) / generate
+        mean_context = context + generate / 2
+        kv = d.streamed_bytes([mean_context] * n)["kv"]
+        res = {"ms_per_step": round(ms, 3), "tok_s": round(n / (ms * 1e-3), 1), "kv_bytes_per_step": int(kv),
+               "streamed_GBps": round((kv + weights.streamed_bytes()) / (ms * 1e-3) / 1e9, 1),
+               "frac_of_hbm_peak": round((kv + weights.streamed_bytes()) / (ms * 1e-3) / 1e9 / peak, 4),
+               "status_word": sum(w.check_status() for w in weights.linears()), "clocks": clocks.summary(t_begin, t_end)}
+        if args.spec:                                              # config 3: exact speculation, k = 5, verify pass at n x 6 rows
+            b.sync_tokens()
+            for s in b.active.values():
+                s["pos"], s["tokens"] = context, s["tokens"][-1:]
+            cycles, emitted = 12, 0
+            rnd = lambda: {slot: torch.randint(0, cfg.vocab, (k,), generator=g).tolist() for slot in b.active}
+            b.verify(rnd())                                        # warm-up (captures the verify graph)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(cycles):
+                emitted += sum(len(v) for v in b.verify(rnd()).values())
+            e1.record()
+            torch.cuda.synchronize()
+            cyc = e0.elapsed_time(e1) / cycles
+            res["speculation_k5"] = {"rows_per_verify_pass": n * (k + 1), "ms_per_cycle": round(cyc, 3), "drafts": "random token IDs",
+                                     "tokens_per_cycle_per_sequence": round(emitted / cycles / n, 3),
+                                     "tok_s_random_drafts": round(emitted / cycles / (cyc * 1e-3), 1),
+                                     "tok_s_if_every_draft_were_accepted": round(n * (k + 1) / (cyc * 1e-3), 1),
+                                     "cycle_over_plain_step": round(cyc / ms, 3)}
+        line["results"][str(n)] = res
+        for slot in list(b.active):
+            b.retire(slot)
+    clocks.stop()
+    line["value"] = line["results"][str(max(seqs))]["tok_s"]
+    line["peak_hbm_GBps"] = peak
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
@@ -765,10 +860,18 @@ def main():
                     help="resident layout of the weights: fixed 4-bit window codes (default), fixed 3-bit window codes, or "
                          "entropy-coded exponent streams")
     ap.add_argument("--skip-layouts", action="store_true", help="do not time the other two layouts after the main run")
+    ap.add_argument("--workload", choices=("linears", "decode"), default="linears",
+                    help="linears: the fused decode-GEMM step (the headline metric); decode: whole-stack tokens per second")
+    ap.add_argument("--seqs", default="64,128", help="decode workload: concurrent sequences, comma separated")
+    ap.add_argument("--layers", type=int, default=64, help="decode workload: decoder layers")
+    ap.add_argument("--distinct-layers", type=int, default=2, help="decode workload: layers built on the host (the rest are device copies)")
+    ap.add_argument("--spec", action="store_true", help="decode workload: also time exact speculation (k = 5, verify at 6 rows per sequence)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_ours(args)
 

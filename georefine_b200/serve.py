@@ -315,6 +315,7 @@ class Batcher:
         if not ids:
             raise ValueError("empty prompt")
         d = self.d
+        self.sync_tokens()                    # the row buffers are about to be reused for the prompt
         slot = d.open_slot()
         d.ensure_pages(slot, len(ids))
         first = None
@@ -328,9 +329,22 @@ class Batcher:
         return slot
 
     def retire(self, slot: int) -> None:
+        self.sync_tokens()
         self.d.close_slot(slot)
         del self.active[slot]
         self._dirty = True
+
+    def sync_tokens(self) -> None:
+        """After steps taken with ``fetch=False``: reads the pending input token of every row back from the device (it is
+        the last token the sequence generated) and puts it in the place of the trailing ``None`` of its token list.
+        Tokens of earlier unfetched steps stay unknown on the host."""
+        rows = [s for s in self._order if s in self.active and self.active[s]["tokens"] and self.active[s]["tokens"][-1] is None]
+        if not rows:
+            return
+        pending = self.d.tokens[:len(self._order)].tolist()
+        for i, s in enumerate(self._order):
+            if s in self.active and self.active[s]["tokens"][-1] is None:
+                self.active[s]["tokens"][-1] = int(pending[i])
 
     def step(self, *, fetch: bool = True):
         """One token for every active sequence.  Returns {slot: token} (``fetch=False``: nothing is read back, the
@@ -345,6 +359,7 @@ class Batcher:
         for slot, s in self.active.items():
             d.ensure_pages(slot, s["pos"])
         if self._dirty:
+            self.sync_tokens()
             self._order = sorted(self.active)
             pad = b - n
             d.set_rows(self._order + [d.pad_slot] * pad, [self.active[s]["pos"] for s in self._order] + [0] * pad,
@@ -370,6 +385,7 @@ class Batcher:
         arg-max rows and emits one more token.  Returns {slot: emitted tokens}; positions are rewound by bookkeeping
         alone (the surplus KV entries are overwritten by the next pass)."""
         d = self.d
+        self.sync_tokens()
         slots, positions, tokens = [], [], []
         for slot, ds in drafts.items():
             s = self.active[slot]
