@@ -534,6 +534,68 @@ def dense_times(layer):
     return own, lib
 
 
+def indexed_decode_times(device):
+    """Decode of UNCHANGED BCTX streams on the GPU (what an embedding gather and ``CudaContextTensor.decode`` run): the
+    configuration-0 matrix (4096 x 4096, seed 0) through this library's kernel and - when the reference's own modules
+    have been staged under baseline/_ref/ - through the reference's Triton kernels followed by F.linear at M = 1, the
+    reference's simple path on the same GPU."""
+    import torch
+    import torch.nn.functional as F
+
+    from georefine_b200 import codec
+    from georefine_b200.gpu import CudaContextTensor
+
+    words = synthetic_words(torch.Generator().manual_seed(0), 4096, 4096)
+    frame = codec.encode(words)
+    x = torch.randn(1, 4096, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(device)
+
+    def timed_us(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    out = {"matrix": "4096x4096 seed 0", "frame_bytes": len(frame)}
+    for stride in (1024, 128):
+        t = CudaContextTensor(frame, stride=stride, device=device, fused=False)
+        ok = bool(np.array_equal(t.decode().view(torch.int16).cpu().numpy().view(np.uint16), words))
+        us = timed_us(lambda: t.decode(check=False))
+        out[f"bctx_decode_kernel_stride{stride}"] = {"us": round(us, 1), "dense_GBps": round(2 * words.size / us / 1e3, 1), "bit_exact": ok}
+        if stride == 1024:
+            us = timed_us(lambda: F.linear(x, t.decode(check=False)))
+            out["decode_plus_linear_m1_us"] = round(us, 1)
+        del t
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "georefine_context_runtime" / "bitexact_context_gpu.py").is_file():
+        out["reference_triton"] = {"unavailable": "the reference's modules are not staged under baseline/_ref"}
+        return out
+    try:
+        import importlib
+        import tempfile
+
+        os.environ.setdefault("BITEXACT_CONTEXT_CACHE_DIR", tempfile.mkdtemp(prefix="bctx-ref-"))
+        sys.path.insert(0, str(ref_root))
+        ref_gpu = importlib.import_module("georefine_context_runtime.bitexact_context_gpu")
+        t = ref_gpu.CudaContextTensor(frame, stride=1024, device=str(device))
+        ok = bool(np.array_equal(t.decode().view(torch.int16).cpu().numpy().view(np.uint16), words))
+        us_decode = timed_us(lambda: t.decode(check=False), reps=3)
+        us_both = timed_us(lambda: F.linear(x, t.decode()), reps=3)          # the reference's BctxLinear.forward, check included
+        out["reference_triton"] = {"decode_us": round(us_decode, 1), "decode_plus_linear_m1_us": round(us_both, 1),
+                                   "dense_GBps": round(2 * words.size / us_decode / 1e3, 1), "bit_exact": ok,
+                                   "what": "the reference's CudaContextTensor.decode() (Triton decode_words) + F.linear, unmodified, stride 1024"}
+    except Exception as exc:  # noqa: BLE001
+        out["reference_triton"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+    finally:
+        if str(ref_root) in sys.path:
+            sys.path.remove(str(ref_root))
+    return out
+
+
 def capture(step, eager_steps=2):
     """The step as one CUDA graph (the entry points neither allocate nor synchronise)."""
     import torch
@@ -719,6 +781,25 @@ def run_ours(args):
                                          "status_word": alt.status()}
             del alt
             torch.cuda.empty_cache()
+    if world == 1 and rank == 0:
+        line["indexed_decode"] = indexed_decode_times(device)
+        fused_c0 = None
+        try:
+            from georefine_b200 import tune as _tune
+
+            fused_c0 = _tune.tune_shape(4096, 4096, device, ms=(1,), workers=[128], reps=200, log=lambda m: None,
+                                        words=synthetic_words(torch.Generator().manual_seed(0), 4096, 4096))["us"]["window4,128,M1"]
+        except Exception:  # noqa: BLE001
+            pass
+        line["indexed_decode"]["fused_linear_m1_us"] = fused_c0
+    if world == 1 and not args.skip_decode:
+        # the other half of the headline metric: whole-stack decode tokens per second at 1, 64 and 128 concurrent sequences
+        torch.cuda.empty_cache()
+        rec = decode_measurement(device, [1, 64, 128], generate=32)
+        line["decode"] = {"tok_s": {n: r["tok_s"] for n, r in rec["results"].items()}, "ms_per_step": {n: r["ms_per_step"] for n, r in rec["results"].items()},
+                          "weight_bytes_per_step": rec["weight_bytes_per_step"], "kv_bytes_per_step": {n: r["kv_bytes_per_step"] for n, r in rec["results"].items()},
+                          "frac_of_hbm_peak": {n: r["frac_of_hbm_peak"] for n, r in rec["results"].items()}, "config": rec["config"],
+                          "generated_tokens_timed": 32, "status_word": sum(r["status_word"] for r in rec["results"].values())}
     if rank == 0 and world == 1:
         value, dt, info = cpu_reference_run(sample_rows=2048, steps=1, warmup=0, threads=os.cpu_count() or 1)
         line["cpu_baseline"] = {"value": round(value, 4), "unit": UNIT, **info, "seconds": round(dt, 2)}
@@ -751,21 +832,29 @@ def run_decode(args):
     minutes).  One JSON line: tok/s per configuration, with the weight and KV bytes a step streams."""
     import torch
 
-    from georefine_b200 import serve
-
     _deadline(1500)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    cfg = serve.DecoderConfig(layers=args.layers)
+    line = decode_measurement(dev, [int(v) for v in args.seqs.split(",")], layers=args.layers, distinct_layers=args.distinct_layers,
+                              spec=args.spec, generate=128)
+    print(json.dumps(line), flush=True)
+
+
+def decode_measurement(dev, seqs, *, layers=64, distinct_layers=2, spec=False, generate=128):
+    """See run_decode.  Returns the JSON-ready record."""
+    import torch
+
+    from georefine_b200 import serve
+
+    cfg = serve.DecoderConfig(layers=layers)
     t0 = time.time()
-    weights = serve.DecoderWeights.synthetic(cfg, dev, seed=SEED, distinct_layers=args.distinct_layers, max_m=128)
+    weights = serve.DecoderWeights.synthetic(cfg, dev, seed=SEED, distinct_layers=distinct_layers, max_m=128)
     build_s = time.time() - t0
-    seqs = [int(v) for v in args.seqs.split(",")]
-    context, generate, k = 2048, 128, 5
+    context, k = 2048, 5
     spec_rows = max(seqs) * (k + 1)
-    d = serve.BatchDecoder(weights, max_rows=spec_rows if args.spec else max(seqs), max_slots=max(seqs), max_context=context + generate + 2 * k + 2, device=dev)
+    d = serve.BatchDecoder(weights, max_rows=spec_rows if spec else max(seqs), max_slots=max(seqs), max_context=context + generate + 2 * k + 2, device=dev)
     for part in d.kv.view(-1, d.kv.shape[-3] * d.kv.shape[-2] * d.kv.shape[-1]).split(4096):
         part.uniform_(-0.5, 0.5)                                   # a synthetic context in every page
     peak, peak_kind = measured_hbm_peak()
@@ -806,7 +895,7 @@ def run_decode(args):
                "streamed_GBps": round((kv + weights.streamed_bytes()) / (ms * 1e-3) / 1e9, 1),
                "frac_of_hbm_peak": round((kv + weights.streamed_bytes()) / (ms * 1e-3) / 1e9 / peak, 4),
                "status_word": sum(w.check_status() for w in weights.linears()), "clocks": clocks.summary(t_begin, t_end)}
-        if args.spec:                                              # config 3: exact speculation, k = 5, verify pass at n x 6 rows
+        if spec:                                              # config 3: exact speculation, k = 5, verify pass at n x 6 rows
             b.sync_tokens()
             for s in b.active.values():
                 s["pos"], s["tokens"] = context, s["tokens"][-1:]
@@ -831,7 +920,9 @@ def run_decode(args):
     clocks.stop()
     line["value"] = line["results"][str(max(seqs))]["tok_s"]
     line["peak_hbm_GBps"] = peak
-    print(json.dumps(line), flush=True)
+    del b, d, weights
+    torch.cuda.empty_cache()
+    return line
 
 
 def run_reference(args):
@@ -860,6 +951,7 @@ def main():
                     help="resident layout of the weights: fixed 4-bit window codes (default), fixed 3-bit window codes, or "
                          "entropy-coded exponent streams")
     ap.add_argument("--skip-layouts", action="store_true", help="do not time the other two layouts after the main run")
+    ap.add_argument("--skip-decode", action="store_true", help="do not time the whole-stack decode step after the main run")
     ap.add_argument("--workload", choices=("linears", "decode"), default="linears",
                     help="linears: the fused decode-GEMM step (the headline metric); decode: whole-stack tokens per second")
     ap.add_argument("--seqs", default="64,128", help="decode workload: concurrent sequences, comma separated")

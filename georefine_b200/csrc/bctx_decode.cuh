@@ -87,6 +87,11 @@ __global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
   }
   uint16_t* out = a.out + i * a.stride;
   const uint32_t steps = uint32_t(min(uint64_t(a.stride), a.n - start));
+  // A lane's words go out eight at a time as one 16-byte store (its run of the output is contiguous); with 2-byte
+  // stores the 32 lanes of a warp, 2 * stride bytes apart, would issue sixteen times as many store instructions, each
+  // touching 32 sectors.  Needs runs that start on 16-byte boundaries; any other stride keeps the plain stores.
+  const bool wide = (a.stride & 7u) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+  uint32_t packed[4] = {0, 0, 0, 0};
   for (uint32_t step = 0; step < steps && !bad; ++step) {
     const uint32_t ctx = uint32_t(__ldg(a.row_class + row)) * a.nc + __ldg(a.col_class + col);
     uint32_t sym = 0, res = 0;
@@ -103,7 +108,19 @@ __global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
         res = bctx_symbol<64>(a.resid_s, sym, rx, rip, bad);
       }
     }
-    out[step] = uint16_t((sym << 5) | (res & 31u) | ((res & 32u) << 10));
+    const uint32_t word = ((sym << 5) | (res & 31u) | ((res & 32u) << 10)) & 0xFFFFu;
+    if (wide) {
+      const uint32_t k = step & 7u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (uint32_t(j) == (k >> 1)) packed[j] = (k & 1u) ? (packed[j] | word << 16) : word;
+      if (k == 7u) *reinterpret_cast<uint4*>(out + step - 7) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      else if (step + 1 == steps) {  // a ragged last block: what has been gathered so far
+        for (uint32_t e = 0; e <= k; ++e) out[step - k + e] = uint16_t(packed[e >> 1] >> (16 * (e & 1)));
+      }
+    } else {
+      out[step] = uint16_t(word);
+    }
     if (++col == a.cols) {
       col = 0;
       ++row;

@@ -209,16 +209,16 @@ attn_prep_kernel(const AttnArgs a) {
 // One split of one row for one kv head and ALL the query heads of its group: the 64 KB of K and of V of the split are
 // read once.  grid (max_splits, nkv, rows), 256 threads.
 //   scores: half a warp per position (16 lanes x 16 bytes = one K row), G dot products per position, xor butterfly over
-//           the 16 lanes; a warp handles two positions per step, four steps in flight;
+//           the 16 lanes; a warp handles two positions per step, eight steps in flight;
 //   soft-max partials per query head: maximum, exponentials, sum (fixed order);
-//   values: thread = (group of positions, pair of dimensions): acc += p[i] * V[i][d]; the four position groups are
-//           added in order.
+//   values: half a warp per position too (16 lanes x 16 bytes = one V row): acc += p[i] * V[i][d]; the sixteen
+//           position groups are added in a fixed order (the halves of a warp by shuffle, the warps in warp order).
 template <int G>
-__global__ void __launch_bounds__(kAttnThreads)
+__global__ void __launch_bounds__(kAttnThreads, G <= 5 ? 3 : 2)
 attn_split_kernel(const AttnArgs a) {
   __shared__ float score[G][kAttnSplit];
   __shared__ float red[kAttnThreads / 32];
-  __shared__ float acc_sm[3][G][kAttnDim];
+  __shared__ float acc_sm[kAttnThreads / 32 - 1][G][kAttnDim];
   const uint32_t split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
   const int32_t nk = a.row_pos[row] + 1;
   const int32_t start = int32_t(split) * kAttnSplit;
@@ -239,16 +239,17 @@ attn_split_kernel(const AttnArgs a) {
     for (int i = 0; i < 4; ++i) { q[g][2 * i] = bf_lo(w[i]); q[g][2 * i + 1] = bf_hi(w[i]); }
   }
   // scores
-  constexpr int kFlight = 4;
-  for (uint32_t i0 = warp * 2 * kFlight; i0 < n; i0 += (kAttnThreads / 32) * 2 * kFlight) {
-    uint4 kv[kFlight];
+  constexpr int kFlight = 4;     // value rows in flight per lane
+  constexpr int kKeyFlight = 8;  // key rows in flight per lane
+  for (uint32_t i0 = warp * 2 * kKeyFlight; i0 < n; i0 += (kAttnThreads / 32) * 2 * kKeyFlight) {
+    uint4 kv[kKeyFlight];
 #pragma unroll
-    for (int f = 0; f < kFlight; ++f) {
+    for (int f = 0; f < kKeyFlight; ++f) {
       const uint32_t i = i0 + 2 * f + half;
       kv[f] = i < n ? *reinterpret_cast<const uint4*>(kp + size_t(i) * kAttnDim + l16 * 8) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int f = 0; f < kFlight; ++f) {
+    for (int f = 0; f < kKeyFlight; ++f) {
       const uint32_t i = i0 + 2 * f + half;
       const uint32_t w[4] = {kv[f].x, kv[f].y, kv[f].z, kv[f].w};
       float dot[G];
@@ -291,46 +292,65 @@ attn_split_kernel(const AttnArgs a) {
     if (t < n) score[g][t] = p;
   }
   __syncthreads();
-  // values: position group pg = t / 64 takes positions pg, pg + 4, ...; dimensions 2 * (t % 64), + 1
-  const uint32_t pg = t >> 6, d2 = t & 63;
-  float acc[G][2];
+  // values: half a warp per position again (16 lanes x 16 bytes = one V row, eight dimensions per lane); half-warp hw of
+  // the 16 takes positions hw, hw + 16, ..., four rows in flight per lane.  The two halves of a warp are added by one
+  // shuffle, the eight warps through shared memory in warp order.
+  const uint32_t hw = t >> 4;
+  float acc[G][8];
 #pragma unroll
-  for (int g = 0; g < G; ++g) acc[g][0] = acc[g][1] = 0.f;
-  for (uint32_t i0 = pg; i0 < n; i0 += 4 * kFlight) {
-    uint32_t vv[kFlight];
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  for (uint32_t i0 = hw; i0 < n; i0 += 16 * kFlight) {
+    uint4 vv[kFlight];
 #pragma unroll
     for (int f = 0; f < kFlight; ++f) {
-      const uint32_t i = i0 + 4 * f;
-      vv[f] = i < n ? *reinterpret_cast<const uint32_t*>(vp + size_t(i) * kAttnDim + 2 * d2) : 0u;
+      const uint32_t i = i0 + 16 * f;
+      vv[f] = i < n ? *reinterpret_cast<const uint4*>(vp + size_t(i) * kAttnDim + l16 * 8) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int f = 0; f < kFlight; ++f) {
-      const uint32_t i = i0 + 4 * f;
+      const uint32_t i = i0 + 16 * f;
       if (i < n) {
-        const float v0 = bf_lo(vv[f]), v1 = bf_hi(vv[f]);
+        const uint32_t w[4] = {vv[f].x, vv[f].y, vv[f].z, vv[f].w};
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           const float p = score[g][i];
-          acc[g][0] = __fmaf_rn(p, v0, acc[g][0]);
-          acc[g][1] = __fmaf_rn(p, v1, acc[g][1]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[g][2 * e] = __fmaf_rn(p, bf_lo(w[e]), acc[g][2 * e]);
+            acc[g][2 * e + 1] = __fmaf_rn(p, bf_hi(w[e]), acc[g][2 * e + 1]);
+          }
         }
       }
     }
   }
-  if (pg) {
 #pragma unroll
-    for (int g = 0; g < G; ++g) { acc_sm[pg - 1][g][2 * d2] = acc[g][0]; acc_sm[pg - 1][g][2 * d2 + 1] = acc[g][1]; }
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = __fadd_rn(acc[g][e], __shfl_xor_sync(0xFFFFFFFFu, acc[g][e], 16));
+  if (warp && half == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc_sm[warp - 1][g][l16 * 8 + e] = acc[g][e];
   }
   __syncthreads();
-  if (pg == 0) {
+  if (warp == 0 && half == 0) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float o0 = acc[g][0], o1 = acc[g][1];
+      float o[8];
 #pragma unroll
-      for (int k = 0; k < 3; ++k) { o0 = __fadd_rn(o0, acc_sm[k][g][2 * d2]); o1 = __fadd_rn(o1, acc_sm[k][g][2 * d2 + 1]); }
+      for (int e = 0; e < 8; ++e) {
+        o[e] = acc[g][e];
+#pragma unroll
+        for (int k = 0; k < kAttnThreads / 32 - 1; ++k) o[e] = __fadd_rn(o[e], acc_sm[k][g][l16 * 8 + e]);
+      }
       const size_t base = (size_t(row) * a.nq + hq0 + g) * a.max_splits + split;
-      *reinterpret_cast<float2*>(a.part_acc + base * kAttnDim + 2 * d2) = make_float2(o0, o1);
-      if (d2 == 0) { a.part_ml[base * 2] = mx[g]; a.part_ml[base * 2 + 1] = sum[g]; }
+      float4* dst = reinterpret_cast<float4*>(a.part_acc + base * kAttnDim + l16 * 8);
+      dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+      if (l16 == 0) { a.part_ml[base * 2] = mx[g]; a.part_ml[base * 2 + 1] = sum[g]; }
     }
   }
 }
