@@ -53,7 +53,8 @@ class BctxTensor(ctypes.Structure):
                 ("row_class", VOIDP), ("col_class", VOIDP), ("main_stream", VOIDP), ("main_bytes", ctypes.c_uint64),
                 ("main_states", VOIDP), ("main_offsets", VOIDP), ("main_cum", VOIDP), ("main_bucket", VOIDP),
                 ("residual_stream", VOIDP), ("residual_bytes", ctypes.c_uint64), ("residual_states", VOIDP),
-                ("residual_offsets", VOIDP), ("residual_cum", VOIDP), ("residual_bucket", VOIDP)]
+                ("residual_offsets", VOIDP), ("residual_cum", VOIDP), ("residual_bucket", VOIDP),
+                ("main_bucket_shift", ctypes.c_uint32), ("residual_bucket_shift", ctypes.c_uint32)]
 
 
 class AttnStep(ctypes.Structure):

@@ -4,9 +4,21 @@
 // 114-169): same inputs, same output order (count * stride words, block-major), same end-of-block check
 // against the next restart point, with the status bits split by cause.
 //
-// Differences in method: the symbol is found through a 4096-bucket inverse index plus a short forward scan
-// of the prefix sums (two or three dependent loads, served by L1/L2) instead of an 11-probe bisection, and
-// a block never touches memory outside [0, bytes) of its stream: overruns set a status bit and stop.
+// Differences in method.  A lane's walk is one serial chain - symbol k+1 cannot start before symbol k has
+// renormalised the state - so the kernel's time is (symbols per block) x (latency of one step), whatever the
+// number of blocks; everything below shortens the step:
+//  * the symbol is found through an inverse index (one 2-byte entry per bucket of 2^shift slots; the caller
+//    picks the shift so that the tables of all contexts stay in L1) plus a short forward scan of the prefix
+//    sums, instead of an 11-probe bisection;
+//  * the stream is read through a 12-byte look-ahead window of aligned 32-bit words, refilled two symbols
+//    before the bytes are needed, so no load of stream bytes sits on the chain; the number of bytes a
+//    renormalisation takes (0, 1 or 2: the state after a step is at least 2^7) comes from a leading-zero
+//    count, the bytes from one funnel shift;
+//  * eight symbols at a time: their contexts and their six bytes of raw residuals are loaded up front, the
+//    eight words leave as one 16-byte store.
+// Blocks that cannot take that path (a stride that is not a multiple of 8, rows shorter than 8, unaligned
+// buffers, the ragged end of the tensor) take a plain symbol-by-symbol loop.  No path touches memory
+// outside its streams: the window clamps at the stream's last word, an overrun sets a status bit.
 #pragma once
 #include "device_utils.cuh"
 
@@ -18,7 +30,8 @@ struct BctxStream {
   const uint32_t* states;
   const uint32_t* offsets;
   const uint32_t* cum;      // [nctx][vocab + 1]
-  const uint16_t* bucket;   // [nctx][4096]
+  const uint16_t* bucket;   // [nctx][65536 >> shift]: the symbol that owns the first slot of each bucket
+  uint32_t shift;           // log2 of the slots per bucket
 };
 
 struct BctxArgs {
@@ -38,7 +51,7 @@ template <uint32_t VOCAB>
 __device__ __forceinline__ uint32_t bctx_symbol(const BctxStream& st, uint32_t ctx, uint32_t& x, uint64_t& ip, uint32_t& bad) {
   const uint32_t slot = x & 0xFFFFu;
   const uint32_t* cum = st.cum + size_t(ctx) * (VOCAB + 1);
-  uint32_t s = __ldg(st.bucket + size_t(ctx) * 4096 + (slot >> 4));
+  uint32_t s = min(uint32_t(__ldg(st.bucket + (size_t(ctx) << (16 - st.shift)) + (slot >> st.shift))), VOCAB - 1);
   uint32_t lo = __ldg(cum + s), hi = __ldg(cum + s + 1);
   while (hi <= slot && s + 1 < VOCAB) {  // bounded by the vocabulary
     ++s;
@@ -65,7 +78,147 @@ __device__ __forceinline__ uint32_t bctx_symbol(const BctxStream& st, uint32_t c
   return s;
 }
 
-__global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
+// Big-endian look-ahead over a byte stream: w0, w1 hold the eight bytes from `base` (a multiple of 4, counted
+// from the stream's address rounded down to 4 bytes), w2 the four after them, already on their way.
+struct ByteWindow {
+  const uint32_t* words;
+  uint32_t limit;   // bytes from `words` to the end of the stream's last word
+  uint32_t base, w0, w1, w2;
+  __device__ __forceinline__ uint32_t fetch(uint32_t off) const {
+    return off < limit ? __byte_perm(__ldg(words + (off >> 2)), 0, 0x0123) : 0u;
+  }
+  // Returns the position of stream byte `at` in the window's own count (the stream's misalignment added).
+  __device__ __forceinline__ uint32_t open(const uint8_t* bytes, uint64_t size, uint32_t at) {
+    const uint32_t skew = uint32_t(reinterpret_cast<uintptr_t>(bytes) & 3u);
+    words = reinterpret_cast<const uint32_t*>(bytes - skew);
+    limit = uint32_t(min(uint64_t(0xFFFFFFF0u), (size + skew + 3) & ~uint64_t(3)));
+    const uint32_t ip = at + skew;
+    base = ip & ~3u;
+    w0 = fetch(base);
+    w1 = fetch(base + 4);
+    w2 = fetch(base + 8);
+    return ip;
+  }
+  // The state takes n (0..2) bytes from position ip.
+  __device__ __forceinline__ void feed(uint32_t& x, uint32_t& ip, uint32_t n) {
+    const uint32_t top = __funnelshift_l(w1, w0, (ip - base) * 8);
+    x = __funnelshift_l(top, x, n * 8);
+    ip += n;
+    if (ip - base >= 4) {
+      w0 = w1;
+      w1 = w2;
+      base += 4;
+      w2 = fetch(base + 8);
+    }
+  }
+};
+
+// Where the main stream's tables are read from.  Global: the caller's arrays (through L1).  Shared: a copy the CTA
+// made at its start - prefix sums as 16-bit values (65536 stored as 0: a symbol's upper bound is never 0 otherwise) and
+// the inverse index thinned to what fits - for frames whose contexts' tables fit in one SM's shared memory; there a
+// look-up costs a shared-memory access instead of an L1 or L2 round trip, twice per symbol on the serial chain.
+struct TablesGlobal {
+  const uint32_t* cum;      // [nctx][vocab + 1]
+  const uint16_t* bucket;   // [nctx][65536 >> shift]
+  uint32_t shift, vocab1;
+  __device__ __forceinline__ uint32_t first(uint32_t ctx, uint32_t slot) const {
+    return __ldg(bucket + (size_t(ctx) << (16 - shift)) + (slot >> shift));
+  }
+  __device__ __forceinline__ uint32_t bound(uint32_t ctx, uint32_t s) const { return __ldg(cum + size_t(ctx) * vocab1 + s); }
+};
+struct TablesShared {
+  uint32_t cum_at, bucket_at;   // shared-memory byte addresses
+  uint32_t shift, cum_stride;   // cum_stride: 16-bit entries per context (odd number of 32-bit words)
+  __device__ __forceinline__ uint32_t first(uint32_t ctx, uint32_t slot) const {
+    return lds_u16(bucket_at + (((ctx << (16 - shift)) + (slot >> shift)) << 1));
+  }
+  __device__ __forceinline__ uint32_t bound(uint32_t ctx, uint32_t s) const {
+    const uint32_t v = lds_u16(cum_at + ((ctx * cum_stride + s) << 1));
+    return s && v == 0 ? 65536u : v;
+  }
+  static __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+  }
+};
+
+// One decoding step on the look-ahead window.  The scan ends at the latest on the table's last entry (65536).
+template <uint32_t VOCAB, class Tables>
+__device__ __forceinline__ uint32_t bctx_symbol_fast(const Tables& t, uint32_t ctx, uint32_t& x, ByteWindow& w, uint32_t& ip) {
+  const uint32_t slot = x & 0xFFFFu;
+  uint32_t s = min(t.first(ctx, slot), VOCAB - 1);
+  uint32_t lo = t.bound(ctx, s), hi = t.bound(ctx, s + 1);
+  while (hi <= slot && s + 1 < VOCAB) {
+    ++s;
+    lo = hi;
+    hi = t.bound(ctx, s + 1);
+  }
+  x = (hi - lo) * (x >> 16) + (slot - lo);
+  w.feed(x, ip, min(2u, (uint32_t(__clz(int(x | 1u))) - 1u) >> 3));
+  return s;
+}
+
+// `groups` runs of eight symbols from (row, col) on; leaves x, ip (and rx, rip) where the plain loop can carry on.
+template <bool RAW6, class MainTables>
+__device__ __forceinline__ void bctx_block_fast(const BctxArgs& a, const MainTables& mt, uint32_t groups, uint64_t start, uint32_t& row,
+                                                uint32_t& col, uint32_t& x, uint64_t& ip64, uint32_t& rx, uint64_t& rip64, uint16_t* out,
+                                                uint32_t& bad) {
+  ByteWindow mw, rw;
+  uint32_t ip = mw.open(a.main_s.bytes, a.main_s.size, uint32_t(ip64));
+  const uint32_t skew = ip - uint32_t(ip64);
+  uint32_t rip = 0, rskew = 0;
+  if (!RAW6) {
+    rip = rw.open(a.resid_s.bytes, a.resid_s.size, uint32_t(rip64));
+    rskew = rip - uint32_t(rip64);
+  }
+  const TablesGlobal rt{a.resid_s.cum, a.resid_s.bucket, a.resid_s.shift, 65};
+  const uint32_t cols = a.cols, nc = a.nc, top_ctx = a.main_contexts - 1;
+  const uint16_t* raw = reinterpret_cast<const uint16_t*>(a.resid_s.bytes + (start >> 2) * 3);   // 6 bytes per group
+  for (uint32_t g = 0; g < groups; ++g) {
+    uint32_t ctx[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {               // a group crosses at most one row end (cols >= 8)
+      uint32_t c = col + j, r = row;
+      if (c >= cols) { c -= cols; ++r; }
+      const uint32_t v = uint32_t(__ldg(a.row_class + r)) * nc + __ldg(a.col_class + c);
+      if (v > top_ctx) bad |= kStatusBadSymbol;
+      ctx[j] = min(v, top_ctx);
+    }
+    uint32_t r32 = 0, r16 = 0;
+    if (RAW6) {
+      const uint32_t h0 = __ldg(raw + 3 * g), h1 = __ldg(raw + 3 * g + 1), h2 = __ldg(raw + 3 * g + 2);
+      r32 = __byte_perm(h0 | (h1 << 16), 0, 0x0123);     // the first four bytes, most significant first
+      r16 = __byte_perm(h2, 0, 0x4401);                  // the last two
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t sym = bctx_symbol_fast<1024>(mt, ctx[j], x, mw, ip);
+      uint32_t res;
+      if (RAW6) {
+        res = j < 5 ? (r32 >> (26 - 6 * j)) & 63u : j == 5 ? ((r32 & 3u) << 4) | (r16 >> 12) : j == 6 ? (r16 >> 6) & 63u : r16 & 63u;
+      } else {
+        res = bctx_symbol_fast<64>(rt, sym, rx, rw, rip);
+      }
+      const uint32_t word = ((sym << 5) | (res & 31u) | ((res & 32u) << 10)) & 0xFFFFu;
+      if (j & 1) packed[j >> 1] |= word << 16;
+      else packed[j >> 1] = word;
+    }
+    *reinterpret_cast<uint4*>(out + 8 * g) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    col += 8;
+    if (col >= cols) { col -= cols; ++row; }
+  }
+  ip64 = ip - skew;
+  if (ip64 > a.main_s.size) bad |= kStatusOverrun;
+  if (!RAW6) {
+    rip64 = rip - rskew;
+    if (rip64 > a.resid_s.size) bad |= kStatusOverrun;
+  }
+}
+
+template <class MainTables>
+__device__ __forceinline__ void bctx_decode_lane(const BctxArgs& a, const MainTables& mt) {
   const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= a.count) return;
   const uint64_t block = a.block_ids ? uint64_t(a.block_ids[i]) : i;
@@ -87,12 +240,18 @@ __global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
   }
   uint16_t* out = a.out + i * a.stride;
   const uint32_t steps = uint32_t(min(uint64_t(a.stride), a.n - start));
-  // A lane's words go out eight at a time as one 16-byte store (its run of the output is contiguous); with 2-byte
-  // stores the 32 lanes of a warp, 2 * stride bytes apart, would issue sixteen times as many store instructions, each
-  // touching 32 sectors.  Needs runs that start on 16-byte boundaries; any other stride keeps the plain stores.
+  // Runs of eight symbols on the look-ahead path (16-byte stores: needs runs that start on 16-byte boundaries), what
+  // is left - at most seven symbols of a ragged last block, or everything when the path does not apply - step by step.
   const bool wide = (a.stride & 7u) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
-  uint32_t packed[4] = {0, 0, 0, 0};
-  for (uint32_t step = 0; step < steps && !bad; ++step) {
+  uint32_t done = 0;
+  if (wide && a.cols >= 8 && (reinterpret_cast<uintptr_t>(a.resid_s.bytes) & 1u) == 0 && a.main_s.size < 0xFFFFFF00ull &&
+      a.resid_s.size < 0xFFFFFF00ull) {
+    const uint32_t groups = steps >> 3;
+    if (a.raw6) bctx_block_fast<true>(a, mt, groups, start, row, col, x, ip, rx, rip, out, bad);
+    else bctx_block_fast<false>(a, mt, groups, start, row, col, x, ip, rx, rip, out, bad);
+    done = groups << 3;
+  }
+  for (uint32_t step = done; step < steps && !bad; ++step) {
     const uint32_t ctx = uint32_t(__ldg(a.row_class + row)) * a.nc + __ldg(a.col_class + col);
     uint32_t sym = 0, res = 0;
     if (ctx >= a.main_contexts) {
@@ -109,18 +268,7 @@ __global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
       }
     }
     const uint32_t word = ((sym << 5) | (res & 31u) | ((res & 32u) << 10)) & 0xFFFFu;
-    if (wide) {
-      const uint32_t k = step & 7u;
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (uint32_t(j) == (k >> 1)) packed[j] = (k & 1u) ? (packed[j] | word << 16) : word;
-      if (k == 7u) *reinterpret_cast<uint4*>(out + step - 7) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      else if (step + 1 == steps) {  // a ragged last block: what has been gathered so far
-        for (uint32_t e = 0; e <= k; ++e) out[step - k + e] = uint16_t(packed[e >> 1] >> (16 * (e & 1)));
-      }
-    } else {
-      out[step] = uint16_t(word);
-    }
+    out[step] = uint16_t(word);
     if (++col == a.cols) {
       col = 0;
       ++row;
@@ -139,6 +287,35 @@ __global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
     }
   }
   if (bad) atomicOr(a.status, bad);
+}
+
+__global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
+  bctx_decode_lane(a, TablesGlobal{a.main_s.cum, a.main_s.bucket, a.main_s.shift, 1025});
+}
+
+// The same walk with the main stream's tables copied into shared memory first: prefix sums [nctx][1026] and the inverse
+// index [nctx][65536 >> shift] as 16-bit values, `shift` chosen by the host so that both fit.  One CTA per SM; the
+// host sizes the CTA so that the blocks of the call spread over all SMs.
+constexpr uint32_t kBctxCumStride = 1026;   // 16-bit entries per context: 1025 used; 513 32-bit words, odd, so contexts spread over the banks
+__host__ __device__ inline uint32_t bctx_shared_bytes(uint32_t nctx, uint32_t shift) {
+  return nctx * (kBctxCumStride + (65536u >> shift)) * 2u;
+}
+__global__ void __launch_bounds__(512) bctx_decode_shared_kernel(const BctxArgs a, uint32_t shift) {
+  extern __shared__ __align__(16) uint16_t bctx_tables[];
+  const uint32_t nctx = a.main_contexts, per = 65536u >> shift;
+  uint16_t* cum16 = bctx_tables;
+  uint16_t* bucket16 = bctx_tables + size_t(nctx) * kBctxCumStride;
+  for (uint32_t e = threadIdx.x; e < nctx * 1025u; e += blockDim.x) {
+    const uint32_t c = e / 1025u, k = e - c * 1025u;
+    cum16[c * kBctxCumStride + k] = uint16_t(__ldg(a.main_s.cum + e));
+  }
+  const uint32_t thin = shift - a.main_s.shift;    // the caller's index has 65536 >> main_s.shift entries per context
+  for (uint32_t e = threadIdx.x; e < nctx * per; e += blockDim.x) {
+    const uint32_t c = e / per, k = e - c * per;
+    bucket16[e] = __ldg(a.main_s.bucket + (size_t(c) << (16 - a.main_s.shift)) + (size_t(k) << thin));
+  }
+  __syncthreads();
+  bctx_decode_lane(a, TablesShared{smem_u32(cum16), smem_u32(bucket16), shift, kBctxCumStride});
 }
 
 }  // namespace grb

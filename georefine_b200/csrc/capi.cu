@@ -204,9 +204,31 @@ int dense_launch(const DenseArgs& a, uint32_t groups, uint32_t sms, cudaStream_t
   return wide ? dense_launch_as<M, true>(a, groups, sms, stream) : dense_launch_as<M, false>(a, groups, sms, stream);
 }
 
+// SM count of a device, looked up once.
+int device_sm_count(int dev) {
+  static std::mutex mu;
+  static int sms[64] = {0};
+  if (dev < 0 || dev >= 64) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!sms[dev] && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 0;
+  return sms[dev];
+}
+
+constexpr uint32_t kBctxSharedLimit = 220u * 1024u;   // dynamic shared memory the table-resident decode kernel may ask for
+
 template <int G>
-int attn_split_launch(const AttnArgs& a, cudaStream_t stream) {
-  attn_split_kernel<G><<<dim3(a.max_splits, a.nkv, a.rows), kAttnThreads, 0, stream>>>(a);
+int attn_part_launch(const AttnArgs& a, cudaStream_t stream) {
+  static std::once_flag once[64];
+  static int prepared[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return GRB_ERR_CUDA;
+  std::call_once(once[dev], [&] {
+    prepared[dev] = cuda_status(cudaFuncSetAttribute(attn_part_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kAttnPartSmem)));
+  });
+  if (prepared[dev]) return prepared[dev];
+  constexpr uint32_t kRowsPerGroup = 16 / G;
+  const uint32_t columns = (a.max_splits + kAttnPartsPerCta - 1) / kAttnPartsPerCta;
+  attn_part_kernel<G><<<dim3(columns, a.nkv, (a.rows + kRowsPerGroup - 1) / kRowsPerGroup), kAttnPartThreads, kAttnPartSmem, stream>>>(a);
   return cuda_status(cudaGetLastError());
 }
 
@@ -231,9 +253,11 @@ int grb_bctx_decode_words(const grb_bctx_tensor* t, const int64_t* block_ids, ui
   if (count == 0) return GRB_OK;
   if (count > (uint64_t(1) << 37)) return GRB_ERR_ARGUMENT;
   BctxArgs a{};
-  a.main_s = {t->main_stream, t->main_bytes, t->main_states, t->main_offsets, t->main_cum, t->main_bucket};
+  const uint32_t main_shift = t->main_bucket_shift ? t->main_bucket_shift : 4, resid_shift = t->residual_bucket_shift ? t->residual_bucket_shift : 4;
+  if (main_shift > 16 || resid_shift > 16) return GRB_ERR_ARGUMENT;
+  a.main_s = {t->main_stream, t->main_bytes, t->main_states, t->main_offsets, t->main_cum, t->main_bucket, main_shift};
   a.resid_s = {t->residual_stream, t->residual_bytes, t->residual_states, t->residual_offsets, t->residual_cum,
-               t->residual_bucket};
+               t->residual_bucket, resid_shift};
   a.row_class = t->row_class;
   a.col_class = t->col_class;
   a.n = t->n;
@@ -246,8 +270,29 @@ int grb_bctx_decode_words(const grb_bctx_tensor* t, const int64_t* block_ids, ui
   a.count = count;
   a.out = out;
   a.status = status;
+  const auto stream = static_cast<cudaStream_t>(cuda_stream);
+  // Large calls on frames whose main tables fit in one SM's shared memory read them from there.
+  int dev = 0, sms = 0;
+  if (count >= 2048 && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && (sms = device_sm_count(dev)) > 0) {
+    uint32_t shift = main_shift;
+    while (shift < 9 && bctx_shared_bytes(a.main_contexts, shift) > kBctxSharedLimit) ++shift;
+    if (bctx_shared_bytes(a.main_contexts, shift) <= kBctxSharedLimit) {
+      static std::once_flag once[64];
+      static int prepared[64];
+      std::call_once(once[dev], [&] {
+        prepared[dev] = cuda_status(cudaFuncSetAttribute(bctx_decode_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kBctxSharedLimit)));
+      });
+      if (prepared[dev]) return prepared[dev];
+      // one CTA per SM (the tables take most of its shared memory): lanes per CTA so that one wave covers the call
+      uint64_t threads = (count + uint64_t(sms) - 1) / uint64_t(sms);
+      threads = std::min<uint64_t>(512, std::max<uint64_t>(64, (threads + 31) / 32 * 32));
+      const unsigned grid = unsigned((count + threads - 1) / threads);
+      bctx_decode_shared_kernel<<<grid, unsigned(threads), bctx_shared_bytes(a.main_contexts, shift), stream>>>(a, shift);
+      return cuda_status(cudaGetLastError());
+    }
+  }
   const unsigned grid = unsigned((count + 63) / 64);
-  bctx_decode_kernel<<<grid, 64, 0, static_cast<cudaStream_t>(cuda_stream)>>>(a);
+  bctx_decode_kernel<<<grid, 64, 0, stream>>>(a);
   return cuda_status(cudaGetLastError());
 }
 
@@ -439,7 +484,7 @@ int grb_attn_decode_bf16(const grb_attn_step* s, void* cuda_stream) {
       ((reinterpret_cast<uintptr_t>(s->qkv) | reinterpret_cast<uintptr_t>(s->q) | reinterpret_cast<uintptr_t>(s->k_pages) |
         reinterpret_cast<uintptr_t>(s->v_pages) | reinterpret_cast<uintptr_t>(s->part_acc)) & 15))
     return GRB_ERR_ARGUMENT;
-  if (s->rows > 65535 || s->nq + 2 * s->nkv > 65535 || s->max_splits > s->max_pages) return GRB_ERR_UNSUPPORTED;
+  if (s->rows > 65535 || s->nq + 2 * s->nkv > 65535 || s->max_splits > 2 * s->max_pages) return GRB_ERR_UNSUPPORTED;
   AttnArgs a{};
   a.qkv = static_cast<const __nv_bfloat16*>(s->qkv);
   a.ldq = s->ldq;
@@ -465,11 +510,11 @@ int grb_attn_decode_bf16(const grb_attn_step* s, void* cuda_stream) {
   int st = cuda_status(cudaGetLastError());
   if (st) return st;
   switch (a.nq / a.nkv) {
-    case 1: st = attn_split_launch<1>(a, stream); break;
-    case 2: st = attn_split_launch<2>(a, stream); break;
-    case 4: st = attn_split_launch<4>(a, stream); break;
-    case 5: st = attn_split_launch<5>(a, stream); break;
-    case 8: st = attn_split_launch<8>(a, stream); break;
+    case 1: st = attn_part_launch<1>(a, stream); break;
+    case 2: st = attn_part_launch<2>(a, stream); break;
+    case 4: st = attn_part_launch<4>(a, stream); break;
+    case 5: st = attn_part_launch<5>(a, stream); break;
+    case 8: st = attn_part_launch<8>(a, stream); break;
     default: return GRB_ERR_UNSUPPORTED;
   }
   if (st) return st;

@@ -1,29 +1,31 @@
 // The element-wise and attention kernels of a batched decode step, around the fused linears: RMSNorm with the residual
-// add folded in, rotary embedding + paged KV append, decode attention over a paged KV cache (fixed 256-position splits,
-// merged in split order), SwiGLU and arg-max.  Counterparts of the reference's step kernels
+// add folded in, rotary embedding + paged KV append, decode attention over a paged KV cache (fixed 128-position parts,
+// merged in part order), SwiGLU and arg-max.  Counterparts of the reference's step kernels
 // (glc_serve/fastdec_kernels.cu:83-110 rmsnorm, :324-359 attn_prep, :365-423 attn_split, :426-448 attn_combine, :451-459
 // silu_mul, :462-488 argmax) and of their batched twins with a page table (glc_serve/bidec.py:71-81), for a plain
 // grouped-query decoder: no per-head q/k norm, no output gate, full-width rotary embedding, head dimension 128.
 //
 // Numerical contract (what makes a row of the step independent of the batch it is in): every row is computed by CTAs of
 // its own, with a fixed order of additions; every intermediate that the BF16 model rounds is rounded here (norm output,
-// rotary products and their sum, attention output, SiLU before the product).  A KV page holds 256 positions of one
-// sequence - exactly one attention split - as [kv head][position][128] BF16, so a split streams one contiguous 64 KB
-// run per kv head for K and one for V, once for all the query heads of the group.
+// rotary products and their sum, attention weights, attention output, SiLU before the product).  A KV page holds 256
+// positions of one sequence as [kv head][position][128] BF16, so an attention part (128 positions) streams one
+// contiguous 32 KB run per kv head for K and one for V, once for all the query heads of the group and for all the rows
+// of the step that belong to the same sequence and share the CTA.
 //
 // These are HBM-bound streaming kernels: coalesced 128-bit loads, several CTAs resident per SM, grids far larger than
-// 148 so that the tail does not matter; nothing here is GEMM-shaped (a decode query is one row), so no tensor cores.
+// 148 so that the tail does not matter.  Only the attention has products to form (scores and weighted values of up to
+// 16 query rows per part); it uses the warp-level MMA, see attn_part_kernel.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "device_utils.cuh"
+
 namespace grb {
 
 constexpr int kAttnDim = 128;     // head dimension the attention kernels are written for
-constexpr int kAttnSplit = 256;   // positions per split = positions per KV page
-constexpr int kAttnThreads = 256;
-constexpr int kAttnMaxGroup = 8;  // query heads per kv head
+constexpr int kAttnSplit = 256;   // positions per KV page
 
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xFFFF0000u); }
@@ -206,167 +208,285 @@ attn_prep_kernel(const AttnArgs a) {
   else a.k_pages[(size_t(page) * a.nkv + (head - a.nq)) * kAttnSplit * kAttnDim + in_page] = o;
 }
 
-// One split of one row for one kv head and ALL the query heads of its group: the 64 KB of K and of V of the split are
-// read once.  grid (max_splits, nkv, rows), 256 threads.
-//   scores: half a warp per position (16 lanes x 16 bytes = one K row), G dot products per position, xor butterfly over
-//           the 16 lanes; a warp handles two positions per step, eight steps in flight;
-//   soft-max partials per query head: maximum, exponentials, sum (fixed order);
-//   values: half a warp per position too (16 lanes x 16 bytes = one V row): acc += p[i] * V[i][d]; the sixteen
-//           position groups are added in a fixed order (the halves of a warp by shuffle, the warps in warp order).
+// ---- one part (128 positions) of the context, for one kv head and a group of rows ----------------------------
+// grid (parts, kv heads, row groups), 128 threads, 64 KB of dynamic shared memory, three CTAs per SM.
+//
+// A row group is R = 16 / G consecutive rows of the step (G = query heads per kv head).  Inside a group, each run of
+// rows that belong to one sequence - the k + 1 rows of a speculative verify, the rows of a prompt chunk, or a single
+// row of a plain decode step - shares its passes: a pass brings the 32 KB of K and the 32 KB of V of one part into
+// shared memory once (16-byte asynchronous copies, the 16-byte pieces of a row permuted by the row's low bits so that
+// the matrix loads below are conflict-free) for all the run's rows and all G query heads: the M = 16 rows of a
+// warp-level MMA are (row of the run, query head).
+//   scores  S[16 x 32 per warp] = Q[16 x 128] K^T   mma.m16n8k16, K fragments by ldmatrix
+//   soft-max partials per warp over its 32 positions (each row of the MMA masked by its own context length)
+//   values  O[16 x 128] += P[16 x 32] V[32 x 128]   P from the score registers rounded to BF16, V by ldmatrix.trans
+//   the four warps' (maximum, sum, O) merged in warp order under their common maximum -> part_acc, part_ml.
+// The CTA's passes (one per run that sees the part) are listed up front and software-pipelined: the K tile of the next
+// pass is requested as soon as the scores of this one are done, its V tile as soon as the merge (which borrows the V
+// tile's place) is, so the memory system always has the next 32 KB in flight while the SM computes.
+// Five query rows would fill 5 of the 64 rows that a tcgen05 instruction computes at least; the warp-level MMA has 16,
+// and the kernel is bound by HBM either way (8 flops per byte of K and V).  Every output element depends on its own
+// row's operands only, so a row's bits do not depend on what shares the MMA with it.
+constexpr int kAttnPart = 128;          // positions per pass; two parts per 256-position page
+constexpr int kAttnPartsPerCta = 1;     // parts per CTA (x its runs = its passes)
+constexpr int kAttnPartThreads = 128;
+constexpr int kAttnTileBytes = kAttnPart * kAttnDim * 2;   // 32 KB: K or V of one part
+constexpr uint32_t kAttnPartSmem = 2 * kAttnTileBytes;
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D (16 x 8, FP32) += A (16 x 16, BF16, row) * B (16 x 8, BF16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float exp2_approx(float v) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+// Byte offset of 16-byte piece `piece` (0..15) of tile row `row` (256 bytes per row).
+__device__ __forceinline__ uint32_t attn_tile_offset(uint32_t row, uint32_t piece) {
+  return row * 256u + ((((piece ^ row) & 7u) | (piece & 8u)) << 4);
+}
+// Float index of (MMA row m, dimension d) in a warp's 16 x 128 block of the merge buffer: the columns of a row are
+// permuted by the row's low bits, which spreads a warp's accumulator stores (eight rows, same columns) over the banks.
+__device__ __forceinline__ uint32_t attn_merge_index(uint32_t m, uint32_t d) { return m * kAttnDim + (d ^ ((m & 7u) << 2)); }
+
+struct AttnPass {
+  const __nv_bfloat16* k;   // the part's K tile: [128][128]
+  const __nv_bfloat16* v;
+  uint32_t run_first;       // first row of the run in the step
+  uint32_t run_rows;
+  int32_t start;            // first position of the part
+  uint32_t npos;            // positions of the part that the run's longest row sees
+  uint32_t part;
+};
+
+// One tile (K or V) of a pass into shared memory: 2048 pieces of 16 bytes, rows beyond the context zero-filled.
+__device__ __forceinline__ void attn_request_tile(uint32_t dst, const __nv_bfloat16* src, uint32_t npos, uint32_t tid) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t c = tid + i * kAttnPartThreads, r = c >> 4, piece = c & 15u;
+    cp_async_16(dst + attn_tile_offset(r, piece), src + r * kAttnDim + piece * 8, r < npos ? 16u : 0u);
+  }
+  cp_async_commit();
+}
+
 template <int G>
-__global__ void __launch_bounds__(kAttnThreads, G <= 5 ? 3 : 2)
-attn_split_kernel(const AttnArgs a) {
-  __shared__ float score[G][kAttnSplit];
-  __shared__ float red[kAttnThreads / 32];
-  __shared__ float acc_sm[kAttnThreads / 32 - 1][G][kAttnDim];
-  const uint32_t split = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
-  const int32_t nk = a.row_pos[row] + 1;
-  const int32_t start = int32_t(split) * kAttnSplit;
-  if (start >= nk) return;
-  const uint32_t n = uint32_t(min(kAttnSplit, nk - start));
-  const int32_t page = a.page_table[size_t(a.row_seq[row]) * a.max_pages + split];
-  const __nv_bfloat16* kp = a.k_pages + (size_t(page) * a.nkv + kvh) * kAttnSplit * kAttnDim;
-  const __nv_bfloat16* vp = a.v_pages + (size_t(page) * a.nkv + kvh) * kAttnSplit * kAttnDim;
-  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
-  const uint32_t hq0 = kvh * G;
-  // the group's queries: this lane's eight dimensions of each head
-  float q[G][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const uint4 u = *reinterpret_cast<const uint4*>(a.q + (size_t(row) * a.nq + hq0 + g) * kAttnDim + l16 * 8);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { q[g][2 * i] = bf_lo(w[i]); q[g][2 * i + 1] = bf_hi(w[i]); }
-  }
-  // scores
-  constexpr int kFlight = 4;     // value rows in flight per lane
-  constexpr int kKeyFlight = 8;  // key rows in flight per lane
-  for (uint32_t i0 = warp * 2 * kKeyFlight; i0 < n; i0 += (kAttnThreads / 32) * 2 * kKeyFlight) {
-    uint4 kv[kKeyFlight];
-#pragma unroll
-    for (int f = 0; f < kKeyFlight; ++f) {
-      const uint32_t i = i0 + 2 * f + half;
-      kv[f] = i < n ? *reinterpret_cast<const uint4*>(kp + size_t(i) * kAttnDim + l16 * 8) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int f = 0; f < kKeyFlight; ++f) {
-      const uint32_t i = i0 + 2 * f + half;
-      const uint32_t w[4] = {kv[f].x, kv[f].y, kv[f].z, kv[f].w};
-      float dot[G];
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float s = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          s = __fmaf_rn(q[g][2 * e], bf_lo(w[e]), s);
-          s = __fmaf_rn(q[g][2 * e + 1], bf_hi(w[e]), s);
-        }
-        dot[g] = s;
+__global__ void __launch_bounds__(kAttnPartThreads, 3)
+attn_part_kernel(const AttnArgs a) {
+  constexpr int R = 16 / G;              // rows of the step per group
+  constexpr int kMaxPasses = R * kAttnPartsPerCta;
+  extern __shared__ __align__(128) unsigned char attn_smem[];
+  __shared__ float ml_sm[kAttnPartThreads / 32][16][2];
+  __shared__ AttnPass passes[kMaxPasses];
+  __shared__ uint32_t pass_count;
+  const uint32_t ks = smem_u32(attn_smem), vs = ks + kAttnTileBytes;
+  float* const merge = reinterpret_cast<float*>(attn_smem + kAttnTileBytes);   // [4][16][128], in the V tile's place once it is used up
+  const uint32_t part0 = blockIdx.x * kAttnPartsPerCta, kvh = blockIdx.y, row0 = blockIdx.z * R;
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t m0 = lane >> 2, m1 = m0 + 8;      // the two MMA rows whose scores and outputs this lane holds
+  const float scale2 = __fmul_rn(a.scaling, 1.4426950408889634f);   // scores in units of log 2: exponentials are one ex2 each
+  if (tid == 0) {                                  // the CTA's passes: every run of the group x the page's parts it sees
+    const uint32_t group_rows = min(uint32_t(R), a.rows - row0);
+    uint32_t n = 0;
+    for (uint32_t run_begin = 0; run_begin < group_rows;) {
+      const int32_t seq = a.row_seq[row0 + run_begin];
+      uint32_t run_end = run_begin + 1;
+      int32_t longest = a.row_pos[row0 + run_begin] + 1;
+      while (run_end < group_rows && a.row_seq[row0 + run_end] == seq) {
+        longest = max(longest, a.row_pos[row0 + run_end] + 1);
+        ++run_end;
       }
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-#pragma unroll
-        for (int off = 8; off; off >>= 1) dot[g] = __fadd_rn(dot[g], __shfl_xor_sync(0xFFFFFFFFu, dot[g], off));
-        if (l16 == 0 && i < n) score[g][i] = __fmul_rn(dot[g], a.scaling);
+      for (uint32_t h = 0; h < uint32_t(kAttnPartsPerCta); ++h) {
+        const uint32_t part = part0 + h;
+        const int32_t start = int32_t(part) * kAttnPart;
+        if (start >= longest || part >= a.max_splits) break;
+        const int32_t page = a.page_table[size_t(seq) * a.max_pages + part / (kAttnSplit / kAttnPart)];
+        const size_t tile_at = ((size_t(page) * a.nkv + kvh) * kAttnSplit + (part % (kAttnSplit / kAttnPart)) * kAttnPart) * kAttnDim;
+        AttnPass& p = passes[n++];
+        p.k = a.k_pages + tile_at;
+        p.v = a.v_pages + tile_at;
+        p.run_first = row0 + run_begin;
+        p.run_rows = run_end - run_begin;
+        p.start = start;
+        p.npos = uint32_t(min(kAttnPart, longest - start));
+        p.part = part;
       }
+      run_begin = run_end;
     }
+    pass_count = n;
   }
   __syncthreads();
-  // soft-max partials: thread t looks at position t of every head
-  const uint32_t t = threadIdx.x;
-  float mx[G], sum[G];
+  const uint32_t n_passes = pass_count;
+  if (n_passes == 0) return;
+  attn_request_tile(ks, passes[0].k, passes[0].npos, tid);
+  attn_request_tile(vs, passes[0].v, passes[0].npos, tid);
+  for (uint32_t ip = 0; ip < n_passes; ++ip) {
+    const AttnPass pass = passes[ip];
+    const uint32_t run_first = pass.run_first, run_rows = pass.run_rows, part = pass.part;
+    const int32_t start = pass.start;
+    // the queries as A fragments: MMA row m = (row of the run) * G + (query head of the group)
+    uint32_t qa[8][4];
+    int32_t n0 = 0, n1 = 0;                         // positions of this part that MMA rows m0 and m1 may see
+    {
+      const uint32_t rl0 = m0 / G, rl1 = m1 / G;
+      const bool ok0 = rl0 < run_rows, ok1 = rl1 < run_rows;
+      const __nv_bfloat16* q0 = a.q + (size_t(run_first + (ok0 ? rl0 : 0)) * a.nq + kvh * G + m0 % G) * kAttnDim + (lane & 3u) * 2;
+      const __nv_bfloat16* q1 = a.q + (size_t(run_first + (ok1 ? rl1 : 0)) * a.nq + kvh * G + m1 % G) * kAttnDim + (lane & 3u) * 2;
+      if (ok0) n0 = min(kAttnPart, a.row_pos[run_first + rl0] + 1 - start);
+      if (ok1) n1 = min(kAttnPart, a.row_pos[run_first + rl1] + 1 - start);
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float m = t < n ? score[g][t] : -INFINITY;
-#pragma unroll
-    for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+      for (int k = 0; k < 8; ++k) {
+        qa[k][0] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k) : 0u;
+        qa[k][1] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k) : 0u;
+        qa[k][2] = ok0 ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 8) : 0u;
+        qa[k][3] = ok1 ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 8) : 0u;
+      }
+    }
+    cp_async_wait<1>();                             // all but the newest request: this pass's K
     __syncthreads();
-    if (lane == 0) red[warp] = m;
+    const uint32_t p_warp = warp * 32;              // this warp's 32 positions of the part
+    float sc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
+#pragma unroll
+    for (int kq = 0; kq < 4; ++kq) {                // 32 dimensions per step; the four position tiles are independent chains
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        uint32_t b[4];
+        ldsm_x4(ks + attn_tile_offset(p_warp + 8 * nt + (lane & 7u), 4 * kq + (lane >> 3)), b);
+        mma_bf16_16816(sc[nt], qa[2 * kq], b[0], b[1]);
+        mma_bf16_16816(sc[nt], qa[2 * kq + 1], b[2], b[3]);
+      }
+    }
+    // soft-max partials of the warp's 32 positions, per MMA row
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int32_t pos = int32_t(p_warp) + 8 * nt + int32_t(lane & 3u) * 2 + j;
+        sc[nt][j] = pos < n0 ? __fmul_rn(sc[nt][j], scale2) : -INFINITY;
+        sc[nt][2 + j] = pos < n1 ? __fmul_rn(sc[nt][2 + j], scale2) : -INFINITY;
+        mx0 = fmaxf(mx0, sc[nt][j]);
+        mx1 = fmaxf(mx1, sc[nt][2 + j]);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+    const float base0 = mx0 == -INFINITY ? 0.f : mx0, base1 = mx1 == -INFINITY ? 0.f : mx1;
+    float l0 = 0.f, l1 = 0.f;
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      // the weights as the MMA will see them (BF16); the sums are taken over these, so numerator and denominator agree
+      const float p00 = round_bf(exp2_approx(__fsub_rn(sc[nt][0], base0))), p01 = round_bf(exp2_approx(__fsub_rn(sc[nt][1], base0)));
+      const float p10 = round_bf(exp2_approx(__fsub_rn(sc[nt][2], base1))), p11 = round_bf(exp2_approx(__fsub_rn(sc[nt][3], base1)));
+      l0 = __fadd_rn(l0, __fadd_rn(p00, p01));
+      l1 = __fadd_rn(l1, __fadd_rn(p10, p11));
+      pa[nt >> 1][(nt & 1) * 2] = pack_bf(p00, p01);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf(p10, p11);
+    }
+    l0 = __fadd_rn(l0, __shfl_xor_sync(0xFFFFFFFFu, l0, 1));
+    l0 = __fadd_rn(l0, __shfl_xor_sync(0xFFFFFFFFu, l0, 2));
+    l1 = __fadd_rn(l1, __shfl_xor_sync(0xFFFFFFFFu, l1, 1));
+    l1 = __fadd_rn(l1, __shfl_xor_sync(0xFFFFFFFFu, l1, 2));
+    cp_async_wait<0>();
+    __syncthreads();                                // V is in shared memory, and every warp is done with K
+    const bool more = ip + 1 < n_passes;
+    if (more) attn_request_tile(ks, passes[ip + 1].k, passes[ip + 1].npos, tid);
+    float o[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {                   // 16 positions per step
+      const uint32_t vrow = p_warp + 16 * t + ((lane >> 3) & 1u) * 8 + (lane & 7u);
+#pragma unroll
+      for (int dn = 0; dn < 8; ++dn) {              // 16 dimensions per step
+        uint32_t b[4];
+        ldsm_x4_trans(vs + attn_tile_offset(vrow, 2 * dn + (lane >> 4)), b);
+        mma_bf16_16816(o[2 * dn], pa[t], b[0], b[1]);
+        mma_bf16_16816(o[2 * dn + 1], pa[t], b[2], b[3]);
+      }
+    }
+    __syncthreads();                                // every warp is done with V: the merge buffer takes its place
+    {
+      float* mine = merge + size_t(warp) * 16 * kAttnDim;
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        const uint32_t col = 8 * nt + (lane & 3u) * 2;
+        *reinterpret_cast<float2*>(mine + attn_merge_index(m0, col)) = make_float2(o[nt][0], o[nt][1]);
+        *reinterpret_cast<float2*>(mine + attn_merge_index(m1, col)) = make_float2(o[nt][2], o[nt][3]);
+      }
+      if ((lane & 3u) == 0) {
+        ml_sm[warp][m0][0] = mx0; ml_sm[warp][m0][1] = l0;
+        ml_sm[warp][m1][0] = mx1; ml_sm[warp][m1][1] = l1;
+      }
+    }
     __syncthreads();
-    m = red[0];
+    // warp w merges MMA rows w, w + 4, ... (a lane: four dimensions), the four warps' shares in warp order under their
+    // common maximum (maxima and sums are in units of log 2 here and in part_ml)
+    for (uint32_t m = warp; m < run_rows * G; m += kAttnPartThreads / 32) {
+      float wm[kAttnPartThreads / 32];
+      float mx = -INFINITY;
 #pragma unroll
-    for (int w = 1; w < kAttnThreads / 32; ++w) m = fmaxf(m, red[w]);
-    mx[g] = m;
-    const float p = t < n ? expf(__fsub_rn(score[g][t], m)) : 0.f;
-    sum[g] = cta_sum<kAttnThreads>(p, red);
-    if (t < n) score[g][t] = p;
-  }
-  __syncthreads();
-  // values: half a warp per position again (16 lanes x 16 bytes = one V row, eight dimensions per lane); half-warp hw of
-  // the 16 takes positions hw, hw + 16, ..., four rows in flight per lane.  The two halves of a warp are added by one
-  // shuffle, the eight warps through shared memory in warp order.
-  const uint32_t hw = t >> 4;
-  float acc[G][8];
+      for (int w = 0; w < kAttnPartThreads / 32; ++w) { wm[w] = ml_sm[w][m][0]; mx = fmaxf(mx, wm[w]); }
+      if (mx == -INFINITY) continue;                // this row's context ends before this part
+      float den = 0.f;
+      float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
-  for (uint32_t i0 = hw; i0 < n; i0 += 16 * kFlight) {
-    uint4 vv[kFlight];
-#pragma unroll
-    for (int f = 0; f < kFlight; ++f) {
-      const uint32_t i = i0 + 16 * f;
-      vv[f] = i < n ? *reinterpret_cast<const uint4*>(vp + size_t(i) * kAttnDim + l16 * 8) : make_uint4(0, 0, 0, 0);
-    }
-#pragma unroll
-    for (int f = 0; f < kFlight; ++f) {
-      const uint32_t i = i0 + 16 * f;
-      if (i < n) {
-        const uint32_t w[4] = {vv[f].x, vv[f].y, vv[f].z, vv[f].w};
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float p = score[g][i];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            acc[g][2 * e] = __fmaf_rn(p, bf_lo(w[e]), acc[g][2 * e]);
-            acc[g][2 * e + 1] = __fmaf_rn(p, bf_hi(w[e]), acc[g][2 * e + 1]);
-          }
-        }
+      for (int w = 0; w < kAttnPartThreads / 32; ++w) {
+        const float e = wm[w] == -INFINITY ? 0.f : exp2_approx(__fsub_rn(wm[w], mx));
+        den = __fmaf_rn(e, ml_sm[w][m][1], den);
+        const float4 v = *reinterpret_cast<const float4*>(merge + size_t(w) * 16 * kAttnDim + attn_merge_index(m, lane * 4));
+        num.x = __fmaf_rn(e, v.x, num.x);
+        num.y = __fmaf_rn(e, v.y, num.y);
+        num.z = __fmaf_rn(e, v.z, num.z);
+        num.w = __fmaf_rn(e, v.w, num.w);
       }
+      const size_t base = (size_t(run_first + m / G) * a.nq + kvh * G + m % G) * a.max_splits + part;
+      *reinterpret_cast<float4*>(a.part_acc + base * kAttnDim + lane * 4) = num;
+      if (lane == 0) { a.part_ml[base * 2] = mx; a.part_ml[base * 2 + 1] = den; }
     }
-  }
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int e = 0; e < 8; ++e) acc[g][e] = __fadd_rn(acc[g][e], __shfl_xor_sync(0xFFFFFFFFu, acc[g][e], 16));
-  if (warp && half == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc_sm[warp - 1][g][l16 * 8 + e] = acc[g][e];
-  }
-  __syncthreads();
-  if (warp == 0 && half == 0) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float o[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        o[e] = acc[g][e];
-#pragma unroll
-        for (int k = 0; k < kAttnThreads / 32 - 1; ++k) o[e] = __fadd_rn(o[e], acc_sm[k][g][l16 * 8 + e]);
-      }
-      const size_t base = (size_t(row) * a.nq + hq0 + g) * a.max_splits + split;
-      float4* dst = reinterpret_cast<float4*>(a.part_acc + base * kAttnDim + l16 * 8);
-      dst[0] = make_float4(o[0], o[1], o[2], o[3]);
-      dst[1] = make_float4(o[4], o[5], o[6], o[7]);
-      if (l16 == 0) { a.part_ml[base * 2] = mx[g]; a.part_ml[base * 2 + 1] = sum[g]; }
+    if (more) {
+      __syncthreads();                              // the merge buffer has been read: V of the next pass may land there
+      attn_request_tile(vs, passes[ip + 1].v, passes[ip + 1].npos, tid);
     }
   }
 }
 
-// The splits of a (row, query head) merged in split order under their common maximum, one division, BF16 out.
+// The parts of a (row, query head) merged in part order under their common maximum, one division, BF16 out.
 // grid (rows, nq), 128 threads.
 __global__ void __launch_bounds__(kAttnDim)
 attn_combine_kernel(const AttnArgs a) {
   const uint32_t row = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
-  const uint32_t ns = (uint32_t(a.row_pos[row]) + kAttnSplit) / kAttnSplit;   // ceil((pos + 1) / 256)
+  const uint32_t ns = (uint32_t(a.row_pos[row]) + kAttnPart) / kAttnPart;   // ceil((pos + 1) / 128)
   const size_t base = (size_t(row) * a.nq + hq) * a.max_splits;
   float mx = a.part_ml[base * 2];
   for (uint32_t s = 1; s < ns; ++s) mx = fmaxf(mx, a.part_ml[(base + s) * 2]);
   float den = 0.f, num = 0.f;
   for (uint32_t s = 0; s < ns; ++s) {
-    const float e = expf(__fsub_rn(a.part_ml[(base + s) * 2], mx));
+    const float e = exp2f(__fsub_rn(a.part_ml[(base + s) * 2], mx));   // the parts' maxima are in units of log 2
     den = __fmaf_rn(e, a.part_ml[(base + s) * 2 + 1], den);
     num = __fmaf_rn(e, a.part_acc[(base + s) * kAttnDim + d], num);
   }

@@ -92,6 +92,9 @@ def index_frame(frame: bytes, stride: int = 1024, *, keep_words: bool = False):
 
 
 def _lookup_tables(freq):
+    """Prefix sums and the inverse index of every context, the index thinned out so that all contexts' tables together
+    stay around 128 KB (they are read once per symbol on the decoder's serial chain: they have to live in L1).
+    Returns (cum, bucket, log2 of the slots per bucket)."""
     nctx, vocab = freq.shape
     cum = np.empty((nctx, vocab + 1), dtype=np.uint32)
     bucket = np.empty((nctx, 4096), dtype=np.uint16)
@@ -100,7 +103,10 @@ def _lookup_tables(freq):
                                                  _p(bucket, ctypes.c_uint16))
     if status:
         raise base.CodecError(f"invalid frequency tables ({status})")
-    return cum, bucket
+    shift = 4
+    while shift < 8 and nctx * (65536 >> shift) * 2 > 128 * 1024:
+        shift += 1
+    return cum, np.ascontiguousarray(bucket[:, ::1 << (shift - 4)]), shift
 
 
 class CudaContextTensor:
@@ -129,12 +135,14 @@ class CudaContextTensor:
         self.n = math.prod(self.shape)
         # every array of the index goes to the device under its own name; coded streams get their lookup tables
         self.buffers = {name: torch.from_numpy(array).to(self.device) for name, array in indexed.items() if isinstance(array, np.ndarray)}
+        self._bucket_shift = {}
         for kind in ("main", "residual"):
             table = indexed.get(kind + "_freq")
             if table is not None:
-                cum, bucket = _lookup_tables(table)
+                cum, bucket, shift = _lookup_tables(table)
                 self.buffers[kind + "_cum"] = torch.from_numpy(cum).to(self.device)
                 self.buffers[kind + "_bucket"] = torch.from_numpy(bucket).to(self.device)
+                self._bucket_shift[kind] = shift
         self.error = torch.zeros((), device=self.device, dtype=torch.int32)
         self.resident = None
         if fused and words is not None:
@@ -154,10 +162,12 @@ class CudaContextTensor:
         t.main_stream, t.main_bytes = b["main_stream"].data_ptr(), b["main_stream"].numel()
         t.main_states, t.main_offsets = b["main_states"].data_ptr(), b["main_offsets"].data_ptr()
         t.main_cum, t.main_bucket = b["main_cum"].data_ptr(), b["main_bucket"].data_ptr()
+        t.main_bucket_shift = self._bucket_shift["main"]
         t.residual_stream, t.residual_bytes = b["residual_stream"].data_ptr(), b["residual_stream"].numel()
         if self.mode == 128:
             t.residual_states, t.residual_offsets = b["residual_states"].data_ptr(), b["residual_offsets"].data_ptr()
             t.residual_cum, t.residual_bucket = b["residual_cum"].data_ptr(), b["residual_bucket"].data_ptr()
+            t.residual_bucket_shift = self._bucket_shift["residual"]
         return t
 
     def _decode_blocks(self, blocks=None, *, check=True):

@@ -13,7 +13,8 @@ import math
 
 from . import _native
 
-PAGE = 256        # positions per KV page = positions per attention split
+PAGE = 256        # positions per KV page
+PART = 128        # positions per attention CTA pass: two parts per page
 HEAD_DIM = 128
 
 
@@ -68,8 +69,9 @@ class PagedAttention:
             raise ValueError("query heads per kv head must be 1, 2, 4, 5 or 8")
         self.nq, self.nkv, self.max_rows, self.max_pages = nq, nkv, max_rows, max_pages
         self.q = torch.empty(max_rows, nq, HEAD_DIM, device=device, dtype=torch.bfloat16)
-        self.part_acc = torch.empty(max_rows, nq, max_pages, HEAD_DIM, device=device, dtype=torch.float32)
-        self.part_ml = torch.empty(max_rows, nq, max_pages, 2, device=device, dtype=torch.float32)
+        self.max_parts = max_pages * (PAGE // PART)
+        self.part_acc = torch.empty(max_rows, nq, self.max_parts, HEAD_DIM, device=device, dtype=torch.float32)
+        self.part_ml = torch.empty(max_rows, nq, self.max_parts, 2, device=device, dtype=torch.float32)
         self.scratch_bytes = sum(t.numel() * t.element_size() for t in (self.q, self.part_acc, self.part_ml))
 
     def __call__(self, qkv, cos, sin, row_seq, row_pos, page_table, k_pages, v_pages, out, *, max_splits=None):
@@ -84,10 +86,10 @@ class PagedAttention:
         step.k_pages, step.v_pages = k_pages.data_ptr(), v_pages.data_ptr()
         step.q, step.part_acc, step.part_ml, step.out = self.q.data_ptr(), self.part_acc.data_ptr(), self.part_ml.data_ptr(), out.data_ptr()
         step.rows, step.nq, step.nkv, step.head_dim = rows, self.nq, self.nkv, HEAD_DIM
-        # splits launched per (row, kv head) = the stride of the partial buffers in this call; rows shorter than that
-        # leave their surplus CTAs at once.  A caller that knows every row is short passes fewer than max_pages.
-        step.max_splits = min(self.max_pages, page_table.shape[1]) if max_splits is None else int(max_splits)
-        if not 1 <= step.max_splits <= self.max_pages:
+        # parts (128 positions each) launched per (row group, kv head) = the stride of the partial buffers in this call;
+        # rows shorter than that leave their surplus CTAs at once.  A caller that knows every row is short passes fewer.
+        step.max_splits = min(self.max_parts, page_table.shape[1] * (PAGE // PART)) if max_splits is None else int(max_splits)
+        if not 1 <= step.max_splits <= self.max_parts:
             raise ValueError("max_splits outside the scratch that was allocated")
         step.scaling = 1.0 / math.sqrt(HEAD_DIM)
         st = _native.lib().grb_attn_decode_bf16(ctypes.byref(step), _stream(qkv))

@@ -113,6 +113,10 @@ typedef struct grb_bctx_tensor {
   const uint8_t* residual_stream; uint64_t residual_bytes;     /* raw6 bytes or the conditional stream */
   const uint32_t* residual_states; const uint32_t* residual_offsets;  /* mode 128 only */
   const uint32_t* residual_cum;    const uint16_t* residual_bucket;   /* mode 128 only */
+  /* log2 of the slots per bucket of the two inverse indexes; 0 = 4, the tables grb_bctx_build_lookup writes.  A caller
+   * may thin them out (every 2^(shift-4)-th entry, [nctx][65536 >> shift]) so that all contexts' tables stay in L1:
+   * the walk is one serial chain per lane, and a first-level miss costs it an L2 round trip per symbol. */
+  uint32_t main_bucket_shift, residual_bucket_shift;
 } grb_bctx_tensor;
 
 /* Replaces the launch of decode_words, cr/bitexact_context_gpu.py:130-152 / bitexact_context_gpu_kernels.py:
@@ -306,8 +310,8 @@ typedef struct grb_attn_step {
   void* k_pages;              /* BF16 [pages][nkv][256][128] */
   void* v_pages;
   void* q;                    /* scratch: BF16 [rows][nq][128] */
-  float* part_acc;            /* scratch: [rows][nq][max_splits][128] */
-  float* part_ml;             /* scratch: [rows][nq][max_splits][2] */
+  float* part_acc;            /* scratch: [rows][nq][max_splits][128]; a split is 128 positions, half a page */
+  float* part_ml;             /* scratch: [rows][nq][max_splits][2]; max_splits <= 2 * max_pages */
   void* out;                  /* BF16 [rows][nq * 128] */
   uint32_t rows, nq, nkv, head_dim, max_splits;   /* head_dim must be 128; nq / nkv in {1, 2, 4, 5, 8} */
   float scaling;              /* 1 / sqrt(head_dim) */
