@@ -113,46 +113,21 @@ struct ByteWindow {
   }
 };
 
-// Where the main stream's tables are read from.  Global: the caller's arrays (through L1).  Shared: a copy the CTA
-// made at its start - prefix sums as 16-bit values (65536 stored as 0: a symbol's upper bound is never 0 otherwise) and
-// the inverse index thinned to what fits - for frames whose contexts' tables fit in one SM's shared memory; there a
-// look-up costs a shared-memory access instead of an L1 or L2 round trip, twice per symbol on the serial chain.
-struct TablesGlobal {
-  const uint32_t* cum;      // [nctx][vocab + 1]
-  const uint16_t* bucket;   // [nctx][65536 >> shift]
-  uint32_t shift, vocab1;
-  __device__ __forceinline__ uint32_t first(uint32_t ctx, uint32_t slot) const {
-    return __ldg(bucket + (size_t(ctx) << (16 - shift)) + (slot >> shift));
-  }
-  __device__ __forceinline__ uint32_t bound(uint32_t ctx, uint32_t s) const { return __ldg(cum + size_t(ctx) * vocab1 + s); }
-};
-struct TablesShared {
-  uint32_t cum_at, bucket_at;   // shared-memory byte addresses
-  uint32_t shift, cum_stride;   // cum_stride: 16-bit entries per context (odd number of 32-bit words)
-  __device__ __forceinline__ uint32_t first(uint32_t ctx, uint32_t slot) const {
-    return lds_u16(bucket_at + (((ctx << (16 - shift)) + (slot >> shift)) << 1));
-  }
-  __device__ __forceinline__ uint32_t bound(uint32_t ctx, uint32_t s) const {
-    const uint32_t v = lds_u16(cum_at + ((ctx * cum_stride + s) << 1));
-    return s && v == 0 ? 65536u : v;
-  }
-  static __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return v;
-  }
-};
-
-// One decoding step on the look-ahead window.  The scan ends at the latest on the table's last entry (65536).
-template <uint32_t VOCAB, class Tables>
-__device__ __forceinline__ uint32_t bctx_symbol_fast(const Tables& t, uint32_t ctx, uint32_t& x, ByteWindow& w, uint32_t& ip) {
+// One decoding step on the look-ahead window, on one context's tables: prefix sums `cum` (vocab + 1 entries) and the
+// inverse index `bucket` (65536 >> shift entries).  The scan ends at the latest on the table's last entry (65536).
+// (Measured alternatives that did not pay: a bisection between the owners of this bucket's and the next bucket's first
+// slots - the warp waits for its slowest lane either way, and the common case got longer - and a copy of the tables in
+// shared memory: the step is bound by its chain of dependent instructions, not by where the tables live.)
+template <uint32_t VOCAB>
+__device__ __forceinline__ uint32_t bctx_symbol_fast(const uint32_t* cum, const uint16_t* bucket, uint32_t shift, uint32_t& x,
+                                                     ByteWindow& w, uint32_t& ip) {
   const uint32_t slot = x & 0xFFFFu;
-  uint32_t s = min(t.first(ctx, slot), VOCAB - 1);
-  uint32_t lo = t.bound(ctx, s), hi = t.bound(ctx, s + 1);
+  uint32_t s = min(uint32_t(__ldg(bucket + (slot >> shift))), VOCAB - 1);
+  uint32_t lo = __ldg(cum + s), hi = __ldg(cum + s + 1);
   while (hi <= slot && s + 1 < VOCAB) {
     ++s;
     lo = hi;
-    hi = t.bound(ctx, s + 1);
+    hi = __ldg(cum + s + 1);
   }
   x = (hi - lo) * (x >> 16) + (slot - lo);
   w.feed(x, ip, min(2u, (uint32_t(__clz(int(x | 1u))) - 1u) >> 3));
@@ -160,10 +135,9 @@ __device__ __forceinline__ uint32_t bctx_symbol_fast(const Tables& t, uint32_t c
 }
 
 // `groups` runs of eight symbols from (row, col) on; leaves x, ip (and rx, rip) where the plain loop can carry on.
-template <bool RAW6, class MainTables>
-__device__ __forceinline__ void bctx_block_fast(const BctxArgs& a, const MainTables& mt, uint32_t groups, uint64_t start, uint32_t& row,
-                                                uint32_t& col, uint32_t& x, uint64_t& ip64, uint32_t& rx, uint64_t& rip64, uint16_t* out,
-                                                uint32_t& bad) {
+template <bool RAW6>
+__device__ __forceinline__ void bctx_block_fast(const BctxArgs& a, uint32_t groups, uint64_t start, uint32_t& row, uint32_t& col,
+                                                uint32_t& x, uint64_t& ip64, uint32_t& rx, uint64_t& rip64, uint16_t* out, uint32_t& bad) {
   ByteWindow mw, rw;
   uint32_t ip = mw.open(a.main_s.bytes, a.main_s.size, uint32_t(ip64));
   const uint32_t skew = ip - uint32_t(ip64);
@@ -172,18 +146,27 @@ __device__ __forceinline__ void bctx_block_fast(const BctxArgs& a, const MainTab
     rip = rw.open(a.resid_s.bytes, a.resid_s.size, uint32_t(rip64));
     rskew = rip - uint32_t(rip64);
   }
-  const TablesGlobal rt{a.resid_s.cum, a.resid_s.bucket, a.resid_s.shift, 65};
   const uint32_t cols = a.cols, nc = a.nc, top_ctx = a.main_contexts - 1;
+  const uint32_t mshift = a.main_s.shift, rshift = a.resid_s.shift;
+  const uint32_t* const mcum = a.main_s.cum;
+  const uint16_t* const mbucket = a.main_s.bucket;
   const uint16_t* raw = reinterpret_cast<const uint16_t*>(a.resid_s.bytes + (start >> 2) * 3);   // 6 bytes per group
   for (uint32_t g = 0; g < groups; ++g) {
-    uint32_t ctx[8];
+    // the eight contexts and the eight raw residuals first: nothing of this depends on the decoder's state
+    const uint32_t here = uint32_t(__ldg(a.row_class + row)) * nc;
+    const uint32_t below = col + 7 >= cols ? uint32_t(__ldg(a.row_class + row + 1)) * nc : here;   // a group crosses at most one row end (cols >= 8)
+    uint32_t ctx[8], worst = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {               // a group crosses at most one row end (cols >= 8)
-      uint32_t c = col + j, r = row;
-      if (c >= cols) { c -= cols; ++r; }
-      const uint32_t v = uint32_t(__ldg(a.row_class + r)) * nc + __ldg(a.col_class + c);
-      if (v > top_ctx) bad |= kStatusBadSymbol;
-      ctx[j] = min(v, top_ctx);
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t c = col + j;
+      const bool wrapped = c >= cols;
+      ctx[j] = (wrapped ? below : here) + __ldg(a.col_class + (wrapped ? c - cols : c));
+      worst = max(worst, ctx[j]);
+    }
+    if (worst > top_ctx) {          // labels outside the model: flag, and stay inside the tables
+      bad |= kStatusBadSymbol;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ctx[j] = min(ctx[j], top_ctx);
     }
     uint32_t r32 = 0, r16 = 0;
     if (RAW6) {
@@ -194,12 +177,12 @@ __device__ __forceinline__ void bctx_block_fast(const BctxArgs& a, const MainTab
     uint32_t packed[4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const uint32_t sym = bctx_symbol_fast<1024>(mt, ctx[j], x, mw, ip);
+      const uint32_t sym = bctx_symbol_fast<1024>(mcum + ctx[j] * 1025u, mbucket + (size_t(ctx[j]) << (16 - mshift)), mshift, x, mw, ip);
       uint32_t res;
       if (RAW6) {
         res = j < 5 ? (r32 >> (26 - 6 * j)) & 63u : j == 5 ? ((r32 & 3u) << 4) | (r16 >> 12) : j == 6 ? (r16 >> 6) & 63u : r16 & 63u;
       } else {
-        res = bctx_symbol_fast<64>(rt, sym, rx, rw, rip);
+        res = bctx_symbol_fast<64>(a.resid_s.cum + sym * 65u, a.resid_s.bucket + (size_t(sym) << (16 - rshift)), rshift, rx, rw, rip);
       }
       const uint32_t word = ((sym << 5) | (res & 31u) | ((res & 32u) << 10)) & 0xFFFFu;
       if (j & 1) packed[j >> 1] |= word << 16;
@@ -217,8 +200,7 @@ __device__ __forceinline__ void bctx_block_fast(const BctxArgs& a, const MainTab
   }
 }
 
-template <class MainTables>
-__device__ __forceinline__ void bctx_decode_lane(const BctxArgs& a, const MainTables& mt) {
+__global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
   const uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= a.count) return;
   const uint64_t block = a.block_ids ? uint64_t(a.block_ids[i]) : i;
@@ -247,8 +229,8 @@ __device__ __forceinline__ void bctx_decode_lane(const BctxArgs& a, const MainTa
   if (wide && a.cols >= 8 && (reinterpret_cast<uintptr_t>(a.resid_s.bytes) & 1u) == 0 && a.main_s.size < 0xFFFFFF00ull &&
       a.resid_s.size < 0xFFFFFF00ull) {
     const uint32_t groups = steps >> 3;
-    if (a.raw6) bctx_block_fast<true>(a, mt, groups, start, row, col, x, ip, rx, rip, out, bad);
-    else bctx_block_fast<false>(a, mt, groups, start, row, col, x, ip, rx, rip, out, bad);
+    if (a.raw6) bctx_block_fast<true>(a, groups, start, row, col, x, ip, rx, rip, out, bad);
+    else bctx_block_fast<false>(a, groups, start, row, col, x, ip, rx, rip, out, bad);
     done = groups << 3;
   }
   for (uint32_t step = done; step < steps && !bad; ++step) {
@@ -287,35 +269,6 @@ __device__ __forceinline__ void bctx_decode_lane(const BctxArgs& a, const MainTa
     }
   }
   if (bad) atomicOr(a.status, bad);
-}
-
-__global__ void __launch_bounds__(64) bctx_decode_kernel(const BctxArgs a) {
-  bctx_decode_lane(a, TablesGlobal{a.main_s.cum, a.main_s.bucket, a.main_s.shift, 1025});
-}
-
-// The same walk with the main stream's tables copied into shared memory first: prefix sums [nctx][1026] and the inverse
-// index [nctx][65536 >> shift] as 16-bit values, `shift` chosen by the host so that both fit.  One CTA per SM; the
-// host sizes the CTA so that the blocks of the call spread over all SMs.
-constexpr uint32_t kBctxCumStride = 1026;   // 16-bit entries per context: 1025 used; 513 32-bit words, odd, so contexts spread over the banks
-__host__ __device__ inline uint32_t bctx_shared_bytes(uint32_t nctx, uint32_t shift) {
-  return nctx * (kBctxCumStride + (65536u >> shift)) * 2u;
-}
-__global__ void __launch_bounds__(512) bctx_decode_shared_kernel(const BctxArgs a, uint32_t shift) {
-  extern __shared__ __align__(16) uint16_t bctx_tables[];
-  const uint32_t nctx = a.main_contexts, per = 65536u >> shift;
-  uint16_t* cum16 = bctx_tables;
-  uint16_t* bucket16 = bctx_tables + size_t(nctx) * kBctxCumStride;
-  for (uint32_t e = threadIdx.x; e < nctx * 1025u; e += blockDim.x) {
-    const uint32_t c = e / 1025u, k = e - c * 1025u;
-    cum16[c * kBctxCumStride + k] = uint16_t(__ldg(a.main_s.cum + e));
-  }
-  const uint32_t thin = shift - a.main_s.shift;    // the caller's index has 65536 >> main_s.shift entries per context
-  for (uint32_t e = threadIdx.x; e < nctx * per; e += blockDim.x) {
-    const uint32_t c = e / per, k = e - c * per;
-    bucket16[e] = __ldg(a.main_s.bucket + (size_t(c) << (16 - a.main_s.shift)) + (size_t(k) << thin));
-  }
-  __syncthreads();
-  bctx_decode_lane(a, TablesShared{smem_u32(cum16), smem_u32(bucket16), shift, kBctxCumStride});
 }
 
 }  // namespace grb

@@ -25,19 +25,22 @@ constexpr int kWideWarpEpilogue = 20;  // 4 warps: warp % 4 = the tensor-memory 
 // Tensor memory: columns [0, 256) accumulators, FP32: an item has two, one per MMA issuer (even chunks, odd chunks;
 // the epilogue adds them), NB columns each.  Up to NB = 64 two items fit (one being multiplied, one being drained);
 // at NB = 128 there is room for one, and the issuers wait for the drain at an item boundary while the decoders fill
-// the operand stages.  Columns [256, 512): the decoded weights of kWideStages chunks, 64 columns each (two 128 x 64
-// atoms, two BF16 per column).
+// the operand stages.  Columns [256, 512): the decoded weights of four chunks, 64 columns each (two 128 x 64 atoms, two
+// BF16 per column).  (The narrow tiles would leave room for six or seven stages and a deeper activation ring; measured at
+// NB = 16 with 7 stages, 8 activation stages and 6 requests in flight, every M = 1 launch got slower, gate|up by 4.6 us.)
 constexpr int kWideNextBlobs = 8;      // blobs per CTA of the next launch that a finishing CTA asks the L2 for
 constexpr uint32_t kWideTmemCols = 512;
-constexpr uint32_t kWideOperandCol = 256;
+template <int NB>
 constexpr int kWideStages = 4;
+template <int NB>
+constexpr uint32_t kWideOperandCol = kWideTmemCols - 64u * kWideStages<NB>;
 
 // Shared-memory plan: a ring of chunk blobs and a ring of activation tiles (two NB x 64 atoms per chunk), the
 // latter requested kXLag chunks ahead of the weights they will meet (they come from L2 with a latency of about a
 // microsecond).
 template <int MODE, int NB>
 struct BxqSmem {
-  static constexpr int kOp = (MODE == kUmma) ? kWideStages : 0;
+  static constexpr int kOp = (MODE == kUmma) ? kWideStages<NB> : 0;
   static constexpr int kX = (MODE == kUmma) ? (NB <= 64 ? 4 : 3) : 0;
   static constexpr int kXLag = 2;
   static constexpr uint32_t kXStage = 2 * NB * 128;
@@ -61,7 +64,7 @@ struct BxqSmem {
   static_assert(MODE != kUmma || kIn >= 4, "ring too shallow");
   // what keeps the activation loader at most one barrier phase behind the MMA issuer (see its role below)
   static_assert(MODE != kUmma || (kXLag < kX && kOp + kXLag + 1 > kX), "activation ring and lag do not fit the operand ring");
-  static_assert(MODE != kUmma || 2 * NB * (NB <= 64 ? 2 : 1) <= int(kWideOperandCol), "accumulators overlap the operand columns");
+  static_assert(MODE != kUmma || 2 * NB * (NB <= 64 ? 2 : 1) <= int(kWideOperandCol<NB>), "accumulators overlap the operand columns");
   static_assert(8 * nbars + 64 <= 512, "barrier area");
   static_assert(MODE != kUmma || (1 + kRing) * NB * 512u <= bars, "the closing reduction's tiles would overwrite the barriers");
   static_assert(alloc <= 232448, "exceeds the 227 KB of shared memory a CTA may opt into");
@@ -378,7 +381,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     const uint32_t raw_at = BXQ_RAW_AT + ((2 * q) * BXR_ROWS + r) * 16;
     const uint32_t code_at = BXQ_CODES_AT + 4 * (q * BXR_ROWS + r);
     // this lane's 16 operand columns: lane = row, columns = its 32 weights inside the chunk's atom
-    const uint32_t operand_at = ((rg * 32u) << 16) + kWideOperandCol + (q >> 1) * 32 + (q & 1) * 16;
+    const uint32_t operand_at = ((rg * 32u) << 16) + kWideOperandCol<NB> + (q >> 1) * 32 + (q & 1) * 16;
     bool live = true;
     uint32_t next_base = first_base;
     for (uint32_t u = unit_begin; u < unit_end && live;) {
@@ -539,7 +542,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           if (!ctx.wait(bar_op_full + 8 * so, pho)) { live = false; break; }
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t a_tmem = tmem_base + kWideOperandCol + so * 64;
+            const uint32_t a_tmem = tmem_base + kWideOperandCol<NB> + so * 64;
             const uint64_t bdesc = umma_desc_sw128(smem + L::xs + sx * L::kXStage);
             uint32_t accumulate = i >= 2 ? 1u : 0u;
 #pragma unroll

@@ -214,8 +214,6 @@ int device_sm_count(int dev) {
   return sms[dev];
 }
 
-constexpr uint32_t kBctxSharedLimit = 220u * 1024u;   // dynamic shared memory the table-resident decode kernel may ask for
-
 template <int G>
 int attn_part_launch(const AttnArgs& a, cudaStream_t stream) {
   static std::once_flag once[64];
@@ -271,26 +269,6 @@ int grb_bctx_decode_words(const grb_bctx_tensor* t, const int64_t* block_ids, ui
   a.out = out;
   a.status = status;
   const auto stream = static_cast<cudaStream_t>(cuda_stream);
-  // Large calls on frames whose main tables fit in one SM's shared memory read them from there.
-  int dev = 0, sms = 0;
-  if (count >= 2048 && cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && (sms = device_sm_count(dev)) > 0) {
-    uint32_t shift = main_shift;
-    while (shift < 9 && bctx_shared_bytes(a.main_contexts, shift) > kBctxSharedLimit) ++shift;
-    if (bctx_shared_bytes(a.main_contexts, shift) <= kBctxSharedLimit) {
-      static std::once_flag once[64];
-      static int prepared[64];
-      std::call_once(once[dev], [&] {
-        prepared[dev] = cuda_status(cudaFuncSetAttribute(bctx_decode_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kBctxSharedLimit)));
-      });
-      if (prepared[dev]) return prepared[dev];
-      // one CTA per SM (the tables take most of its shared memory): lanes per CTA so that one wave covers the call
-      uint64_t threads = (count + uint64_t(sms) - 1) / uint64_t(sms);
-      threads = std::min<uint64_t>(512, std::max<uint64_t>(64, (threads + 31) / 32 * 32));
-      const unsigned grid = unsigned((count + threads - 1) / threads);
-      bctx_decode_shared_kernel<<<grid, unsigned(threads), bctx_shared_bytes(a.main_contexts, shift), stream>>>(a, shift);
-      return cuda_status(cudaGetLastError());
-    }
-  }
   const unsigned grid = unsigned((count + 63) / 64);
   bctx_decode_kernel<<<grid, 64, 0, stream>>>(a);
   return cuda_status(cudaGetLastError());
@@ -404,19 +382,12 @@ int grb_dense_gemv_bf16(const void* w, int64_t ldw, uint32_t rows, uint32_t cols
   if ((cols & 7) || ldw < int64_t(cols) || ldx < int64_t(cols) || ldy < int64_t(rows) || (ldw & 7) || (ldx & 7) ||
       (reinterpret_cast<uintptr_t>(w) & 15) || (reinterpret_cast<uintptr_t>(x) & 15))
     return GRB_ERR_ARGUMENT;
-  static std::mutex mu;
-  static int sms[64] = {0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_status(e);
   if (dev < 0 || dev >= 64) return GRB_ERR_UNSUPPORTED;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (!sms[dev]) {
-      e = cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
-      if (e != cudaSuccess) return cuda_status(e);
-    }
-  }
+  const int sm_count = device_sm_count(dev);
+  if (sm_count <= 0) return GRB_ERR_CUDA;
   DenseArgs a{};
   a.w = static_cast<const __nv_bfloat16*>(w);
   a.x = static_cast<const __nv_bfloat16*>(x);
@@ -427,9 +398,9 @@ int grb_dense_gemv_bf16(const void* w, int64_t ldw, uint32_t rows, uint32_t cols
   a.ldy = ldy;
   a.rows = rows;
   a.cols = cols;
-  a.slices = dense_slices(rows, cols, uint32_t(sms[dev]));
+  a.slices = dense_slices(rows, cols, uint32_t(sm_count));
   const uint32_t groups = (rows + kDenseWarps / a.slices - 1) / (kDenseWarps / a.slices);
-  const uint32_t ctas = uint32_t(sms[dev]);
+  const uint32_t ctas = uint32_t(sm_count);
   const auto stream = static_cast<cudaStream_t>(cuda_stream);
   switch (m) {
     case 1: return dense_launch<1>(a, groups, ctas, stream);
