@@ -204,6 +204,25 @@ int dense_launch(const DenseArgs& a, uint32_t groups, uint32_t sms, cudaStream_t
   return wide ? dense_launch_as<M, true>(a, groups, sms, stream) : dense_launch_as<M, false>(a, groups, sms, stream);
 }
 
+// Launch of a decode-step kernel with programmatic stream serialisation: the kernel calls
+// griddepcontrol.launch_dependents and griddepcontrol.wait before anything else, so the kernel after it in the stream
+// (a fused linear, mostly) is set up and already streams its first weights on the SMs this one leaves idle, and every
+// kernel still sees the complete output of the one before it.
+template <class... Params, class... Args>
+int launch_step(void (*kernel)(Params...), dim3 grid, dim3 block, uint32_t smem_bytes, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cuda_status(cudaLaunchKernelEx(&cfg, kernel, Params(args)...));
+}
+
 // SM count of a device, looked up once.
 int device_sm_count(int dev) {
   static std::mutex mu;
@@ -226,8 +245,8 @@ int attn_part_launch(const AttnArgs& a, cudaStream_t stream) {
   if (prepared[dev]) return prepared[dev];
   constexpr uint32_t kRowsPerGroup = 16 / G;
   const uint32_t columns = (a.max_splits + kAttnPartsPerCta - 1) / kAttnPartsPerCta;
-  attn_part_kernel<G><<<dim3(columns, a.nkv, (a.rows + kRowsPerGroup - 1) / kRowsPerGroup), kAttnPartThreads, kAttnPartSmem, stream>>>(a);
-  return cuda_status(cudaGetLastError());
+  return launch_step(attn_part_kernel<G>, dim3(columns, a.nkv, (a.rows + kRowsPerGroup - 1) / kRowsPerGroup), dim3(kAttnPartThreads),
+                     kAttnPartSmem, stream, a);
 }
 
 }  // namespace
@@ -424,25 +443,23 @@ int grb_rmsnorm_bf16(void* h, int64_t ldh, const void* delta, int64_t ldd, const
   if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(out) |
        reinterpret_cast<uintptr_t>(delta)) & 15)
     return GRB_ERR_ARGUMENT;
-  rmsnorm_kernel<<<rows, kRmsThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<__nv_bfloat16*>(h), ldh, static_cast<const __nv_bfloat16*>(delta), ldd, static_cast<const __nv_bfloat16*>(weight),
-      static_cast<__nv_bfloat16*>(out), ldo, hidden, eps, unit_offset);
-  return cuda_status(cudaGetLastError());
+  return launch_step(rmsnorm_kernel, dim3(rows), dim3(kRmsThreads), 0, static_cast<cudaStream_t>(cuda_stream),
+                     static_cast<__nv_bfloat16*>(h), ldh, static_cast<const __nv_bfloat16*>(delta), ldd,
+                     static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), ldo, hidden, eps, unit_offset);
 }
 
 int grb_silu_mul_bf16(const void* gate_up, int64_t ldg, void* out, int64_t ldo, uint32_t rows, uint32_t f, void* cuda_stream) {
   if (!gate_up || !out || !rows || !f || (f & 7) || ldg < 2 * int64_t(f) || ldo < int64_t(f) || (ldg & 7) || (ldo & 7)) return GRB_ERR_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) return GRB_ERR_ARGUMENT;
   if (rows > 65535) return GRB_ERR_UNSUPPORTED;
-  silu_mul_kernel<<<dim3(((f >> 3) + 255) / 256, rows), 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), ldg, static_cast<__nv_bfloat16*>(out), ldo, f);
-  return cuda_status(cudaGetLastError());
+  return launch_step(silu_mul_kernel, dim3(((f >> 3) + 255) / 256, rows), dim3(256), 0, static_cast<cudaStream_t>(cuda_stream),
+                     static_cast<const __nv_bfloat16*>(gate_up), ldg, static_cast<__nv_bfloat16*>(out), ldo, f);
 }
 
 int grb_argmax_bf16(const void* logits, int64_t ld, uint32_t rows, uint32_t vocab, int32_t* out, void* cuda_stream) {
   if (!logits || !out || !rows || !vocab || ld < int64_t(vocab) || (ld & 7) || (reinterpret_cast<uintptr_t>(logits) & 15)) return GRB_ERR_ARGUMENT;
-  argmax_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab, out);
-  return cuda_status(cudaGetLastError());
+  return launch_step(argmax_kernel, dim3(rows), dim3(kArgmaxThreads), 0, static_cast<cudaStream_t>(cuda_stream),
+                     static_cast<const __nv_bfloat16*>(logits), ld, vocab, out);
 }
 
 int grb_attn_decode_bf16(const grb_attn_step* s, void* cuda_stream) {
@@ -477,8 +494,7 @@ int grb_attn_decode_bf16(const grb_attn_step* s, void* cuda_stream) {
   a.max_splits = s->max_splits;
   a.scaling = s->scaling;
   const auto stream = static_cast<cudaStream_t>(cuda_stream);
-  attn_prep_kernel<<<dim3(a.rows, a.nq + 2 * a.nkv), kAttnDim, 0, stream>>>(a);
-  int st = cuda_status(cudaGetLastError());
+  int st = launch_step(attn_prep_kernel, dim3(a.rows, (a.nq + 2 * a.nkv + kPrepHeadsPerCta - 1) / kPrepHeadsPerCta), dim3(kAttnDim), 0, stream, a);
   if (st) return st;
   switch (a.nq / a.nkv) {
     case 1: st = attn_part_launch<1>(a, stream); break;
@@ -489,8 +505,7 @@ int grb_attn_decode_bf16(const grb_attn_step* s, void* cuda_stream) {
     default: return GRB_ERR_UNSUPPORTED;
   }
   if (st) return st;
-  attn_combine_kernel<<<dim3(a.rows, a.nq), kAttnDim, 0, stream>>>(a);
-  return cuda_status(cudaGetLastError());
+  return launch_step(attn_combine_kernel, dim3(a.rows * a.nq), dim3(kCombineWarps * 32), 0, stream, a);
 }
 
 // ---- allocation-free variant ----------------------------------------------------------------------

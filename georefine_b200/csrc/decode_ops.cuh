@@ -35,6 +35,14 @@ __device__ __forceinline__ uint32_t pack_bf(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// First thing in every kernel of this file (they are launched with programmatic stream serialisation): let the next
+// kernel of the stream begin its set-up, then wait until the kernel before this one has finished and its writes are
+// visible.
+__device__ __forceinline__ void step_kernel_entry() {
+  grid_dependents_may_launch();
+  grid_dependency_wait();
+}
+
 // Sum over the CTA in a fixed order: lanes by xor butterfly, then the warps' sums in warp order.  Every thread gets it.
 template <int THREADS>
 __device__ __forceinline__ float cta_sum(float v, float* scratch /* THREADS / 32 floats */) {
@@ -58,6 +66,7 @@ constexpr int kRmsVectors = 8;  // hidden <= 256 * 8 * 8 = 16384
 __global__ void __launch_bounds__(kRmsThreads)
 rmsnorm_kernel(__nv_bfloat16* h, int64_t ldh, const __nv_bfloat16* delta, int64_t ldd, const __nv_bfloat16* w, __nv_bfloat16* out,
                int64_t ldo, uint32_t hidden, float eps, int unit_offset) {
+  step_kernel_entry();
   __shared__ float scratch[kRmsThreads / 32];
   const uint32_t row = blockIdx.x, vectors = hidden >> 3;
   uint4* hr = reinterpret_cast<uint4*>(h + row * ldh);
@@ -108,6 +117,7 @@ rmsnorm_kernel(__nv_bfloat16* h, int64_t ldh, const __nv_bfloat16* delta, int64_
 // ---- SwiGLU: out = bf16(bf16(silu(gate)) * up), gate|up side by side in one row --------------------------
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __nv_bfloat16* gu, int64_t ldg, __nv_bfloat16* out, int64_t ldo, uint32_t f) {
+  step_kernel_entry();
   const uint32_t row = blockIdx.y, v = blockIdx.x * blockDim.x + threadIdx.x;
   if (v >= (f >> 3)) return;
   const uint4 g = reinterpret_cast<const uint4*>(gu + row * ldg)[v];
@@ -127,6 +137,7 @@ silu_mul_kernel(const __nv_bfloat16* gu, int64_t ldg, __nv_bfloat16* out, int64_
 constexpr int kArgmaxThreads = 1024;
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_kernel(const __nv_bfloat16* logits, int64_t ld, uint32_t vocab, int32_t* out) {
+  step_kernel_entry();
   __shared__ float best_v[kArgmaxThreads / 32];
   __shared__ int best_i[kArgmaxThreads / 32];
   const __nv_bfloat16* r = logits + blockIdx.x * ld;
@@ -184,28 +195,40 @@ struct AttnArgs {
 
 // Rotary embedding of the query and key heads (rotate-half convention, each product and the sum rounded to BF16 as
 // the BF16 model does), queries to `q`, keys and values appended to the row's page at its position.
-// grid (rows, nq + 2 nkv), 128 threads.
+// grid (rows, ceil((nq + 2 nkv) / 2)), 128 threads: 64 threads per head (a thread owns dimensions d and d + 64, the two
+// that the rotation pairs), two heads per CTA (more per CTA was measured slower on a one-row step).
+constexpr int kPrepHeadsPerCta = 2;
 __global__ void __launch_bounds__(kAttnDim)
 attn_prep_kernel(const AttnArgs a) {
-  __shared__ float xs[kAttnDim];
-  const uint32_t row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+  step_kernel_entry();
+  const uint32_t row = blockIdx.x, d = threadIdx.x & 63u;
   const int32_t pos = a.row_pos[row], slot = a.row_seq[row];
-  const __nv_bfloat16* src = a.qkv + row * a.ldq + size_t(head) * kAttnDim;
   const int32_t page = a.page_table[size_t(slot) * a.max_pages + uint32_t(pos) / kAttnSplit];
-  const size_t in_page = size_t(uint32_t(pos) % kAttnSplit) * kAttnDim + d;
-  if (head >= a.nq + a.nkv) {  // value head: copy
-    const uint32_t vh = head - a.nq - a.nkv;
-    a.v_pages[(size_t(page) * a.nkv + vh) * kAttnSplit * kAttnDim + in_page] = src[d];
-    return;
+  const size_t in_page = size_t(uint32_t(pos) % kAttnSplit) * kAttnDim;
+  const float c0 = __bfloat162float(a.cos_table[size_t(pos) * kAttnDim + d]), c1 = __bfloat162float(a.cos_table[size_t(pos) * kAttnDim + d + 64]);
+  const float s0 = __bfloat162float(a.sin_table[size_t(pos) * kAttnDim + d]), s1 = __bfloat162float(a.sin_table[size_t(pos) * kAttnDim + d + 64]);
+  const uint32_t heads = a.nq + 2 * a.nkv;
+#pragma unroll
+  for (int i = 0; i < kPrepHeadsPerCta / 2; ++i) {
+    const uint32_t head = blockIdx.y * kPrepHeadsPerCta + 2 * i + (threadIdx.x >> 6);
+    if (head >= heads) break;
+    const __nv_bfloat16* src = a.qkv + row * a.ldq + size_t(head) * kAttnDim;
+    const __nv_bfloat16 lo = src[d], hi = src[d + 64];
+    if (head >= a.nq + a.nkv) {  // value head: copy
+      __nv_bfloat16* dst = a.v_pages + (size_t(page) * a.nkv + (head - a.nq - a.nkv)) * kAttnSplit * kAttnDim + in_page;
+      dst[d] = lo;
+      dst[d + 64] = hi;
+      continue;
+    }
+    const float x0 = __bfloat162float(lo), x1 = __bfloat162float(hi);
+    // out[d] = x[d] cos[d] - x[d + 64] sin[d];  out[d + 64] = x[d + 64] cos[d + 64] + x[d] sin[d + 64]
+    const __nv_bfloat16 o0 = __float2bfloat16_rn(__fadd_rn(round_bf(__fmul_rn(x0, c0)), round_bf(__fmul_rn(-x1, s0))));
+    const __nv_bfloat16 o1 = __float2bfloat16_rn(__fadd_rn(round_bf(__fmul_rn(x1, c1)), round_bf(__fmul_rn(x0, s1))));
+    __nv_bfloat16* dst = head < a.nq ? a.q + (size_t(row) * a.nq + head) * kAttnDim
+                                     : a.k_pages + (size_t(page) * a.nkv + (head - a.nq)) * kAttnSplit * kAttnDim + in_page;
+    dst[d] = o0;
+    dst[d + 64] = o1;
   }
-  const float x = __bfloat162float(src[d]);
-  xs[d] = x;
-  __syncthreads();
-  const float c = __bfloat162float(a.cos_table[size_t(pos) * kAttnDim + d]), s = __bfloat162float(a.sin_table[size_t(pos) * kAttnDim + d]);
-  const float rot = d < kAttnDim / 2 ? -xs[d + kAttnDim / 2] : xs[d - kAttnDim / 2];
-  const __nv_bfloat16 o = __float2bfloat16_rn(__fadd_rn(round_bf(__fmul_rn(x, c)), round_bf(__fmul_rn(rot, s))));
-  if (head < a.nq) a.q[(size_t(row) * a.nq + head) * kAttnDim + d] = o;
-  else a.k_pages[(size_t(page) * a.nkv + (head - a.nq)) * kAttnSplit * kAttnDim + in_page] = o;
 }
 
 // ---- one part (128 positions) of the context, for one kv head and a group of rows ----------------------------
@@ -289,6 +312,7 @@ __device__ __forceinline__ void attn_request_tile(uint32_t dst, const __nv_bfloa
 template <int G>
 __global__ void __launch_bounds__(kAttnPartThreads, 3)
 attn_part_kernel(const AttnArgs a) {
+  step_kernel_entry();
   constexpr int R = 16 / G;              // rows of the step per group
   constexpr int kMaxPasses = R * kAttnPartsPerCta;
   extern __shared__ __align__(128) unsigned char attn_smem[];
@@ -475,22 +499,69 @@ attn_part_kernel(const AttnArgs a) {
   }
 }
 
-// The parts of a (row, query head) merged in part order under their common maximum, one division, BF16 out.
-// grid (rows, nq), 128 threads.
-__global__ void __launch_bounds__(kAttnDim)
+// The parts of a (row, query head) merged under their common maximum, one division, BF16 out.
+// One CTA of four warps per (row, query head); a lane owns four dimensions.  The parts are cut into four runs of
+// consecutive parts, one per warp, each added up in part order (all of a run's loads are in flight together: on a
+// one-row step this kernel is one L2 round trip long, not one per part); the four sums are then added in warp order.
+// The cut depends on the row's own context length only.
+constexpr int kCombineWarps = 4;
+constexpr int kCombineUnroll = 8;
+__global__ void __launch_bounds__(kCombineWarps * 32)
 attn_combine_kernel(const AttnArgs a) {
-  const uint32_t row = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
+  step_kernel_entry();
+  __shared__ float4 sums[kCombineWarps - 1][32];
+  __shared__ float dens[kCombineWarps - 1];
+  const uint32_t pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  const uint32_t row = pair / a.nq;
   const uint32_t ns = (uint32_t(a.row_pos[row]) + kAttnPart) / kAttnPart;   // ceil((pos + 1) / 128)
-  const size_t base = (size_t(row) * a.nq + hq) * a.max_splits;
-  float mx = a.part_ml[base * 2];
-  for (uint32_t s = 1; s < ns; ++s) mx = fmaxf(mx, a.part_ml[(base + s) * 2]);
-  float den = 0.f, num = 0.f;
-  for (uint32_t s = 0; s < ns; ++s) {
-    const float e = exp2f(__fsub_rn(a.part_ml[(base + s) * 2], mx));   // the parts' maxima are in units of log 2
-    den = __fmaf_rn(e, a.part_ml[(base + s) * 2 + 1], den);
-    num = __fmaf_rn(e, a.part_acc[(base + s) * kAttnDim + d], num);
+  const size_t base = size_t(pair) * a.max_splits;
+  float mx = -INFINITY;
+  for (uint32_t s = lane; s < ns; s += 32) mx = fmaxf(mx, a.part_ml[(base + s) * 2]);
+#pragma unroll
+  for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+  const uint32_t per = (ns + kCombineWarps - 1) / kCombineWarps;
+  const uint32_t first = min(ns, warp * per), last = min(ns, first + per);
+  float den = 0.f;
+  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t s0 = first; s0 < last; s0 += kCombineUnroll) {
+    float4 v[kCombineUnroll];
+    float2 ml[kCombineUnroll];
+#pragma unroll
+    for (int j = 0; j < kCombineUnroll; ++j) {
+      const bool in = s0 + j < last;
+      v[j] = in ? *(reinterpret_cast<const float4*>(a.part_acc + (base + s0 + j) * kAttnDim) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      ml[j] = in ? *reinterpret_cast<const float2*>(a.part_ml + (base + s0 + j) * 2) : make_float2(-INFINITY, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < kCombineUnroll; ++j) {
+      if (s0 + j < last) {
+        const float e = exp2f(__fsub_rn(ml[j].x, mx));   // the parts' maxima are in units of log 2
+        den = __fmaf_rn(e, ml[j].y, den);
+        num.x = __fmaf_rn(e, v[j].x, num.x);
+        num.y = __fmaf_rn(e, v[j].y, num.y);
+        num.z = __fmaf_rn(e, v[j].z, num.z);
+        num.w = __fmaf_rn(e, v[j].w, num.w);
+      }
+    }
   }
-  a.out[(size_t(row) * a.nq + hq) * kAttnDim + d] = __float2bfloat16_rn(__fdiv_rn(num, den));
+  if (warp) {
+    sums[warp - 1][lane] = num;
+    if (lane == 0) dens[warp - 1] = den;
+  }
+  __syncthreads();
+  if (warp == 0) {
+#pragma unroll
+    for (int w = 0; w < kCombineWarps - 1; ++w) {
+      const float4 o = sums[w][lane];
+      den = __fadd_rn(den, dens[w]);
+      num.x = __fadd_rn(num.x, o.x);
+      num.y = __fadd_rn(num.y, o.y);
+      num.z = __fadd_rn(num.z, o.z);
+      num.w = __fadd_rn(num.w, o.w);
+    }
+    const uint32_t lo = pack_bf(__fdiv_rn(num.x, den), __fdiv_rn(num.y, den)), hi = pack_bf(__fdiv_rn(num.z, den), __fdiv_rn(num.w, den));
+    *reinterpret_cast<uint2*>(a.out + size_t(pair) * kAttnDim + lane * 4) = make_uint2(lo, hi);
+  }
 }
 
 }  // namespace grb
