@@ -303,11 +303,36 @@ class Layer:
         return e["res"].coded_bytes + 2 * m * (e["k1"] - e["k0"]) + 2 * m * e["res"].N
 
     def step(self):
+        """The twelve launches.  More than one rank: the sums of the column-split linears' partial outputs run on a side
+        stream, in launch order, each behind the linear that feeds it; the step's launches do not read one another's
+        outputs, so a sum (mostly a wait for the peers' flags) overlaps the next linear instead of standing between two.
+        The side stream joins before the step ends; captured, this is one graph with two branches."""
+        import torch
+
+        side = self._side_stream() if (self.peer is not None and self.world > 1) else None
+        main = torch.cuda.current_stream(self.device) if side is not None else None
         for m in BATCHES:
             for e in self.entries:
                 e["res"].gemm(self.xv[(m, e["name"])], e["y"][m])
                 if e["kind"] == "row" and self.world > 1:
-                    self.all_reduce(e, m)
+                    if side is None:
+                        self.all_reduce(e, m)
+                    else:
+                        ready = torch.cuda.Event()
+                        ready.record(main)
+                        side.wait_event(ready)
+                        self.peer.reduce(f'{e["name"]}:{m}', e["sum"][m], stream=side)
+        if side is not None:
+            done = torch.cuda.Event()
+            done.record(side)
+            main.wait_event(done)
+
+    def _side_stream(self):
+        import torch
+
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(self.device)
+        return self._side
 
     def segmented_step(self):
         """Multi-rank step as CUDA graphs of the fused launches with the NCCL all-reduces launched between them
@@ -377,18 +402,24 @@ class Layer:
                         self.x[(m, k)].copy_(self.x_host[(m, k)], non_blocking=True)
                     ready[m] = torch.cuda.Event()
                     ready[m].record(side)
+            sums = self._side_stream() if self.peer is not None else None   # the cross-rank sums, as in step()
             for m in BATCHES:
                 main.wait_event(ready[m])
                 for e in self.entries:
                     e["res"](self.xv[(m, e["name"])], e["y"][m])
-                    if e["kind"] == "row" and self.peer is not None:
-                        self.all_reduce(e, m)
+                    if e["kind"] == "row" and sums is not None:
+                        partial = torch.cuda.Event()
+                        partial.record(main)
+                        sums.wait_event(partial)
+                        self.peer.reduce(f'{e["name"]}:{m}', e["sum"][m], stream=sums)
                 done = torch.cuda.Event()
-                done.record(main)
+                done.record(main if sums is None else sums)
                 with torch.cuda.stream(side):   # the down projection's output goes back while the next batch runs
                     side.wait_event(done)
                     self.y_host[m].copy_(self.result(self.entries[-1], m), non_blocking=True)
             main.wait_stream(side)
+            if sums is not None:
+                main.wait_stream(sums)
 
         def step():
             graph.replay()

@@ -39,6 +39,28 @@ class BctxLinear(nn.Module):
         return self.context_weight.linear(x, bias=bias)
 
 
+class BCTXLinear(nn.Module):
+    """The linear of the speculation head (``BCTXLinear`` of
+    ``context-runtime/georefine_context_runtime/bitexact_context_mtp.py:279-297``): ``tensor``, ``name`` and a ``calls``
+    counter, no bias.  The reference decodes the weight for every call and runs a dense product; here the product
+    reads the compressed image, and a tensor whose decoded shape no longer matches its descriptor is refused as there."""
+
+    def __init__(self, tensor, name: str):
+        super().__init__()
+        if len(tensor.shape) != 2:
+            raise ContextServingError("linear BCTX weight must be rank two")
+        self.tensor = tensor
+        self.name = str(name)
+        self.calls = 0
+
+    def forward(self, x):
+        self.calls += 1
+        y = self.tensor.linear(x)
+        if y.shape[-1] != int(self.tensor.shape[0]) or x.shape[-1] != int(self.tensor.shape[1]):
+            raise ValueError(f"decoded shape changed for {self.name}")
+        return y if y.dtype == x.dtype else y.to(dtype=x.dtype)
+
+
 class BctxEmbedding(nn.Module):
     """Embedding table that stays compressed; rows are decoded by indexed gather."""
 

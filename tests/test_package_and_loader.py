@@ -222,3 +222,31 @@ def test_loader_refusals(checkpoint, tmp_path):
     (out / "manifest.json").write_text(json.dumps(json.loads((out / "manifest.json").read_text()) | {"tensors": manifest["tensors"]}))
     with pytest.raises(serving.ContextServingError, match="unfilled meta tensors"):
         serving.load_bctx_model(out, model_factory=Stuck, device="cpu", tensor_factory=RecordingContext, log=lambda m: None)
+
+
+def test_speculation_head_linear_counts_calls_and_checks_shapes():
+    """``BCTXLinear`` (the module the reference's speculation-head loader puts in place of a dense linear): the product
+    goes to the tensor's fused ``linear``, calls are counted, a tensor that answers with another shape is refused."""
+    import torch
+
+    from georefine_b200 import serving
+
+    class Stand:
+        shape = (6, 4)
+
+        def __init__(self, out_features=6):
+            self.out_features = out_features
+
+        def linear(self, x, bias=None):
+            return torch.ones(*x.shape[:-1], self.out_features, dtype=torch.float32)
+
+    layer = serving.BCTXLinear(Stand(), "mtp.fc")
+    y = layer(torch.zeros(3, 4, dtype=torch.bfloat16))
+    assert y.shape == (3, 6) and y.dtype == torch.bfloat16 and layer.calls == 1 and layer.name == "mtp.fc"
+    assert not list(layer.state_dict())
+    with pytest.raises(ValueError):
+        serving.BCTXLinear(Stand(out_features=5), "mtp.fc")(torch.zeros(3, 4, dtype=torch.bfloat16))
+    with pytest.raises(serving.ContextServingError):
+        bad = Stand()
+        bad.shape = (6,)
+        serving.BCTXLinear(bad, "v")
