@@ -117,10 +117,14 @@ struct RoleCtx {
     asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_addr), "r"(1u) : "memory");
     atomicOr(status, bits);
   }
-  // Bounded wait; on expiry marks the CTA aborted.
+  // Bounded wait; on expiry marks the CTA aborted.  The first wait of the launch to give up also records where:
+  // bits 8..15 of the status word receive 1 + the barrier's index in the kernel's barrier area, bits 16..23 the CTA
+  // (diagnostic only).
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity) const {
     if (mbar_wait(bar, parity, suspend)) return true;
-    abort(kStatusTimeout);
+    asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(abort_addr), "r"(1u) : "memory");
+    if ((atomicOr(status, kStatusTimeout) & kStatusTimeout) == 0)
+      atomicOr(status, ((((bar - bars) >> 3) + 1u) & 0xFFu) << 8 | (blockIdx.x & 0xFFu) << 16);
     return false;
   }
 };

@@ -94,7 +94,8 @@ int grb_bctx_build_lookup(const uint32_t* freq, uint32_t nctx, uint32_t vocab, u
 #define GRB_STATUS_OVERRUN 2u
 #define GRB_STATUS_LOW_STATE 4u
 #define GRB_STATUS_CHECKPOINT 8u
-#define GRB_STATUS_TIMEOUT 16u
+#define GRB_STATUS_TIMEOUT 16u      /* a bounded wait ran out; the fused kernels also record where: bits 8..15 =
+                                      1 + index of the first barrier that gave up, bits 16..23 = its CTA (diagnostic) */
 #define GRB_STATUS_BAD_ARGUMENT 32u
 
 /* Device pointers of one indexed frame: the arrays CudaContextTensor keeps in .buffers
