@@ -869,20 +869,48 @@ def run_decode(args):
     _deadline(1500)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
-    dev = torch.device("cuda", 0)
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if world > 1:    # BASELINE.json config 4: the same stack under tensor parallelism (see decode_measurement)
+        import datetime
+
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     line = decode_measurement(dev, [int(v) for v in args.seqs.split(",")], layers=args.layers, distinct_layers=args.distinct_layers,
-                              spec=args.spec, generate=128)
-    print(json.dumps(line), flush=True)
+                              spec=args.spec and world == 1, generate=128, rank=rank, world=world)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
 
 
-def decode_measurement(dev, seqs, *, layers=64, distinct_layers=2, spec=False, generate=128):
-    """See run_decode.  Returns the JSON-ready record."""
+def _same_on_every_rank(tensor, dev) -> bool:
+    """Do all ranks hold the same values (the tokens of a step: they must, or the ranks' hosts would drift apart)?"""
+    import torch
+    import torch.distributed as dist
+
+    lo, hi = tensor.clone().to(torch.int64), tensor.clone().to(torch.int64)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    return bool(torch.equal(lo, hi))
+
+
+def decode_measurement(dev, seqs, *, layers=64, distinct_layers=2, spec=False, generate=128, rank=0, world=1):
+    """See run_decode.  Returns the JSON-ready record.  With world > 1 (one process per GPU under torchrun) the stack is
+    tensor-parallel: QKV and gate|up split by weight rows - a rank keeps its query heads, its KV heads (and their
+    cache) and its FFN columns -, O and down by weight columns with their partial outputs summed over peer memory
+    inside the step's graph; embedding, norms and the output head are replicated.  Times are the maximum over the
+    ranks; the byte counts are per rank."""
     import torch
 
     from georefine_b200 import serve
 
-    cfg = serve.DecoderConfig(layers=layers)
+    cfg = serve.DecoderConfig(layers=layers, tp_world=world, tp_rank=rank)
     t0 = time.time()
     weights = serve.DecoderWeights.synthetic(cfg, dev, seed=SEED, distinct_layers=distinct_layers, max_m=128)
     build_s = time.time() - t0
@@ -893,13 +921,14 @@ def decode_measurement(dev, seqs, *, layers=64, distinct_layers=2, spec=False, g
         part.uniform_(-0.5, 0.5)                                   # a synthetic context in every page
     peak, peak_kind = measured_hbm_peak()
     g = torch.Generator().manual_seed(SEED)
-    line = {"metric": "decode_tokens_per_second", "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+    line = {"metric": "decode_tokens_per_second", "unit": "tok/s", "n_gpus": world, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{cfg.layers}-layer decoder hidden={cfg.hidden} heads={cfg.heads}/{cfg.kv_heads}x{cfg.head_dim} ffn={cfg.ffn} "
                                    f"vocab={cfg.vocab}, {context}-token context, {generate} generated tokens, random token IDs",
-                       "distinct_layers": weights.notes["distinct_layers"], "resident_format": "BXR1/window4", "launch": "cuda_graph per row bucket",
+                       "parallelism": f"tp{world}", "distinct_layers": weights.notes["distinct_layers"], "resident_format": "BXR1/window4",
+                       "launch": "cuda_graph per row bucket" + (", sums of O and down over peer memory inside the graph" if world > 1 else ""),
                        "host_build_seconds": round(build_s, 1)},
             "weight_bytes_per_step": weights.streamed_bytes(), "results": {}}
-    clocks = ClockSampler(0).start()
+    clocks = ClockSampler(dev.index or 0).start()
     for n in seqs:
         b = serve.Batcher(d)
         for _ in range(n):                                         # admit n sequences whose context is already "in the cache"
@@ -923,12 +952,22 @@ def decode_measurement(dev, seqs, *, layers=64, distinct_layers=2, spec=False, g
         torch.cuda.synchronize()
         t_end = time.monotonic()
         ms = e0.elapsed_time(e1) / generate
+        if world > 1:
+            import torch.distributed as dist
+
+            slowest = torch.tensor([ms], device=dev)
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+            ms = float(slowest.item())
         mean_context = context + generate / 2
         kv = d.streamed_bytes([mean_context] * n)["kv"]
         res = {"ms_per_step": round(ms, 3), "tok_s": round(n / (ms * 1e-3), 1), "kv_bytes_per_step": int(kv),
                "streamed_GBps": round((kv + weights.streamed_bytes()) / (ms * 1e-3) / 1e9, 1),
                "frac_of_hbm_peak": round((kv + weights.streamed_bytes()) / (ms * 1e-3) / 1e9 / peak, 4),
-               "status_word": sum(w.check_status() for w in weights.linears()), "clocks": clocks.summary(t_begin, t_end)}
+               "status_word": sum(w.check_status() for w in weights.linears()) + (d.peer.check_status() if d.peer is not None else 0),
+               "clocks": clocks.summary(t_begin, t_end)}
+        if world > 1:
+            res["per_gpu_streamed_GBps"] = res["streamed_GBps"]
+            res["tokens_agree_across_ranks"] = _same_on_every_rank(d.next_token[:n], dev)
         if spec:                                              # config 3: exact speculation, k = 5, verify pass at n x 6 rows
             b.sync_tokens()
             for s in b.active.values():

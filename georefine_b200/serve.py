@@ -40,15 +40,59 @@ class DecoderConfig:
     vocab: int = 152064
     rope_theta: float = 1e6
     eps: float = 1e-6
+    tp_world: int = 1        # tensor parallelism over the GPUs of one node: this process is rank tp_rank of tp_world
+    tp_rank: int = 0
+
+    def __post_init__(self):
+        w = self.tp_world
+        if w < 1 or not 0 <= self.tp_rank < w or self.heads % w or self.kv_heads % w or self.ffn % w or (self.ffn // w) % 128:
+            raise ValueError("tensor parallelism needs the query heads, the KV heads and the FFN width (in 128-column chunks) to divide evenly")
 
     @property
     def qkv_rows(self) -> int:
         return (self.heads + 2 * self.kv_heads) * self.head_dim
 
+    # what this rank holds: its share of the heads and of the FFN columns
+    @property
+    def local_heads(self) -> int:
+        return self.heads // self.tp_world
+
+    @property
+    def local_kv_heads(self) -> int:
+        return self.kv_heads // self.tp_world
+
+    @property
+    def local_ffn(self) -> int:
+        return self.ffn // self.tp_world
+
+    @property
+    def local_qkv_rows(self) -> int:
+        return (self.local_heads + 2 * self.local_kv_heads) * self.head_dim
+
     def linear_shapes(self):
-        """(name, weight rows, weight columns) of the four linears of a layer, in the order a step runs them."""
+        """(name, weight rows, weight columns) of the four linears of a layer (whole, before any sharding), in the order
+        a step runs them."""
         return [("qkv", self.qkv_rows, self.hidden), ("o", self.hidden, self.heads * self.head_dim),
                 ("gate_up", 2 * self.ffn, self.hidden), ("down", self.hidden, self.ffn)]
+
+    def shard(self, leaf: str, words):
+        """This rank's part of a whole weight: QKV and gate|up by weight rows (the rank's query heads, its key heads, its
+        value heads; its columns of the gate half and of the up half), O and down by weight columns (the rank's heads'
+        outputs; its FFN columns), whose partial products are then summed over the ranks.  Anything else is replicated."""
+        if self.tp_world == 1:
+            return words
+        r, d = self.tp_rank, self.head_dim
+        lh, lkv, lf = self.local_heads * d, self.local_kv_heads * d, self.local_ffn
+        if leaf == "qkv":
+            k_at, v_at = self.heads * d, (self.heads + self.kv_heads) * d
+            return np.concatenate([words[r * lh:(r + 1) * lh], words[k_at + r * lkv:k_at + (r + 1) * lkv], words[v_at + r * lkv:v_at + (r + 1) * lkv]])
+        if leaf == "gate_up":
+            return np.concatenate([words[r * lf:(r + 1) * lf], words[self.ffn + r * lf:self.ffn + (r + 1) * lf]])
+        if leaf == "o":
+            return np.ascontiguousarray(words[:, r * lh:(r + 1) * lh])
+        if leaf == "down":
+            return np.ascontiguousarray(words[:, r * lf:(r + 1) * lf])
+        return words
 
 
 def synthetic_words(rows, cols, seed):
@@ -101,7 +145,7 @@ class DecoderWeights:
             return torch.from_numpy(np.ascontiguousarray(words_of(name)).view(np.int16)).view(torch.bfloat16).to(dev)
 
         def linear(name):
-            words = np.ascontiguousarray(words_of(name))
+            words = np.ascontiguousarray(config.shard(name.split(".")[-1], words_of(name)))
             if lin_factory is not None:
                 return lin_factory(name, words)
             return ResidentWeight.from_words(words, dev, max_m=max_m, verify=False, tune=tune, layout=layout)
@@ -177,19 +221,28 @@ class BatchDecoder:
         n_pages = self.max_slots * self.pages_per_seq + 1           # the last page: where padding rows write
         self.scratch_page, self.pad_slot = n_pages - 1, self.max_slots
         bf, i32 = torch.bfloat16, torch.int32
-        self.kv = torch.zeros(cfg.layers, 2, n_pages, cfg.kv_heads, PAGE, cfg.head_dim, device=self.dev, dtype=bf)
+        self.kv = torch.zeros(cfg.layers, 2, n_pages, cfg.local_kv_heads, PAGE, cfg.head_dim, device=self.dev, dtype=bf)
         self.page_table = torch.full((self.max_slots + 1, self.pages_per_seq), self.scratch_page, device=self.dev, dtype=i32)
         self._table_host = np.full((self.max_slots + 1, self.pages_per_seq), -1, dtype=np.int64)
         self._free_pages = list(range(n_pages - 2, -1, -1))
         self._free_slots = list(range(self.max_slots - 1, -1, -1))
         self.cos, self.sin = ops.rope_tables(self.max_context, cfg.rope_theta, self.dev)
-        self.attn = ops.PagedAttention(cfg.heads, cfg.kv_heads, self.max_rows, self.pages_per_seq, self.dev)
+        self.attn = ops.PagedAttention(cfg.local_heads, cfg.local_kv_heads, self.max_rows, self.pages_per_seq, self.dev)
         R, H = self.max_rows, cfg.hidden
         z = lambda *shape, dtype=bf: torch.zeros(*shape, device=self.dev, dtype=dtype)
         self.tokens, self.row_seq, self.row_pos = z(R, dtype=i32), torch.full((R,), self.pad_slot, device=self.dev, dtype=i32), z(R, dtype=i32)
-        self.h, self.x, self.qkv, self.ctx = z(R, H), z(R, H), z(R, cfg.qkv_rows), z(R, cfg.heads * cfg.head_dim)
-        self.o_out, self.gate_up, self.act, self.down_out = z(R, H), z(R, 2 * cfg.ffn), z(R, cfg.ffn), z(R, H)
+        self.h, self.x, self.qkv, self.ctx = z(R, H), z(R, H), z(R, cfg.local_qkv_rows), z(R, cfg.local_heads * cfg.head_dim)
+        self.o_out, self.gate_up, self.act, self.down_out = z(R, H), z(R, 2 * cfg.local_ffn), z(R, cfg.local_ffn), z(R, H)
         self.logits, self.next_token = z(R, cfg.vocab), z(R, dtype=i32)
+        # Tensor parallelism: O and down are multiplied by this rank's columns only; the partial outputs land in a buffer
+        # the peers can reach and are summed over peer memory (georefine_b200.peer), inside the step's CUDA graph.  The sum
+        # has the same bits on every rank, so every rank draws the same tokens and the hosts stay in step without
+        # talking to each other.  (Constructing the reducer is a collective: every rank builds its decoder.)
+        self.peer = None
+        if cfg.tp_world > 1:
+            from .peer import PeerReducer
+
+            self.peer = PeerReducer({"o": R * H, "down": R * H}, device=self.dev)
         for w in weights.linears():
             if hasattr(w, "reserve"):
                 w.reserve(min(self.max_rows, 128))
@@ -235,11 +288,11 @@ class BatchDecoder:
             layer.qkv(x, self.qkv[:n])
             self.attn(self.qkv[:n], self.cos, self.sin, self.row_seq[:n], self.row_pos[:n], self.page_table, self.kv[i, 0], self.kv[i, 1],
                       self.ctx[:n])
-            layer.o(self.ctx[:n], self.o_out[:n])
+            self._row_parallel(layer.o, "o", self.ctx[:n], self.o_out[:n])
             ops.rmsnorm(h, layer.norm2, x, delta=self.o_out[:n], eps=cfg.eps)
             layer.gate_up(x, self.gate_up[:n])
             ops.silu_mul(self.gate_up[:n], self.act[:n])
-            layer.down(self.act[:n], self.down_out[:n])
+            self._row_parallel(layer.down, "down", self.act[:n], self.down_out[:n])
             delta = self.down_out[:n]
         ops.rmsnorm(h, w.final_norm, x, delta=delta, eps=cfg.eps)          # h now holds the final residual stream
         w.lm_head(x, self.logits[:n])
@@ -247,6 +300,14 @@ class BatchDecoder:
         if advance:
             self.tokens[:n].copy_(self.next_token[:n])
             self.row_pos[:n].add_(1)
+
+    def _row_parallel(self, linear, slot: str, x, out) -> None:
+        """out = linear(x), summed over the ranks when the weight is split by columns."""
+        if self.peer is None:
+            linear(x, out)
+        else:
+            linear(x, self.peer.slot(slot, out.shape[0], out.shape[1]))
+            self.peer.reduce(slot, out)
 
     def run(self, kind: str, n: int, *, graph: bool = True) -> None:
         """Runs rows 0..n-1 ("ar" or "verify"); replays the step's CUDA graph, capturing it on first use."""
@@ -285,7 +346,7 @@ class BatchDecoder:
 
     def streamed_bytes(self, rows_context) -> dict:
         """Bytes one step streams: the compressed weights, and the KV cache of rows whose contexts are given."""
-        kv = sum(int(c) for c in rows_context) * self.cfg.kv_heads * self.cfg.head_dim * 2 * 2 * self.cfg.layers
+        kv = sum(int(c) for c in rows_context) * self.cfg.local_kv_heads * self.cfg.head_dim * 2 * 2 * self.cfg.layers
         return {"weights": self.w.streamed_bytes(), "kv": kv}
 
 
@@ -517,6 +578,8 @@ class MTPHead:
         import torch
 
         d, cfg = decoder, decoder.cfg
+        if cfg.tp_world != 1:
+            raise ValueError("the draft head runs on one GPU: build it over a decoder without tensor parallelism")
         self.d, self.fc, self.norm_e, self.norm_h, self.layer, self.final_norm = d, fc, norm_e, norm_h, layer, final_norm
         bf, R, H = torch.bfloat16, d.max_rows, cfg.hidden
         z = lambda *shape, dtype=bf: torch.zeros(*shape, device=d.dev, dtype=dtype)
