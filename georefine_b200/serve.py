@@ -407,9 +407,10 @@ class Batcher:
             if s in self.active and self.active[s]["tokens"][-1] is None:
                 self.active[s]["tokens"][-1] = int(pending[i])
 
-    def step(self, *, fetch: bool = True):
+    def step(self, *, fetch: bool = True, sampler=None):
         """One token for every active sequence.  Returns {slot: token} (``fetch=False``: nothing is read back, the
-        tokens stay on the device and feed the next step; ``sync_tokens`` collects them later)."""
+        tokens stay on the device and feed the next step; ``sync_tokens`` collects them later).  With a
+        ``sampling.Sampler`` the tokens are drawn from the step's logits instead of taken as their arg-max."""
         import torch
 
         d = self.d
@@ -431,20 +432,26 @@ class Batcher:
             self.active[s]["pos"] += 1
         if b > n:                                   # padding rows advanced too: park them again
             d.row_pos[n:b].zero_()
+        chosen = d.next_token
+        if sampler is not None:                     # the step fed every row its arg-max: put the drawn tokens in their place
+            chosen = sampler.draw(d.logits[:n]).to(torch.int32)
+            d.tokens[:n].copy_(chosen)
         if not fetch:
             for s in self._order:
                 self.active[s]["tokens"].append(None)
             return None
-        got = d.next_token[:n].tolist()
+        got = chosen[:n].tolist()
         for s, t in zip(self._order, got):
             self.active[s]["tokens"].append(int(t))
         return dict(zip(self._order, got))
 
-    def verify(self, drafts: dict):
+    def verify(self, drafts: dict, *, sampler=None):
         """Exact speculation for every sequence in ``drafts`` ({slot: [k draft tokens]}): one pass over k + 1 rows per
         sequence - its pending token, then the drafts - accepts the longest prefix of drafts equal to the target's own
         arg-max rows and emits one more token.  Returns {slot: emitted tokens}; positions are rewound by bookkeeping
-        alone (the surplus KV entries are overwritten by the next pass)."""
+        alone (the surplus KV entries are overwritten by the next pass).  With a ``sampling.Sampler`` a draft is kept with
+        the probability the target gives it and the first one refused is redrawn (``sampling.accept_drafts``), so the
+        emitted tokens are distributed as plain sampling from the target."""
         d = self.d
         self.sync_tokens()
         slots, positions, tokens = [], [], []
@@ -463,14 +470,17 @@ class Batcher:
         argmax_rows = d.next_token[:len(slots)].tolist()
         for slot, ds in drafts.items():
             k = len(ds)
-            own = argmax_rows[at:at + k + 1]
-            a = 0
-            while a < k and int(ds[a]) == own[a]:
-                a += 1
-            emitted = [int(t) for t in own[:a + 1]]
+            if sampler is None:
+                own = argmax_rows[at:at + k + 1]
+                a = 0
+                while a < k and int(ds[a]) == own[a]:
+                    a += 1
+                emitted = [int(t) for t in own[:a + 1]]
+            else:
+                emitted = sampler.accept(d.logits[at:at + k + 1], [int(t) for t in ds])
             s = self.active[slot]
             s["tokens"] += emitted
-            s["pos"] += a + 1
+            s["pos"] += len(emitted)
             out[slot] = emitted
             at += k + 1
         self._dirty = True
@@ -479,51 +489,89 @@ class Batcher:
 
 @dataclass
 class State:
-    """A live sequence of a ``FastSession``: prompt length and the tokens generated so far."""
+    """A live sequence of a ``FastSession``: prompt length, the tokens generated so far, and the logits the prompt's
+    last position produced (what a sampled first token is drawn from)."""
 
     slot: int
     plen: int
     tokens: list
+    first_logits: object = None
 
 
 class FastSession:
     """One sequence at a time through the batched engine, under the reference's session API
-    (``glc_serve/fastserve.py``): ``load`` / ``prefill`` / ``generate`` / ``extend`` / ``rollback``.  Greedy decoding;
-    ``generate(spec_k=k, drafter=...)`` runs exact speculation: ``drafter(state, k)`` proposes k tokens (an MTP head, or
-    any callable), the verify pass keeps what the target itself would have produced."""
+    (``glc_serve/fastserve.py``): ``load`` / ``prefill`` / ``generate`` / ``extend`` / ``rollback``.  Greedy decoding at
+    temperature 0, else temperature / top-p sampling from a seeded generator.  ``generate(spec_k=k, drafter=...)`` runs
+    speculation: ``drafter(state, k)`` proposes k tokens (an MTP head, or any callable); greedy, the verify pass keeps
+    what the target itself would have produced, bit for bit the tokens of plain decoding; sampling, it keeps a draft
+    with the probability the target gives it, which leaves the distribution of the output that of plain sampling."""
 
     def __init__(self, decoder: BatchDecoder):
         self.d = decoder
         self.batcher = Batcher(decoder)
+        self.mtp_head = None
         self.meta = {"streamed_bytes_per_step": decoder.w.streamed_bytes()}
 
     @classmethod
-    def load(cls, *, config: DecoderConfig, weights: DecoderWeights | None = None, device="cuda:0", max_len=4096, seed=1,
-             lin_factory=None, tune=None, max_rows=128, **kw) -> "FastSession":
-        if weights is None:
+    def load(cls, *, package=None, config: DecoderConfig | None = None, weights: DecoderWeights | None = None, device="cuda:0",
+             max_len=4096, seed=1, lin_factory=None, tune=None, max_rows=128, **kw) -> "FastSession":
+        """A session over ``weights``; or over the decoder of a BCTX ``package`` directory, filled from its frames alone
+        (``georefine_b200.checkpoint``; the draft head too, as ``session.mtp_head``, when the package has ``mtp.*``
+        tensors); or over random-init weights of ``config``."""
+        source = None
+        if weights is None and package is not None:
+            from . import checkpoint
+
+            weights = checkpoint.load_decoder_weights(package, device, config=config, lin_factory=lin_factory, tune=tune, **kw)
+            source = weights.notes["source"]
+        elif weights is None:
+            if config is None:
+                raise ValueError("package=, weights= or config= required")
             weights = DecoderWeights.synthetic(config, device, seed=seed, lin_factory=lin_factory, tune=tune, **kw)
-        return cls(BatchDecoder(weights, max_rows=max_rows, max_slots=4, max_context=max_len, device=device))
+        session = cls(BatchDecoder(weights, max_rows=max_rows, max_slots=4, max_context=max_len, device=device))
+        if source is not None:
+            session.meta["receipt"] = weights.notes["receipt"]
+            if source.has_mtp and weights.config.tp_world == 1:
+                from . import checkpoint
+
+                session.mtp_head = checkpoint.load_mtp_head(source, session.d, lin_factory=lin_factory)
+        return session
 
     def prefill(self, *, token_ids) -> State:
-        slot = self.batcher.admit(token_ids)
-        return State(slot, len(list(token_ids)), self.batcher.active[slot]["tokens"])
+        ids = list(token_ids)
+        slot = self.batcher.admit(ids)
+        last_row = (len(ids) - 1) % self.d.max_rows            # the prompt ran in chunks of max_rows rows
+        return State(slot, len(ids), self.batcher.active[slot]["tokens"], self.d.logits[last_row].clone())
 
-    def generate(self, st: State, *, max_tokens: int, stop_ids=(), spec_k: int = 0, drafter=None):
-        """Yields up to ``max_tokens`` new tokens (the token the prefill produced counts as the first)."""
+    def generate(self, st: State, *, max_tokens: int, stop_ids=(), temperature: float = 0.0, top_p: float = 1.0, seed=None,
+                 spec_k: int = 0, drafter=None):
+        """Yields up to ``max_tokens`` new tokens (the token the prefill produced counts as the first).  ``temperature``
+        > 0 samples (``top_p`` < 1: from the nucleus); ``seed`` makes the draws reproducible, and a tensor-parallel
+        decoder needs one, the same on every rank, for the ranks to stay in step."""
+        from .sampling import Sampler
+
         stops = {int(t) for t in stop_ids}
         seq = self.batcher.active[st.slot]
+        sampler = None
+        if temperature > 0:
+            if self.d.cfg.tp_world > 1 and seed is None:
+                raise ValueError("sampling on a tensor-parallel decoder needs a seed shared by the ranks")
+            sampler = Sampler(temperature, top_p, device=self.d.dev, seed=seed)
         emitted = 0
         if len(seq["tokens"]) == 1 and not getattr(st, "_first_out", False):
             st._first_out = True
+            if sampler is not None and st.first_logits is not None:
+                seq["tokens"][0] = int(sampler.draw(st.first_logits[None])[0])
+                self.batcher._dirty = True
             emitted += 1
             yield seq["tokens"][0]
             if seq["tokens"][0] in stops:
                 return
         while emitted < max_tokens:
             if spec_k and drafter is not None:
-                new = self.batcher.verify({st.slot: drafter(st, spec_k)})[st.slot]
+                new = self.batcher.verify({st.slot: drafter(st, spec_k)}, sampler=sampler)[st.slot]
             else:
-                new = [self.batcher.step()[st.slot]]
+                new = [self.batcher.step(sampler=sampler)[st.slot]]
             for j, t in enumerate(new):
                 emitted += 1
                 yield t
@@ -699,8 +747,9 @@ class MTPSpeculator:
         self.b._dirty = True
         return slot
 
-    def cycle(self):
-        """One speculation cycle for every active sequence.  Returns {slot: emitted tokens}."""
+    def cycle(self, *, sampler=None):
+        """One speculation cycle for every active sequence.  Returns {slot: emitted tokens}.  ``sampler``: see
+        ``Batcher.verify``."""
         import torch
 
         b, d, head, k = self.b, self.b.d, self.head, self.k
@@ -722,7 +771,7 @@ class MTPSpeculator:
                 if j + 1 < k:
                     step = head.extend_draft(n)
         start = {s: b.active[s]["pos"] for s in order}
-        out = b.verify(drafts)
+        out = b.verify(drafts, sampler=sampler)
         # confirm: the head sees the accepted tokens with the trunk's hidden states of the verify pass
         slots, positions, tokens, picks, at = [], [], [], [], 0
         for s in order:

@@ -196,3 +196,122 @@ def test_mtp_head_speculation_in_a_batch_is_exact(dev, small):
         got = b.active[s]["tokens"]
         assert got[:20] == want[:len(got[:20])] and len(got) >= 13
     assert d.w.streamed_bytes() > 0 and d.streamed_bytes([100, 200])["kv"] == 300 * cfg.kv_heads * 128 * 4 * cfg.layers
+
+
+def test_session_sampling_is_seeded_and_keeps_the_engine_in_step(dev, small):
+    """Temperature / top-p sampling through the session (the reference's ``generate(temperature=, top_p=, seed=)``,
+    glc_serve/fastserve.py:250-306): reproducible from the seed, arg-max in the limit of an empty nucleus, and the KV
+    cache and positions stay those of the tokens that were actually emitted - with and without speculation."""
+    from georefine_b200 import sampling, serve
+
+    cfg, w = small
+    d = serve.BatchDecoder(w, max_rows=64, max_slots=8, max_context=1024, device=dev)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, cfg.vocab, (50,), generator=g).tolist()
+    plain = _greedy(d, prompt, 24)
+    sess = serve.FastSession(d)
+    rng = np.random.default_rng(1)
+    drafters = {"none": None, "random": lambda st, k: rng.integers(0, cfg.vocab, k).tolist(),
+                "greedy-path": lambda st, k: (plain[len(st.tokens):len(st.tokens) + k] + [0] * k)[:k]}
+
+    def run(seed, drafter, n=16, **kw):
+        st = sess.prefill(token_ids=prompt)
+        out = list(sess.generate(st, max_tokens=n, seed=seed, spec_k=5 if drafter else 0, drafter=drafter, **kw))
+        seq = sess.batcher.active[st.slot]
+        assert out == st.tokens and len(out) == n and seq["pos"] == len(prompt) + n - 1
+        assert all(0 <= t < cfg.vocab for t in out)
+        following = next(iter(sess.generate(st, max_tokens=1)))          # greedy continuation from the sampled state
+        sess.close(st)
+        return out, following
+
+    for name, drafter in drafters.items():
+        # an empty nucleus is arg-max decoding, whatever the drafter proposes
+        got, _ = run(0, drafter, n=24, temperature=1.0, top_p=1e-9)
+        assert got == plain, name
+        rng = np.random.default_rng(1)
+        a, after_a = run(7, drafter, temperature=0.8, top_p=0.95)
+        rng = np.random.default_rng(1)
+        b, after_b = run(7, drafter, temperature=0.8, top_p=0.95)
+        assert a == b and after_a == after_b, name
+        # the cache behind the sampled tokens is what a fresh pass over prompt + tokens builds
+        assert after_a == _greedy(d, prompt + a, 1)[0], name
+        others = [run(s, drafter, temperature=0.8, top_p=0.95)[0] for s in (8, 9, 10)]
+        assert any(o != a for o in others), name
+    # the batched speculator with the draft head, sampling: bookkeeping stays consistent and the run is reproducible
+    results = []
+    for _ in range(2):
+        b = serve.Batcher(d)
+        spec = serve.MTPSpeculator(b, serve.MTPHead.synthetic(d), k=3)
+        slots = [spec.admit(prompt[:n]) for n in (20, 50)]
+        sampler = sampling.Sampler(0.7, 0.9, device=dev, seed=5)
+        for _ in range(5):
+            out = spec.cycle(sampler=sampler)
+            assert all(1 <= len(v) <= 4 for v in out.values())
+        for s, n in zip(slots, (20, 50)):
+            assert b.active[s]["pos"] == n + len(b.active[s]["tokens"]) - 1
+        results.append([list(b.active[s]["tokens"]) for s in slots])
+        for s in slots:
+            spec.retire(s)
+    assert results[0] == results[1]
+
+
+def test_session_from_a_package_serves_the_checkpoint_it_was_built_from(dev, tmp_path, write_decoder_checkpoint):
+    """``FastSession.load(package=...)``: decoder and draft head filled from the frames of a BCTX package alone
+    (georefine_b200/checkpoint.py) give, token for token, what the same tensors give when handed over in memory."""
+    from georefine_b200 import package, serve
+    from georefine_b200.resident import ResidentWeight
+
+    fields = dict(hidden=512, layers=2, heads=4, kv_heads=2, ffn=1024, vocab=1000)
+    t = write_decoder_checkpoint(tmp_path / "model", seed=5, **fields)
+    package.build(tmp_path / "model", tmp_path / "package", jobs=8)
+    sess = serve.FastSession.load(package=tmp_path / "package", device=dev, max_len=1024, max_rows=64, max_m=64)
+    assert sess.mtp_head is not None and sess.meta["receipt"]["loaded_from_bctx_only"]
+    assert sess.mtp_head.receipt["tensor_count"] == 13 and sess.d.cfg.ffn == 1024
+
+    def group(prefix, leaf):           # the engine's tensors straight from the checkpoint in memory
+        names = {"norm1": ["input_layernorm"], "norm2": ["post_attention_layernorm"], "o": ["self_attn.o_proj"], "down": ["mlp.down_proj"],
+                 "qkv": ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"], "gate_up": ["mlp.gate_proj", "mlp.up_proj"]}[leaf]
+        parts = [np.atleast_2d(t[prefix + n + ".weight"]) for n in names]
+        return np.concatenate(parts) if len(parts) > 1 else parts[0]
+
+    def words_of(name):
+        if name in ("embed", "lm_head", "final_norm"):
+            return np.atleast_2d(t[{"embed": "model.embed_tokens.weight", "lm_head": "lm_head.weight", "final_norm": "model.norm.weight"}[name]])
+        _, i, leaf = name.split(".")
+        return group(f"model.layers.{i}.", leaf)
+
+    direct = serve.DecoderWeights.from_words(sess.d.cfg, words_of, dev, max_m=64)
+    d2 = serve.BatchDecoder(direct, max_rows=64, max_slots=4, max_context=1024, device=dev)
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, 1000, (37,), generator=g).tolist()
+    want = _greedy(d2, prompt, 20)
+    st = sess.prefill(token_ids=prompt)
+    assert list(sess.generate(st, max_tokens=20)) == want
+    sess.close(st)
+    # the draft head: same drafts and same hidden state as a head built from the tensors in memory
+    def res(words):
+        return ResidentWeight.from_words(np.ascontiguousarray(words), dev, max_m=64, verify=False)
+
+    def vec(name):
+        return torch.from_numpy(t[name].view(np.int16).copy()).view(torch.bfloat16).to(dev)
+
+    layer = serve.LayerWeights(vec("mtp.layers.0.input_layernorm.weight"), res(group("mtp.layers.0.", "qkv")), res(group("mtp.layers.0.", "o")),
+                               vec("mtp.layers.0.post_attention_layernorm.weight"), res(group("mtp.layers.0.", "gate_up")),
+                               res(group("mtp.layers.0.", "down")))
+    head2 = serve.MTPHead(sess.d, fc=res(t["mtp.fc.weight"]), norm_e=vec("mtp.pre_fc_norm_embedding.weight"),
+                          norm_h=vec("mtp.pre_fc_norm_hidden.weight"), layer=layer, final_norm=vec("mtp.norm.weight"))
+    slot = sess.d.open_slot()
+    sess.d.ensure_pages(slot, 16)
+    hidden = torch.randn(12, 512, generator=g).to(torch.bfloat16).to(dev)
+    toks = torch.randint(0, 1000, (12,), generator=g).tolist()
+    drafts = [h.absorb([slot] * 12, list(range(1, 13)), toks, hidden) for h in (sess.mtp_head, head2)]
+    assert drafts[0] == drafts[1] and torch.equal(sess.mtp_head.z[:12], head2.z[:12])
+    sess.d.close_slot(slot)
+    # and speculation with the packaged head is exact
+    b = serve.Batcher(sess.d)
+    spec = serve.MTPSpeculator(b, sess.mtp_head, k=4)
+    s = spec.admit(prompt)
+    while len(b.active[s]["tokens"]) < 20:
+        spec.cycle()
+    assert b.active[s]["tokens"][:20] == want
+    spec.retire(s)
