@@ -66,3 +66,27 @@ def test_dense_gemv_strided_operands_and_refusals(dev):
     with pytest.raises(RuntimeError):                                         # 260 columns: not a multiple of 8
         dense_gemv(torch.zeros(8, 260, device=dev, dtype=torch.bfloat16), torch.zeros(1, 260, device=dev, dtype=torch.bfloat16),
                    torch.empty(1, 8, device=dev, dtype=torch.bfloat16))
+
+
+def test_linear_and_install_dense_route_small_batches_to_the_gemv(dev):
+    """``dense.linear`` (F.linear semantics) and ``install_dense``: 1 to 8 rows go to the GEMV - bitwise the rows a larger
+    eligible batch gives -, more rows to ``F.linear``; the counters say which (glc_serve/miv_gemv.py:916-969)."""
+    from torch import nn
+
+    from georefine_b200 import dense
+
+    dense.STATS.reset()
+    g = torch.Generator().manual_seed(77)
+    model = nn.Sequential(nn.Linear(256, 512), nn.Linear(512, 64, bias=False)).to(torch.bfloat16).to(dev)
+    x = torch.randn(2, 4, 256, generator=g).to(torch.bfloat16).to(dev)
+    want = model(x)                                                  # cuBLAS
+    assert dense.install_dense(model) == 2
+    got = model(x)
+    assert got.shape == (2, 4, 64) and dense.STATS.gemv_by_m == {8: 2} and not dense.STATS.fallback_by_reason
+    assert ((got.float() - want.float()).abs().max() / want.float().abs().max()).item() <= 2e-2
+    one = model(x[:1, :1])
+    assert torch.equal(one.reshape(-1), got[0, 0])                   # a row does not depend on the batch it is in
+    big = model(torch.cat([x.reshape(8, 256)] * 2))                  # 16 rows: F.linear
+    assert big.shape == (16, 64) and dense.STATS.fallback_by_reason == {"m_gt8": 2}
+    y = dense.linear(x[0], model[0].weight, model[0].bias.float())   # a bias of another dtype is converted
+    assert torch.equal(y, model[0](x[0]))
