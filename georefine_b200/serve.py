@@ -370,8 +370,9 @@ class Batcher:
         self.active = {}            # slot -> {"pos": position of the next input token, "tokens": generated so far}
         self._order, self._dirty = [], True
 
-    def admit(self, prompt_ids) -> int:
-        """Processes a prompt and returns the sequence's slot; its first generated token is in ``active[slot]['tokens']``."""
+    def admit(self, prompt_ids, *, sampler=None) -> int:
+        """Processes a prompt and returns the sequence's slot; its first generated token is in ``active[slot]['tokens']``
+        (the arg-max of the last position's logits, or a draw from them when a ``sampling.Sampler`` is given)."""
         ids = [int(t) for t in prompt_ids]
         if not ids:
             raise ValueError("empty prompt")
@@ -385,6 +386,8 @@ class Batcher:
             d.set_rows([slot] * len(chunk), range(lo, lo + len(chunk)), chunk)
             d.run("verify", len(chunk), graph=False)
             first = int(d.next_token[len(chunk) - 1].item())
+        if sampler is not None:
+            first = int(sampler.draw(d.logits[len(chunk) - 1][None])[0])
         self.active[slot] = {"pos": len(ids), "tokens": [first]}
         self._dirty = True
         return slot
@@ -718,8 +721,9 @@ class MTPSpeculator:
         self.first = {}     # slot -> the head's pending first draft
         self.hidden = {}    # slot -> the head's own hidden state behind that draft (input of the second draft)
 
-    def admit(self, prompt_ids) -> int:
-        """Admits a sequence and runs the head over its prompt (trunk hidden of position p - 1 with token p)."""
+    def admit(self, prompt_ids, *, sampler=None) -> int:
+        """Admits a sequence and runs the head over its prompt (trunk hidden of position p - 1 with token p).  ``sampler``:
+        the first token is drawn from the prompt's last logits instead of being their arg-max."""
         import torch
 
         ids = [int(t) for t in prompt_ids]
@@ -732,6 +736,8 @@ class MTPSpeculator:
             d.set_rows([slot] * len(chunk), range(lo, lo + len(chunk)), chunk)
             d.run("verify", len(chunk), graph=False)
             first = int(d.next_token[len(chunk) - 1].item())
+            if sampler is not None and lo + len(chunk) == len(ids):
+                first = int(sampler.draw(d.logits[len(chunk) - 1][None])[0])
             hidden = d.h[:len(chunk)].clone()
             # pairs (hidden of p - 1, token p): inside the chunk, plus the pair that straddles the chunk boundary
             pos = list(range(lo + 1, lo + len(chunk)))

@@ -242,8 +242,8 @@ def test_session_sampling_is_seeded_and_keeps_the_engine_in_step(dev, small):
     for _ in range(2):
         b = serve.Batcher(d)
         spec = serve.MTPSpeculator(b, serve.MTPHead.synthetic(d), k=3)
-        slots = [spec.admit(prompt[:n]) for n in (20, 50)]
         sampler = sampling.Sampler(0.7, 0.9, device=dev, seed=5)
+        slots = [spec.admit(prompt[:n], sampler=sampler) for n in (20, 50)]
         for _ in range(5):
             out = spec.cycle(sampler=sampler)
             assert all(1 <= len(v) <= 4 for v in out.values())
