@@ -58,7 +58,7 @@ struct BxqSmem {
   // [2 each]; final; tile_full, tile_used [kRing each] (the closing reduction)
   static constexpr uint32_t kRing = (NB <= 64) ? 4 : 2;  // tiles in flight in the closing reduction (kWideTileRing)
   static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1 + 2 * kRing;
-  static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, verdict
+  static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, decision
   static constexpr uint32_t total = misc + 48;
   static constexpr uint32_t alloc = total + 1024;
   static_assert(MODE != kUmma || kIn >= 4, "ring too shallow");
@@ -351,7 +351,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       }
       mbar_init(ctx.bars + 8 * n, count);
     }
-    // flags: abort at misc + 4, epilogue verdict at misc + 8, final verdict at misc + 16 (misc + 0 receives the TMEM
+    // flags: abort at misc + 4, epilogue decision at misc + 8, final decision at misc + 16 (misc + 0 receives the TMEM
     // base address from the allocating warp and is left alone here)
     if (i == 0) asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
     if (i == 1) asm volatile("st.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 4), "r"(0u) : "memory");
@@ -692,7 +692,7 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           __threadfence();
           const uint32_t first = item.slot - item.part;
           // Reduced at the end of the CTA by the decoder and epilogue warps together (below).  Only the first and the
-          // last item of a CTA can be part of a split row block, hence two verdict slots; anything else is reduced here.
+          // last item of a CTA can be part of a split row block, hence two decision slots; anything else is reduced here.
           if (final_item || !early_taken) {
             if (e == 0 && lane == 0)  // {1 | (index + 1 of the tile kept in shared memory) << 8, row block, first slot, parts}
               asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(smem + L::misc + (final_item ? 16 : 32)),
@@ -731,9 +731,9 @@ bxq_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       uint32_t fetched = 0;  // tiles brought in so far: position in the two-buffer ring
 #pragma unroll 1
       for (uint32_t at = 32; at >= 16; at -= 16) {
-        const uint4 verdict = lds128(smem + L::misc + at);  // {reduce? | own tile << 8, row block, first slot, parts}
-        if (verdict.x)
-          bxq_reduce_row_block<NB>(args, ctx, verdict.y, verdict.z, verdict.w, (verdict.x >> 8) - 1u, smem, bar_tile_full, bar_tile_used,
+        const uint4 decision = lds128(smem + L::misc + at);  // {reduce? | own tile << 8, row block, first slot, parts}
+        if (decision.x)
+          bxq_reduce_row_block<NB>(args, ctx, decision.y, decision.z, decision.w, (decision.x >> 8) - 1u, smem, bar_tile_full, bar_tile_used,
                                    (warp < kDecoderWarps ? warp : warp - 4) * 32 + lane, fetched);
       }
     }

@@ -94,7 +94,7 @@ struct BxrSmem {
   static constexpr uint32_t xf32 = segoff + kIn * kSegOffBytes;
   static constexpr uint32_t bars = (xf32 + kIn * kXStage + 15) & ~15u;
   // barrier order: in_full, in_ready, in_empty [kIn each]; op_full, op_empty [kOp each]; acc_full, acc_empty [2 each]
-  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4 + 2;  // + the table's arrival barrier, + the final verdict
+  static constexpr uint32_t nbars = 3 * kIn + 2 * kOp + 4 + 2;  // + the table's arrival barrier, + the final decision
   static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, reduce flag, spare
   static constexpr uint32_t red = misc + 48;          // GEMV: FP32 [4 phases][128 rows][8]
   static constexpr uint32_t total = red + (MODE == kGemv ? 4 * 128 * kGemvMaxM * 4 : 0);
@@ -312,7 +312,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
     }
     mbar_init(bar_lut, 1);
     mbar_init(bar_final, 4);  // one arrival per epilogue warp once its items are done
-    // flags: abort at misc + 4, verdicts at misc + 8 and misc + 16 (misc + 0 receives the TMEM base address from the
+    // flags: abort at misc + 4, decisions at misc + 8 and misc + 16 (misc + 0 receives the TMEM base address from the
     // allocating warp and is left alone here)
     asm volatile("st.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 4), "r"(0u) : "memory");
     asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
@@ -514,7 +514,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
             uint32_t prev = 0;
             if (warp == 0 && lane == 0) prev = atomicAdd(args.counters + item.row_block, 1u);
             prev = __shfl_sync(0xFFFFFFFFu, prev, 0);
-            // warps 1..3 learn the verdict through shared memory
+            // warps 1..3 learn the decision through shared memory
             if (warp == 0 && lane == 0) asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 8), "r"(prev) : "memory");
             named_barrier(3, 128);
             asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(prev) : "r"(smem + L::misc + 8));
@@ -764,7 +764,7 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           }
           if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
         }
-        named_barrier(1, 128);  // the verdict word may be rewritten
+        named_barrier(1, 128);  // the decision word may be rewritten
       }
     }
     __syncwarp();
@@ -775,9 +775,9 @@ bxr_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   // the 4 epilogue warps together (20 warps instead of 4 on the critical tail of the kernel).
   if (MODE == kUmma && !args.raw && (warp < kDecoderWarps || warp >= kWarpEpilogue)) {
     if (ctx.wait(bar_final, 0)) {
-      const uint4 verdict = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
-      if (verdict.x)
-        reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
+      const uint4 decision = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
+      if (decision.x)
+        reduce_row_block<NB>(args, decision.y, decision.z, decision.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
     }
   }
 

@@ -42,7 +42,7 @@ struct BxwSmem {
   // barrier order: in_full, in_empty [kIn each]; op_full, op_empty [kOp each]; x_full [kX]; acc_full, acc_empty
   // [2 each]; final
   static constexpr uint32_t nbars = 2 * kIn + 2 * kOp + kX + 4 + 1;
-  static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, verdict
+  static constexpr uint32_t misc = (bars + 8 * nbars + 15) & ~15u;  // tmem base, abort flag, decision
   static constexpr uint32_t total = misc + 48;
   static constexpr uint32_t alloc = total + 1024;
   static_assert(MODE != kUmma || kIn >= 4, "ring too shallow");
@@ -145,7 +145,7 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
       count = j < 2 ? 2u : 4u;                                                   // both MMA issuers / the epilogue warps
     }
     if (i < L::nbars) mbar_init(ctx.bars + 8 * i, count);
-    // flags: abort at misc + 4, epilogue verdict at misc + 8, final verdict at misc + 16 (misc + 0 receives the TMEM
+    // flags: abort at misc + 4, epilogue decision at misc + 8, final decision at misc + 16 (misc + 0 receives the TMEM
     // base address from the allocating warp and is left alone here)
     if (i == 0) asm volatile("st.shared.v2.u32 [%0], {%1, %1};" ::"r"(smem + L::misc + 8), "r"(0u) : "memory");
     if (i == 1) asm volatile("st.shared.u32 [%0], %1;" ::"r"(smem + L::misc + 4), "r"(0u) : "memory");
@@ -476,7 +476,7 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
           }
           if (e == 0 && lane == 0) args.counters[item.row_block] = 0;
         }
-        named_barrier(1, 128);  // the verdict word may be rewritten
+        named_barrier(1, 128);  // the decision word may be rewritten
       }
     }
     __syncwarp();
@@ -487,9 +487,9 @@ bxw_kernel(const BxrArgs args, const __grid_constant__ CUtensorMap tmap_x) {
   // the 4 epilogue warps together.
   if (MODE == kUmma && (warp < kDecoderWarps || warp >= kWinWarpEpilogue)) {
     if (ctx.wait(bar_final, 0)) {
-      const uint4 verdict = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
-      if (verdict.x)
-        reduce_row_block<NB>(args, verdict.y, verdict.z, verdict.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
+      const uint4 decision = lds128(smem + L::misc + 16);  // {reduce?, row block, first slot, parts}
+      if (decision.x)
+        reduce_row_block<NB>(args, decision.y, decision.z, decision.w, warp < kDecoderWarps ? warp : warp - 4, kDecoderWarps + 4, lane);
     }
   }
 
