@@ -553,13 +553,13 @@ class FastSession:
         decoder needs one, the same on every rank, for the ranks to stay in step."""
         from .sampling import Sampler
 
-        stops = {int(t) for t in stop_ids}
-        seq = self.batcher.active[st.slot]
         sampler = None
         if temperature > 0:
             if self.d.cfg.tp_world > 1 and seed is None:
                 raise ValueError("sampling on a tensor-parallel decoder needs a seed shared by the ranks")
             sampler = Sampler(temperature, top_p, device=self.d.dev, seed=seed)
+        stops = {int(t) for t in stop_ids}
+        seq = self.batcher.active[st.slot]
         emitted = 0
         if len(seq["tokens"]) == 1 and not getattr(st, "_first_out", False):
             st._first_out = True

@@ -4,8 +4,8 @@
 
 Every rank builds its shard of a small random decoder and a batch decoder over it; rank 0 also builds the whole model
 on its own GPU.  The ranks run a prompt and a few decode steps in step; the sharded logits must agree with the
-one-GPU logits within the tolerance of BF16 partial sums, every rank must draw the same tokens, and a graph replay
-must give what the eager step gave."""
+one-GPU logits within the tolerance of BF16 partial sums, every rank must draw the same tokens - arg-max tokens, and
+sampled ones from generators seeded alike -, and a graph replay must give what the eager step gave."""
 import os
 import sys
 
@@ -13,7 +13,7 @@ import torch
 import torch.distributed as dist
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
-from georefine_b200 import serve  # noqa: E402
+from georefine_b200 import sampling, serve  # noqa: E402
 
 
 def main():
@@ -52,6 +52,22 @@ def main():
         failures += int(worst > 4e-2)
         same_tokens = [batchers[0].active[s]["tokens"] == batchers[1].active[t]["tokens"] for s, t in zip(sorted(batchers[0].active), sorted(batchers[1].active))]
         print(f"sharded vs whole: worst relative logit difference {worst:.4f}; token streams equal: {same_tokens}")
+    # sampling: the summed logits are bit for bit the same on every rank, so generators seeded alike draw the same tokens
+    sampler = sampling.Sampler(0.9, 0.95, device=dev, seed=21)
+    drawn = []
+    for step in range(4):
+        drawn.append(list(batchers[0].step(sampler=sampler).values()))
+    mine = torch.tensor(drawn, device=dev)
+    lo, hi = mine.clone(), mine.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    failures += int(not torch.equal(lo, hi))
+    sess = serve.FastSession(d)
+    try:
+        list(sess.generate(serve.State(0, 1, [0]), max_tokens=1, temperature=0.5))
+        failures += 1                                   # a sharded decoder must demand a seed
+    except ValueError:
+        pass
     # eager against graph on the sharded engine: same rows, same state
     d.set_rows([0, 1], [40, 41], [9, 10])
     for slot in (0, 1):
