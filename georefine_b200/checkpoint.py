@@ -148,29 +148,49 @@ class PackageWords:
         self.consumed[name] = {"frame_sha256": row["frame_sha256"], "source_sha256": row["source_sha256"], "frame_bytes": len(frame)}
         return words.reshape(pkg.frame_shape(shape))
 
-    def _layer(self, prefix: str, leaf: str):
-        shapes = {k.removeprefix("mtp.layers.0."): v for k, v in mtp_shapes(self.config).items() if k.startswith("mtp.layers.0.")}
-        if leaf not in _LAYER:
-            raise KeyError(leaf)
-        parts = [self.tensor(prefix + t, shapes[t]) for t in _LAYER[leaf]]
-        return parts[0] if len(parts) == 1 else np.concatenate(parts, axis=0)
-
-    def __call__(self, name: str):
+    def members(self, name: str):
+        """The package tensors an engine tensor is made of, in row order: [(package name, shape), ...]."""
         cfg = self.config
+        layer_shapes = {k.removeprefix("mtp.layers.0."): v for k, v in mtp_shapes(cfg).items() if k.startswith("mtp.layers.0.")}
+
+        def layer(prefix, leaf):
+            if leaf not in _LAYER:
+                raise KeyError(name)
+            return [(prefix + t, layer_shapes[t]) for t in _LAYER[leaf]]
+
         if name == "embed" or (name == "lm_head" and self.tied):
-            return self.tensor("model.embed_tokens.weight", (cfg.vocab, cfg.hidden))
+            return [("model.embed_tokens.weight", (cfg.vocab, cfg.hidden))]
         if name == "lm_head":
-            return self.tensor("lm_head.weight", (cfg.vocab, cfg.hidden))
+            return [("lm_head.weight", (cfg.vocab, cfg.hidden))]
         if name == "final_norm":
-            return self.tensor("model.norm.weight", (cfg.hidden,))
+            return [("model.norm.weight", (cfg.hidden,))]
         parts = name.split(".")
         if len(parts) == 3 and parts[0] == "layers" and parts[1].isdigit() and int(parts[1]) < cfg.layers:
-            return self._layer(f"model.layers.{int(parts[1])}.", parts[2])
+            return layer(f"model.layers.{int(parts[1])}.", parts[2])
         if len(parts) == 2 and parts[0] == "mtp":
             if parts[1] in _MTP_TOP:
-                return self.tensor(_MTP_TOP[parts[1]], mtp_shapes(cfg)[_MTP_TOP[parts[1]]])
-            return self._layer("mtp.layers.0.", parts[1])
+                return [(_MTP_TOP[parts[1]], mtp_shapes(cfg)[_MTP_TOP[parts[1]]])]
+            return layer("mtp.layers.0.", parts[1])
         raise KeyError(name)
+
+    def __call__(self, name: str):
+        parts = [self.tensor(tensor, shape) for tensor, shape in self.members(name)]
+        return parts[0] if len(parts) == 1 else np.concatenate(parts, axis=0)
+
+    def identity(self, name: str, plan: str) -> str:
+        """A digest that names the resident image of an engine linear without decoding anything: the source digests of
+        its member tensors as the manifest records them, the way they are joined and sharded, and ``plan`` - whatever
+        else decides how the image is built (layout, tune record)."""
+        cfg = self.config
+        members = []
+        for tensor, shape in self.members(name):
+            row = self.rows.get(tensor)
+            if row is None:
+                raise ContextServingError(f"package lacks a tensor the decoder needs: {tensor}")
+            members.append([tensor, row.get("source_sha256"), list(shape)])
+        text = json.dumps({"members": members, "leaf": name.split(".")[-1], "tp": [cfg.tp_world, cfg.tp_rank],
+                           "heads": [cfg.heads, cfg.kv_heads, cfg.head_dim], "ffn": cfg.ffn, "plan": plan}, sort_keys=True)
+        return hashlib.sha256(text.encode()).hexdigest()
 
     def receipt(self) -> dict:
         """What has been loaded so far (the fields of the reference's MTP receipt, ``bitexact_context_mtp.py:379-393``)."""
@@ -180,26 +200,131 @@ class PackageWords:
                 "frame_bytes": sum(r["frame_bytes"] for r in self.consumed.values()), "loaded_from_bctx_only": True}
 
 
-def load_decoder_weights(package, device="cuda:0", *, config=None, tp_world=1, tp_rank=0, host_decoder=None, **kw):
-    """``serve.DecoderWeights`` of the decoder in ``package`` (``kw``: what ``DecoderWeights.from_words`` takes -
-    ``lin_factory``, ``max_m``, ``tune``, ``layout``).  The receipt of what was read is in ``weights.notes['receipt']``;
-    the ``PackageWords`` itself, for a later ``load_mtp_head``, in ``weights.notes['source']``."""
-    from .serve import DecoderWeights
+def linear_names(cfg, *, mtp: bool = False):
+    """The engine's compressed linears in the order a step runs them."""
+    names = [f"layers.{i}.{leaf}" for i in range(cfg.layers) for leaf in ("qkv", "o", "gate_up", "down")] + ["lm_head"]
+    return names + (["mtp.qkv", "mtp.o", "mtp.gate_up", "mtp.down", "mtp.fc"] if mtp else [])
+
+
+def _group_path(cache, identity: str) -> Path:
+    return Path(cache.root) / "groups" / identity[:2] / (identity + ".json")
+
+
+def resident_images(source: PackageWords, names, *, sm_count: int, layout=None, cache=None, tune=None, pool_threads=None, log=None):
+    """Resident images of the engine linears ``names``, built on host threads in parallel and - with an
+    ``image_cache.ImageCache`` - kept on disk, so that a restart reads images instead of decoding frames.  Returns
+    {name: (image, header, hit)}.
+
+    A linear of the engine is a join of package tensors (q | k | v, gate | up), possibly a tensor-parallel shard of it,
+    so its words have no digest in the manifest.  The cache entry itself is keyed and verified by the digest of the words
+    it was built from, like every entry (``ImageCache.get``); a small record ``groups/<identity>.json`` under the cache
+    root maps ``PackageWords.identity`` - known without decoding - to that digest, shape and worker count.  A record
+    that points to a missing or refused entry is a miss: the frames are decoded (each checked against its receipt), the
+    image is rebuilt and both are written again.  The reference's counterpart is its load-time transcode with a verified
+    cache and parallel workers (``glc_serve/bctx_v21_transcode.py``, ``transcode_cache.py``,
+    ``context_parallel_startup.py``)."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    from . import resident
+    from .package import atomic_write
+
+    cfg = source.config
+    log = log or (lambda message: None)
+
+    def plan(rows, cols):
+        chosen_layout, workers = layout, None
+        if tune and (rows, cols) in tune:
+            chosen_layout = tune[(rows, cols)][0] if chosen_layout is None else chosen_layout
+            workers = tune[(rows, cols)][1]
+        return chosen_layout or resident.DEFAULT_LAYOUT, workers or resident.default_workers(rows, cols, sm_count)
+
+    tuned = hashlib.sha256(repr(sorted((tuple(k), tuple(v)) for k, v in (tune or {}).items())).encode()).hexdigest()[:16]
+    build_plan = f"layout={layout},tune={tuned},sms={sm_count}"
+
+    def one(name):
+        identity = source.identity(name, build_plan)
+        if cache is not None:
+            try:
+                record = json.loads(_group_path(cache, identity).read_text())
+                image = cache.get(record["words_sha256"], tuple(record["shape"]), record["layout"], int(record["workers"]))
+                if image is not None:
+                    return image, resident.header_of(image), True
+            except (OSError, ValueError, KeyError, TypeError):
+                pass
+        words = np.ascontiguousarray(cfg.shard(name.split(".")[-1], source(name)))
+        chosen_layout, workers = plan(int(words.shape[0]), int(words.shape[1]))
+        digest = hashlib.sha256(words.astype("<u2").tobytes())
+        image, header = resident.build_image(words, workers, threads=1, layout=chosen_layout, source_sha256=digest.digest())
+        if cache is not None and cache.put(image, chosen_layout):
+            try:
+                atomic_write(_group_path(cache, identity), json.dumps({"words_sha256": digest.hexdigest(), "shape": list(words.shape),
+                                                                       "layout": chosen_layout, "workers": int(workers)}).encode())
+            except OSError as exc:
+                log(f"[checkpoint] cannot record {name} in the image cache: {exc}")
+        return image, header, False
+
+    names = list(names)
+    threads = pool_threads or max(1, min(len(names), os.cpu_count() or 1))
+    with ThreadPoolExecutor(max_workers=threads, thread_name_prefix="grb-checkpoint") as pool:
+        return dict(zip(names, pool.map(one, names)))
+
+
+def load_decoder_weights(package, device="cuda:0", *, config=None, tp_world=1, tp_rank=0, host_decoder=None, cache=None,
+                         pool_threads=None, lin_factory=None, max_m=128, tune=None, layout=None, log=None):
+    """``serve.DecoderWeights`` of the decoder in ``package``.  The linears are resident images built on host threads in
+    parallel (``resident_images``; ``cache``: an ``image_cache.ImageCache`` that keeps them across restarts), or whatever
+    ``lin_factory(name, words)`` returns.  The receipt of what was read from the package is in
+    ``weights.notes['receipt']``, the cache hits in ``weights.notes['image_cache_hits']``, and the ``PackageWords``
+    itself, for a later ``load_mtp_head``, in ``weights.notes['source']``."""
+    import torch
+
+    from . import resident
+    from .serve import DecoderWeights, LayerWeights
 
     if config is None:
         config = decoder_config(Path(package) / "sidecars" / "config.json", tp_world=tp_world, tp_rank=tp_rank)
     source = PackageWords(package, config, host_decoder=host_decoder)
-    weights = DecoderWeights.from_words(config, source, device, **kw)
-    weights.notes.update(receipt=source.receipt(), source=source)
+    if lin_factory is not None:
+        weights = DecoderWeights.from_words(config, source, device, lin_factory=lin_factory, max_m=max_m, tune=tune, layout=layout)
+        weights.notes.update(receipt=source.receipt(), source=source, image_cache_hits=0)
+        return weights
+    dev = torch.device(device)
+    sms, hits = resident.sm_count(dev), 0
+
+    def dense(name):
+        return torch.from_numpy(source(name).view(np.int16).copy()).view(torch.bfloat16).to(dev)
+
+    def linears(names):
+        """Built a batch at a time, so that the host holds the images of a few layers, not of the model."""
+        nonlocal hits
+        images = resident_images(source, names, sm_count=sms, layout=layout, cache=cache, tune=tune, pool_threads=pool_threads, log=log)
+        hits += sum(1 for _, _, hit in images.values() if hit)
+        return {name: resident.ResidentWeight(images.pop(name)[0], dev, max_m=max_m, verify=False) for name in names}
+
+    layers, per_batch = [], 4
+    for lo in range(0, config.layers, per_batch):
+        ids = range(lo, min(lo + per_batch, config.layers))
+        built = linears([f"layers.{i}.{leaf}" for i in ids for leaf in ("qkv", "o", "gate_up", "down")])
+        for i in ids:
+            p = f"layers.{i}."
+            layers.append(LayerWeights(dense(p + "norm1").reshape(-1), built[p + "qkv"], built[p + "o"], dense(p + "norm2").reshape(-1),
+                                       built[p + "gate_up"], built[p + "down"]))
+    lm_head = linears(["lm_head"])["lm_head"]
+    weights = DecoderWeights(config, dense("embed"), layers, dense("final_norm").reshape(-1), lm_head,
+                             {"distinct_layers": config.layers, "layers": config.layers})
+    weights.chain()
+    weights.notes.update(receipt=source.receipt(), source=source, image_cache_hits=hits)
     return weights
 
 
-def load_mtp_head(package, decoder, *, lin_factory=None, host_decoder=None):
+def load_mtp_head(package, decoder, *, lin_factory=None, host_decoder=None, cache=None, pool_threads=None):
     """The draft head (``serve.MTPHead``) over ``decoder`` from the package's ``mtp.*`` frames: all thirteen tensors or an
-    error, each checked against its receipt.  ``head.receipt`` says what was loaded."""
+    error, each checked against its receipt.  ``head.receipt`` says what was loaded (with a warm ``cache`` the matrices
+    come from their cached images, and the receipt lists only what was read from the package)."""
     import torch
 
-    from .resident import ResidentWeight
+    from . import resident
     from .serve import LayerWeights, MTPHead
 
     cfg, dev = decoder.cfg, decoder.dev
@@ -207,15 +332,17 @@ def load_mtp_head(package, decoder, *, lin_factory=None, host_decoder=None):
     missing = sorted(set(mtp_shapes(cfg)) - set(source.rows))
     if missing:
         raise ContextServingError(f"MTP manifest keys differ: missing={missing}")
+    matrices = ["mtp.qkv", "mtp.o", "mtp.gate_up", "mtp.down", "mtp.fc"]
+    images = {} if lin_factory is not None else resident_images(source, matrices, sm_count=resident.sm_count(dev), cache=cache,
+                                                                pool_threads=pool_threads)
 
     def norm(name):
         return torch.from_numpy(source("mtp." + name).view(np.int16).copy()).view(torch.bfloat16).reshape(-1).to(dev)
 
     def linear(name):
-        words = np.ascontiguousarray(source("mtp." + name))
         if lin_factory is not None:
-            return lin_factory("mtp." + name, words)
-        return ResidentWeight.from_words(words, dev, max_m=min(decoder.max_rows, 128), verify=False)
+            return lin_factory("mtp." + name, np.ascontiguousarray(source("mtp." + name)))
+        return resident.ResidentWeight(images.pop("mtp." + name)[0], dev, max_m=min(decoder.max_rows, 128), verify=False)
 
     layer = LayerWeights(norm("norm1"), linear("qkv"), linear("o"), norm("norm2"), linear("gate_up"), linear("down"))
     head = MTPHead(decoder, fc=linear("fc"), norm_e=norm("norm_e"), norm_h=norm("norm_h"), layer=layer, final_norm=norm("final_norm"))

@@ -520,7 +520,8 @@ class FastSession:
              max_len=4096, seed=1, lin_factory=None, tune=None, max_rows=128, **kw) -> "FastSession":
         """A session over ``weights``; or over the decoder of a BCTX ``package`` directory, filled from its frames alone
         (``georefine_b200.checkpoint``; the draft head too, as ``session.mtp_head``, when the package has ``mtp.*``
-        tensors); or over random-init weights of ``config``."""
+        tensors; ``cache=image_cache.ImageCache(...)`` keeps the resident images on disk for the next start); or over
+        random-init weights of ``config``."""
         source = None
         if weights is None and package is not None:
             from . import checkpoint
@@ -537,7 +538,8 @@ class FastSession:
             if source.has_mtp and weights.config.tp_world == 1:
                 from . import checkpoint
 
-                session.mtp_head = checkpoint.load_mtp_head(source, session.d, lin_factory=lin_factory)
+                session.mtp_head = checkpoint.load_mtp_head(source, session.d, lin_factory=lin_factory, cache=kw.get("cache"),
+                                                            pool_threads=kw.get("pool_threads"))
         return session
 
     def prefill(self, *, token_ids) -> State:

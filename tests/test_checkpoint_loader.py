@@ -150,3 +150,68 @@ def test_foreign_or_damaged_packages_are_refused(tmp_path, write_decoder_checkpo
         src("layers.0.down")
     with pytest.raises(ContextServingError):
         checkpoint.PackageWords(tmp_path / "nowhere")
+
+
+def test_resident_images_are_built_once_and_served_from_the_cache(packaged, tmp_path):
+    """The engine's linears as resident images: built from verified frames on the first start, read back from the image
+    cache - without touching a frame - on the next, and rebuilt when a record or an entry does not check out."""
+    from georefine_b200 import resident
+    from georefine_b200.image_cache import ImageCache
+
+    pkg_dir, t = packaged
+    cache = ImageCache(tmp_path / "cache")
+    cfg = checkpoint.decoder_config(pkg_dir / "sidecars" / "config.json")
+    names = checkpoint.linear_names(cfg, mtp=True)
+    assert names[:4] == ["layers.0.qkv", "layers.0.o", "layers.0.gate_up", "layers.0.down"] and names[-1] == "mtp.fc" and len(names) == 14
+    cold_source = checkpoint.PackageWords(pkg_dir)
+    cold = checkpoint.resident_images(cold_source, names, sm_count=148, cache=cache, pool_threads=4)
+    assert not any(hit for _, _, hit in cold.values()) and cache.stats["writes"] == len(names)
+    matrices = {n for n, w in t.items() if w.ndim == 2} - {"model.embed_tokens.weight"}
+    assert set(cold_source.consumed) == matrices                         # every matrix was read; the norms and the embedding were not
+    image, header, _ = cold["layers.1.qkv"]
+    want = np.concatenate([t[f"model.layers.1.self_attn.{x}_proj.weight"] for x in "qkv"])
+    assert (header.rows, header.cols) == want.shape and np.array_equal(resident.decode_image_host(image), want)
+    warm_source = checkpoint.PackageWords(pkg_dir)
+    warm = checkpoint.resident_images(warm_source, names, sm_count=148, cache=cache, pool_threads=4)
+    assert all(hit for _, _, hit in warm.values()) and not warm_source.consumed
+    assert all(np.array_equal(warm[n][0], cold[n][0]) for n in names)
+    # another build plan (layout, SM count) is another identity: nothing is served across plans
+    other = checkpoint.resident_images(checkpoint.PackageWords(pkg_dir), names[:2], sm_count=148, layout="rans", cache=cache)
+    assert not any(hit for _, _, hit in other.values()) and other["layers.0.qkv"][1].mode == resident.LAYOUTS["rans"]
+    assert warm_source.identity("layers.0.qkv", "a") != warm_source.identity("layers.0.qkv", "b") != warm_source.identity("layers.0.o", "b")
+    # a damaged record, and a record whose entry has been damaged, are misses that heal
+    records = sorted((tmp_path / "cache" / "groups").rglob("*.json"))
+    assert len(records) == len(names) + 2
+    records[0].write_text("{not json")
+    entry = next(p for p in (tmp_path / "cache").rglob("*.bxr"))
+    data = bytearray(entry.read_bytes())
+    data[-1] ^= 0xFF
+    entry.write_bytes(bytes(data))
+    again = checkpoint.resident_images(checkpoint.PackageWords(pkg_dir), names, sm_count=148, cache=cache)
+    assert 1 <= sum(1 for _, _, hit in again.values() if not hit) <= 2
+    assert all(np.array_equal(resident.decode_image_host(again[n][0]), resident.decode_image_host(cold[n][0])) for n in names)
+    assert all(hit for _, _, hit in checkpoint.resident_images(checkpoint.PackageWords(pkg_dir), names, sm_count=148, cache=cache).values())
+    # without a cache every call builds
+    assert not any(hit for _, _, hit in checkpoint.resident_images(checkpoint.PackageWords(pkg_dir), names[:3], sm_count=148).values())
+
+
+def test_shards_of_different_ranks_have_different_identities(tmp_path, write_decoder_checkpoint):
+    fields = dict(hidden=128, layers=1, heads=4, kv_heads=2, ffn=512, vocab=64)
+    t = write_decoder_checkpoint(tmp_path / "model", seed=9, mtp=False, **fields)
+    package.build(tmp_path / "model", tmp_path / "package")
+    from georefine_b200 import resident
+
+    got = {}
+    for rank in (0, 1):
+        cfg = checkpoint.decoder_config(tmp_path / "package" / "sidecars" / "config.json", tp_world=2, tp_rank=rank)
+        src = checkpoint.PackageWords(tmp_path / "package", cfg)
+        got[rank] = (src.identity("layers.0.down", "p"), checkpoint.resident_images(src, ["layers.0.down", "layers.0.qkv"], sm_count=148))
+    assert got[0][0] != got[1][0]
+    down = t["model.layers.0.mlp.down_proj.weight"]
+    for rank in (0, 1):
+        image, header, _ = got[rank][1]["layers.0.down"]
+        assert (header.rows, header.cols) == (128, 256)
+        assert np.array_equal(resident.decode_image_host(image), down[:, rank * 256:(rank + 1) * 256])
+        q, k, v = (t[f"model.layers.0.self_attn.{x}_proj.weight"] for x in "qkv")
+        want = np.concatenate([q[rank * 256:(rank + 1) * 256], k[rank * 128:(rank + 1) * 128], v[rank * 128:(rank + 1) * 128]])
+        assert np.array_equal(resident.decode_image_host(got[rank][1]["layers.0.qkv"][0]), want)

@@ -264,8 +264,11 @@ def test_session_from_a_package_serves_the_checkpoint_it_was_built_from(dev, tmp
     fields = dict(hidden=512, layers=2, heads=4, kv_heads=2, ffn=1024, vocab=1000)
     t = write_decoder_checkpoint(tmp_path / "model", seed=5, **fields)
     package.build(tmp_path / "model", tmp_path / "package", jobs=8)
-    sess = serve.FastSession.load(package=tmp_path / "package", device=dev, max_len=1024, max_rows=64, max_m=64)
-    assert sess.mtp_head is not None and sess.meta["receipt"]["loaded_from_bctx_only"]
+    from georefine_b200.image_cache import ImageCache
+
+    cache = ImageCache(tmp_path / "images")
+    sess = serve.FastSession.load(package=tmp_path / "package", device=dev, max_len=1024, max_rows=64, max_m=64, cache=cache)
+    assert sess.mtp_head is not None and sess.meta["receipt"]["loaded_from_bctx_only"] and sess.d.w.notes["image_cache_hits"] == 0
     assert sess.mtp_head.receipt["tensor_count"] == 13 and sess.d.cfg.ffn == 1024
 
     def group(prefix, leaf):           # the engine's tensors straight from the checkpoint in memory
@@ -315,3 +318,10 @@ def test_session_from_a_package_serves_the_checkpoint_it_was_built_from(dev, tmp
         spec.cycle()
     assert b.active[s]["tokens"][:20] == want
     spec.retire(s)
+    # a second start reads every image from the cache (2 layers x 4 + the output head, and the head's 5) and serves the same tokens
+    before = cache.stats["hits"]
+    again = serve.FastSession.load(package=tmp_path / "package", device=dev, max_len=1024, max_rows=64, max_m=64, cache=cache)
+    assert again.d.w.notes["image_cache_hits"] == 9 and cache.stats["hits"] - before == 14
+    assert not any(n.endswith("_proj.weight") for n in again.meta["receipt"]["tensor_names"])
+    st = again.prefill(token_ids=prompt)
+    assert list(again.generate(st, max_tokens=20)) == want
