@@ -178,16 +178,16 @@ class PackageWords:
         return parts[0] if len(parts) == 1 else np.concatenate(parts, axis=0)
 
     def identity(self, name: str, plan: str) -> str:
-        """A digest that names the resident image of an engine linear without decoding anything: the source digests of
-        its member tensors as the manifest records them, the way they are joined and sharded, and ``plan`` - whatever
-        else decides how the image is built (layout, tune record)."""
+        """A digest that names the resident image of an engine linear without decoding anything: the source and frame
+        digests of its member tensors as the manifest records them, the way they are joined and sharded, and ``plan`` -
+        whatever else decides how the image is built (layout, tune record)."""
         cfg = self.config
         members = []
         for tensor, shape in self.members(name):
             row = self.rows.get(tensor)
             if row is None:
                 raise ContextServingError(f"package lacks a tensor the decoder needs: {tensor}")
-            members.append([tensor, row.get("source_sha256"), list(shape)])
+            members.append([tensor, row.get("source_sha256"), row.get("frame_sha256"), list(shape)])
         text = json.dumps({"members": members, "leaf": name.split(".")[-1], "tp": [cfg.tp_world, cfg.tp_rank],
                            "heads": [cfg.heads, cfg.kv_heads, cfg.head_dim], "ffn": cfg.ffn, "plan": plan}, sort_keys=True)
         return hashlib.sha256(text.encode()).hexdigest()
