@@ -616,15 +616,23 @@ def indexed_decode_times(device):
         return a.elapsed_time(b) / reps * 1e3
 
     out = {"matrix": "4096x4096 seed 0", "frame_bytes": len(frame)}
-    for stride in (1024, 128):
-        t = CudaContextTensor(frame, stride=stride, device=device, fused=False)
+    # walk_stride = words per lane of the device walk.  1024 is the reference's geometry (one lane per restart block of
+    # the caller's stride); CudaContextTensor(frame, stride=1024) builds its index at 128 by default.
+    for walk in (1024, 128):
+        t = CudaContextTensor(frame, stride=1024, walk_stride=walk, device=device, fused=False)
         ok = bool(np.array_equal(t.decode().view(torch.int16).cpu().numpy().view(np.uint16), words))
         us = timed_us(lambda: t.decode(check=False))
-        out[f"bctx_decode_kernel_stride{stride}"] = {"us": round(us, 1), "dense_GBps": round(2 * words.size / us / 1e3, 1), "bit_exact": ok}
-        if stride == 1024:
+        out[f"bctx_decode_kernel_stride{walk}"] = {"us": round(us, 1), "dense_GBps": round(2 * words.size / us / 1e3, 1), "bit_exact": ok,
+                                                   "index_bytes": int(sum(v.numel() * v.element_size() for k, v in t.buffers.items()
+                                                                          if k.endswith(("_states", "_offsets"))))}
+        if walk == 1024:
             us = timed_us(lambda: F.linear(x, t.decode(check=False)))
             out["decode_plus_linear_m1_us"] = round(us, 1)
         del t
+    t = CudaContextTensor(frame, stride=1024, device=device, fused=False)
+    out["default"] = {"stride": 1024, "walk_stride": t.walk_stride, "decode_us": round(timed_us(lambda: t.decode(check=False)), 1),
+                      "decode_plus_linear_m1_us": round(timed_us(lambda: F.linear(x, t.decode(check=False))), 1)}
+    del t
     ref_root = ROOT / "baseline" / "_ref"
     if not (ref_root / "georefine_context_runtime" / "bitexact_context_gpu.py").is_file():
         out["reference_triton"] = {"unavailable": "the reference's modules are not staged under baseline/_ref"}

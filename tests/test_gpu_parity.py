@@ -41,9 +41,17 @@ def test_indexed_decode_is_bit_exact(golden, oracle_coder, dev, tag, stride):
     expect = oracle_coder.decode(frame)
     assert t.shape == expect.shape and t.source_sha256 == hashlib.sha256(expect.tobytes()).hexdigest()
     assert np.array_equal(_u16(t.decode()), expect)
+    assert t.stride == stride and t.walk_stride == (128 if stride == 1024 else stride)      # the device index may be finer than asked
     if t.mode != 1:
-        assert t.buffers["main_states"].numel() == (expect.size + stride - 1) // stride
+        assert t.buffers["main_states"].numel() == (expect.size + t.walk_stride - 1) // t.walk_stride
         assert t.resident_bytes >= sum(v.numel() * v.element_size() for v in t.buffers.values())
+    if stride == 1024:                                       # the reference's geometry: one lane per block of the caller's stride
+        coarse = CudaContextTensor(frame, stride=stride, walk_stride=stride, device=dev, fused=False)
+        assert np.array_equal(_u16(coarse.decode()), expect)
+        if coarse.mode != 1:
+            assert coarse.buffers["main_states"].numel() == (expect.size + stride - 1) // stride
+        with pytest.raises(ValueError):
+            CudaContextTensor(frame, stride=stride, walk_stride=100, device=dev, fused=False)
 
 
 @pytest.mark.parametrize("nr,nc", [(1, 1), (16, 4), (64, 16)])
@@ -59,9 +67,11 @@ def test_indexed_decode_class_configurations_and_gather(orc, oracle_coder, dev, 
     assert t.gather_rows(torch.empty(0, dtype=torch.int64)).shape == (0, 2048)
     with pytest.raises(IndexError):
         t.gather_rows(torch.tensor([96]))
+    coarse = CudaContextTensor(frame, stride=1024, walk_stride=1024, device=dev, fused=False)
+    assert np.array_equal(_u16(coarse.gather_rows(ids)), words[ids.numpy()])
     # a stride that does not divide the row length falls back to a full decode + index
     t2 = CudaContextTensor(frame, stride=1000, device=dev, fused=False)
-    assert np.array_equal(_u16(t2.gather_rows(ids)), words[ids.numpy()])
+    assert t2.walk_stride == 1000 and np.array_equal(_u16(t2.gather_rows(ids)), words[ids.numpy()])
 
 
 def test_indexed_decode_reports_corruption_without_faulting(orc, oracle_coder, dev):
