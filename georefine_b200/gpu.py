@@ -134,9 +134,11 @@ class CudaContextTensor:
             raise RuntimeError("CUDA is required")
         self.device = torch.device(device)
         self.stride = stride
+        if not isinstance(stride, int) or not 1 <= stride <= 65536:
+            raise base.CodecError("invalid checkpoint stride")
         if walk_stride is None:
-            walk_stride = WALK_STRIDE if isinstance(stride, int) and stride > WALK_STRIDE and stride % WALK_STRIDE == 0 else stride
-        elif not isinstance(stride, int) or walk_stride <= 0 or stride % walk_stride:
+            walk_stride = WALK_STRIDE if stride > WALK_STRIDE and stride % WALK_STRIDE == 0 else stride
+        elif not isinstance(walk_stride, int) or walk_stride <= 0 or stride % walk_stride:
             raise ValueError("walk_stride must divide stride")
         self.walk_stride = walk_stride
         indexed = index_frame(frame, walk_stride, keep_words=fused)
