@@ -410,22 +410,27 @@ class Batcher:
             if s in self.active and self.active[s]["tokens"][-1] is None:
                 self.active[s]["tokens"][-1] = int(pending[i])
 
-    def step(self, *, fetch: bool = True, sampler=None):
-        """One token for every active sequence.  Returns {slot: token} (``fetch=False``: nothing is read back, the
-        tokens stay on the device and feed the next step; ``sync_tokens`` collects them later).  With a
-        ``sampling.Sampler`` the tokens are drawn from the step's logits instead of taken as their arg-max."""
+    def step(self, *, fetch: bool = True, sampler=None, only=None):
+        """One token for every active sequence - or for the sequences in the slots ``only``, the others standing still.
+        Returns {slot: token} (``fetch=False``: nothing is read back, the tokens stay on the device and feed the next
+        step; ``sync_tokens`` collects them later).  With a ``sampling.Sampler`` the tokens are drawn from the step's
+        logits instead of taken as their arg-max.  As long as consecutive steps run the same sequences, nothing but the
+        replay of the step's graph happens on the host side."""
         import torch
 
         d = self.d
-        if not self.active:
+        wanted = sorted(self.active) if only is None else sorted({int(s) for s in only})
+        if not wanted:
             return {}
-        n = len(self.active)
+        if any(s not in self.active for s in wanted):
+            raise KeyError("step asked for a slot that holds no active sequence")
+        n = len(wanted)
         b = bucket_for(n, self.buckets)
-        for slot, s in self.active.items():
-            d.ensure_pages(slot, s["pos"])
-        if self._dirty:
+        for slot in wanted:
+            d.ensure_pages(slot, self.active[slot]["pos"])
+        if self._dirty or wanted != self._order:
             self.sync_tokens()
-            self._order = sorted(self.active)
+            self._order = wanted
             pad = b - n
             d.set_rows(self._order + [d.pad_slot] * pad, [self.active[s]["pos"] for s in self._order] + [0] * pad,
                        [self.active[s]["tokens"][-1] for s in self._order] + [0] * pad)
@@ -502,7 +507,8 @@ class State:
 
 
 class FastSession:
-    """One sequence at a time through the batched engine, under the reference's session API
+    """Sequences driven one at a time through the batched engine (several may be open; a call moves only its own), under
+    the reference's session API
     (``glc_serve/fastserve.py``): ``load`` / ``prefill`` / ``generate`` / ``extend`` / ``rollback``.  Greedy decoding at
     temperature 0, else temperature / top-p sampling from a seeded generator.  ``generate(spec_k=k, drafter=...)`` runs
     speculation: ``drafter(state, k)`` proposes k tokens (an MTP head, or any callable); greedy, the verify pass keeps
@@ -576,7 +582,7 @@ class FastSession:
             if spec_k and drafter is not None:
                 new = self.batcher.verify({st.slot: drafter(st, spec_k)}, sampler=sampler)[st.slot]
             else:
-                new = [self.batcher.step(sampler=sampler)[st.slot]]
+                new = [self.batcher.step(sampler=sampler, only=[st.slot])[st.slot]]
             for j, t in enumerate(new):
                 emitted += 1
                 yield t
