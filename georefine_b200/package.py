@@ -20,6 +20,7 @@ every frame; ``restore`` rebuilds the shards and compares their digests with the
     python -m georefine_b200.package build  <model dir> <package dir> [--jobs N] [--row-classes 16 --col-classes 4]
     python -m georefine_b200.package verify <package dir> [--no-decode]
     python -m georefine_b200.package restore <package dir> <destination dir>
+    python -m georefine_b200.package decode-check <package dir> <tensor name or frames/<key>.bctx> ...
 """
 from __future__ import annotations
 
@@ -340,7 +341,25 @@ def main(argv=None):
     r.add_argument("package")
     r.add_argument("destination")
     r.add_argument("--jobs", type=int, default=8)
+    c = sub.add_parser("decode-check", help="decode tensors of a package afresh and compare them with their receipts")
+    c.add_argument("package")
+    c.add_argument("tensors", nargs="+", help="tensor names, or frame paths as the manifest names them (frames/<key>.bctx)")
     args = ap.parse_args(argv)
+    if args.command == "decode-check":
+        rows = read_manifest(Path(args.package))["tensors"]
+        by_frame = {r["frame"]: r["name"] for r in rows}
+        results = {}
+        for item in args.tensors:
+            relative = item[len(str(args.package)):].lstrip("/") if item.startswith(str(args.package)) else item
+            name = by_frame.get(relative, item)
+            try:
+                results[name] = bool(decode_check(args.package, name))
+            except (KeyError, OSError, ValueError):
+                results[name] = False
+        print(json.dumps({"decode_check": results, "ok": all(results.values())}))
+        if not all(results.values()):
+            raise SystemExit(1)
+        return
     if args.command == "build":
         m = build(args.model_dir, args.package, jobs=args.jobs, row_classes=args.row_classes, col_classes=args.col_classes, log=print)
     elif args.command == "verify":

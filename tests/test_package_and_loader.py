@@ -250,3 +250,28 @@ def test_speculation_head_linear_counts_calls_and_checks_shapes():
         bad = Stand()
         bad.shape = (6,)
         serving.BCTXLinear(bad, "v")
+
+
+def test_command_line_build_verify_decode_check_restore(checkpoint, tmp_path, capsys):
+    """The tool's four commands (the reference's: build / verify / restore / decode-check,
+    bitexact_context_package.py:766-830)."""
+    model_dir, _ = checkpoint
+    out = tmp_path / "package"
+    package.main(["build", str(model_dir), str(out), "--jobs", "2"])
+    built = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert built["tensors"] == 7 and built["frame_bytes"] > 0
+    package.main(["verify", str(out)])
+    assert json.loads(capsys.readouterr().out)["tensors"] == 7
+    row = next(r for r in package.read_manifest(out)["tensors"] if r["name"] == "lin.weight")
+    package.main(["decode-check", str(out), "cube", row["frame"], str(out / row["frame"])])
+    assert json.loads(capsys.readouterr().out) == {"decode_check": {"cube": True, "lin.weight": True}, "ok": True}
+    frame = out / row["frame"]
+    data = bytearray(frame.read_bytes())
+    data[-40] ^= 1
+    frame.write_bytes(bytes(data))
+    with pytest.raises(SystemExit):
+        package.main(["decode-check", str(out), "lin.weight", "cube", "no.such.tensor"])
+    assert json.loads(capsys.readouterr().out) == {"decode_check": {"lin.weight": False, "cube": True, "no.such.tensor": False}, "ok": False}
+    frame.write_bytes(bytes(data[:-40]) + bytes([data[-40] ^ 1]) + bytes(data[-39:]))
+    package.main(["restore", str(out), str(tmp_path / "restored")])
+    assert sorted(json.loads(capsys.readouterr().out)["restored"]) == sorted(p.name for p in model_dir.glob("*.safetensors"))
