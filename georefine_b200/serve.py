@@ -195,6 +195,15 @@ class DecoderWeights:
         for a, b in zip(seq, seq[1:] + seq[:1]):
             a.then(b)
 
+    def descriptor_kinds(self) -> dict:
+        """How many of the step's linears are of which kind ("bctx", "dense", ...), as ``FastDecoder.descriptor_kinds``
+        reports them (``glc_serve/fastdec.py:942-946``)."""
+        kinds = {}
+        for w in self.linears():
+            kind = getattr(w, "kind", type(w).__name__)
+            kinds[kind] = kinds.get(kind, 0) + 1
+        return kinds
+
     def streamed_bytes(self) -> int:
         """Weight bytes one step streams from HBM (the reference's ``FastDecoder.streamed_bytes``)."""
         return int(sum(getattr(w, "coded_bytes", 0) for w in self.linears()))
@@ -520,6 +529,8 @@ class FastSession:
         self.batcher = Batcher(decoder)
         self.mtp_head = None
         self.meta = {"streamed_bytes_per_step": decoder.w.streamed_bytes()}
+        if hasattr(decoder.w, "descriptor_kinds"):
+            self.meta["descriptors"] = decoder.w.descriptor_kinds()
 
     @classmethod
     def load(cls, *, package=None, config: DecoderConfig | None = None, weights: DecoderWeights | None = None, device="cuda:0",

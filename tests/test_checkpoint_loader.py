@@ -92,7 +92,7 @@ def test_decoder_weights_and_draft_head_from_frames_alone(packaged):
     assert np.array_equal(w.final_norm.view(torch.int16).numpy().view(np.uint16), t["model.norm.weight"])
     every_trunk_tensor = {n for n in t if not n.startswith("mtp.")}
     assert set(w.notes["receipt"]["tensor_names"]) == every_trunk_tensor
-    assert w.streamed_bytes() == sum(x.coded_bytes for x in w.linears())
+    assert w.streamed_bytes() == sum(x.coded_bytes for x in w.linears()) and w.descriptor_kinds() == {"FakeLinear": 9}
     # tensor parallelism: rank 1 of 2 gets its head's rows of q, and the second half of the FFN columns of down
     # (one KV head cannot be split: the configuration refuses)
     with pytest.raises(ValueError):
