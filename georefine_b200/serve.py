@@ -739,6 +739,12 @@ class MTPSpeculator:
         self.b, self.head, self.k = batcher, head, int(k)
         self.first = {}     # slot -> the head's pending first draft
         self.hidden = {}    # slot -> the head's own hidden state behind that draft (input of the second draft)
+        self.stats = {"cycles": 0, "drafts_accepted": 0, "emitted": 0}     # per sequence and cycle (fastdec.py:930-940)
+
+    @property
+    def mean_tokens_per_cycle(self):
+        """Tokens emitted per sequence and cycle so far (1 = no draft ever accepted, k + 1 = all of them)."""
+        return self.stats["emitted"] / self.stats["cycles"] if self.stats["cycles"] else None
 
     def admit(self, prompt_ids, *, sampler=None) -> int:
         """Admits a sequence and runs the head over its prompt (trunk hidden of position p - 1 with token p).  ``sampler``:
@@ -811,6 +817,9 @@ class MTPSpeculator:
             at += len(out[s])
             self.first[s] = got[at - 1]
             self.hidden[s] = head.z[at - 1:at].clone()
+            self.stats["cycles"] += 1
+            self.stats["emitted"] += len(out[s])
+            self.stats["drafts_accepted"] += len(out[s]) - 1
         return out
 
     def retire(self, slot: int) -> None:

@@ -192,6 +192,8 @@ def test_mtp_head_speculation_in_a_batch_is_exact(dev, small):
     for _ in range(12):
         out = spec.cycle()
         assert all(1 <= len(v) <= 6 for v in out.values())
+    assert spec.stats["cycles"] == 36 and spec.stats["emitted"] == sum(len(b.active[s]["tokens"]) - 1 for s in slots)
+    assert spec.stats["drafts_accepted"] == spec.stats["emitted"] - 36 and 1 <= spec.mean_tokens_per_cycle <= 6
     for s, want in zip(slots, alone):
         got = b.active[s]["tokens"]
         assert got[:20] == want[:len(got[:20])] and len(got) >= 13
